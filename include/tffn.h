@@ -1,0 +1,155 @@
+/* tffn.h — C ABI of the B200 inference path of tensor-ffn (Qwen2.5 decode with the base FFN
+ * plus the expert-FFN delta at every layer).
+ *
+ * The reference has no FFI layer: its boundary is a set of C++ free functions over plain
+ * structs of device pointers, called only from its main() (inference/src/main.cpp:97-204).
+ * Each entry point below names the reference function it stands in for. Differences that a
+ * binding has to know about:
+ *   - the reference prints and calls exit(1) on every error (inference/include/backend/memory.h:5-11);
+ *     these functions return a status (0 ok, <0 error) and keep a per-thread message in
+ *     tffn_last_error();
+ *   - the reference keeps one sequence per QwenModel (KV cache and scratch live inside it,
+ *     inference/include/model/qwen.h:59-99); here weights (tffn_model, tffn_expert) are
+ *     immutable after load and a tffn_session owns the paged KV cache, scratch and the per-slot
+ *     sequence state, so one model serves many sessions and a session serves many sequences;
+ *   - token ids and logits cross this boundary in HOST memory; the session moves them.
+ * Threading: a session is used by one host thread at a time; different sessions may be used
+ * from different threads. All functions are synchronous unless stated.
+ */
+#ifndef TFFN_H
+#define TFFN_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tffn_model tffn_model;
+typedef struct tffn_expert tffn_expert;
+typedef struct tffn_session tffn_session;
+typedef struct tffn_tokenizer tffn_tokenizer;
+
+enum {
+    TFFN_OK = 0,
+    TFFN_ERR_INVALID = -1,     /* bad argument */
+    TFFN_ERR_IO = -2,          /* file cannot be opened / read */
+    TFFN_ERR_FORMAT = -3,      /* bad magic, malformed header, missing tensor, wrong dtype */
+    TFFN_ERR_SHAPE = -4,       /* tensor or expert shape does not match the model */
+    TFFN_ERR_CUDA = -5,        /* CUDA runtime error, or no CUDA device */
+    TFFN_ERR_CAPACITY = -6,    /* KV cache / batch / sequence capacity exceeded */
+    TFFN_ERR_UNSUPPORTED = -7, /* shape outside what the kernels support */
+    TFFN_ERR_DEVICE = -8       /* a kernel reported a status (bounded wait ran out, index check) */
+};
+
+/* QwenConfig (inference/include/model/qwen.h:9-23) */
+typedef struct tffn_config {
+    int32_t hidden_size, intermediate_size, num_layers, num_heads, num_kv_heads, head_dim;
+    int32_t vocab_size, max_position_embeddings;
+    float rms_norm_eps, rope_theta;
+    int32_t eos_token_id, bos_token_id, tie_embeddings;
+} tffn_config;
+
+const char* tffn_last_error(void);
+int tffn_version(void);
+/* number of CUDA devices visible, 0 without a GPU (never fails) */
+int tffn_device_count(void);
+
+/* ---- host-only helpers (no GPU needed) ------------------------------------------------- */
+/* qwen_config_from_json (inference/src/model/qwen.cu:21-63) */
+int tffn_config_read(const char* model_dir, tffn_config* out);
+/* Header of an expert .bin (inference/src/io/checkpoint.cpp:15-31); also checks the file length. */
+int tffn_expert_probe(const char* path, uint32_t* version, uint32_t* num_layers, uint32_t* hidden,
+                      uint32_t* intermediate);
+/* checkpoint_save's file format (trainer/src/io/checkpoint.cpp:15-52): mats[layer*3 + m] points
+ * to fp32 [intermediate*hidden], m = 0 gate, 1 up, 2 down. */
+int tffn_expert_write(const char* path, uint32_t num_layers, uint32_t hidden, uint32_t intermediate,
+                      const float* const* mats);
+/* SafeTensorsDir::open / has (inference/src/io/safetensors.cpp:104-131): counts shards and
+ * tensors; dtype_out (>= 8 bytes) and nbytes_out describe `name` when it is not NULL. */
+int tffn_safetensors_probe(const char* model_dir, const char* name, int32_t* num_shards, int32_t* num_tensors,
+                           char* dtype_out, uint64_t* nbytes_out);
+/* io::Tokenizer (inference/include/io/tokenizer.h:9-24, inference/src/io/tokenizer.cpp) */
+int tffn_tokenizer_load(const char* model_dir, tffn_tokenizer** out);
+void tffn_tokenizer_free(tffn_tokenizer* t);
+/* returns the number of ids (may exceed cap; only cap are written), <0 on error */
+int tffn_tokenizer_encode(const tffn_tokenizer* t, const char* text, uint32_t* ids, int cap);
+/* returns the number of bytes of the decoded text (without NUL; may exceed cap), <0 on error */
+int tffn_tokenizer_decode(const tffn_tokenizer* t, const uint32_t* ids, int n, char* out, int cap);
+int tffn_tokenizer_token_id(const tffn_tokenizer* t, const char* token, uint32_t* id);
+int tffn_tokenizer_special(const tffn_tokenizer* t, uint32_t* eos, uint32_t* bos, uint32_t* pad);
+
+/* ---- model / expert -------------------------------------------------------------------- */
+/* qwen_load minus the KV cache and scratch (inference/src/model/qwen.cu:80-132): reads
+ * config.json and every *.safetensors of the directory, uploads the weights to `device`,
+ * builds the layouts the kernels stream. tp_rank/tp_size must be 0/1. */
+int tffn_model_load(const char* model_dir, int device, int tp_rank, int tp_size, tffn_model** out);
+void tffn_model_free(tffn_model* m); /* qwen_free (qwen.cu:176-209) */
+int tffn_model_config(const tffn_model* m, tffn_config* out);
+/* bytes of weight a decode step streams from HBM (every matrix once), with/without an expert */
+uint64_t tffn_model_weight_bytes(const tffn_model* m, int with_expert);
+
+/* expert_alloc + checkpoint_load + output_scale (inference/src/model/expert.cu:9-31,
+ * inference/src/io/checkpoint.cpp:11-65, inference/src/main.cpp:109-119): fp32 file -> bf16 (RNE)
+ * on the device. The shape must match the model. */
+int tffn_expert_load(const tffn_model* m, const char* path, float scale, tffn_expert** out);
+int tffn_expert_set_scale(tffn_expert* e, float scale); /* ExpertModel::output_scale */
+float tffn_expert_get_scale(const tffn_expert* e);
+void tffn_expert_free(tffn_expert* e); /* expert_free (expert.cu:33-42) */
+
+/* ---- session --------------------------------------------------------------------------- */
+/* The KV cache + scratch part of qwen_load (qwen.cu:134-171), paged: max_batch sequence slots
+ * of up to max_seq tokens each. expert may be NULL (base model only). cuda_stream: a
+ * cudaStream_t, or NULL for a stream the session creates. */
+int tffn_session_create(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
+                        tffn_session** out);
+void tffn_session_free(tffn_session* s);
+/* qwen_reset (qwen.cu:174) for one slot, or for all with slot = -1: frees the slot's pages. */
+int tffn_session_reset(tffn_session* s, int slot);
+int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */
+/* 0: plain stream launches. 1: programmatic dependent launch between the batch-1 kernels.
+ * 2: 1 + the whole batch-1 step replayed from a CUDA graph. Default 1. */
+int tffn_session_set_launch_mode(tffn_session* s, int mode);
+/* Which path single-token steps take: 1 (default) the fused batch-1 kernels when the shape
+ * allows, 0 the batched tensor-core path. */
+int tffn_session_set_bs1_path(tffn_session* s, int enable);
+/* Keep a copy of the residual stream after every layer of the next tffn_prefill / tffn_forward
+ * (up to max_rows token rows); read it with tffn_session_get_hidden. 0 rows = off. */
+int tffn_session_capture_hidden(tffn_session* s, int max_rows);
+/* dst: bf16 bits [rows, hidden] of layer `layer` from the last captured call; returns rows. */
+int tffn_session_get_hidden(tffn_session* s, int layer, uint16_t* dst, int max_rows);
+
+/* qwen_forward for a prompt (inference/src/main.cpp:172-180): appends seq_lens[i] tokens to
+ * slot i for i < n_seqs (tokens concatenated in slot order), returns the greedy pick after
+ * each prompt's last token in next_tokens[n_seqs] and, if logits_last != NULL, that row's
+ * fp32 logits in logits_last[n_seqs, vocab]. */
+int tffn_prefill(tffn_session* s, const int32_t* tokens, const int32_t* seq_lens, int n_seqs, int32_t* next_tokens,
+                 float* logits_last);
+/* qwen_forward with all-row logits, one slot: appends T tokens to `slot` and writes fp32
+ * logits[T, vocab] (what the reference's d_logits holds after a call, qwen.cu:450-454). */
+int tffn_forward(tffn_session* s, int slot, const int32_t* tokens, int T, float* logits);
+/* One step of the decode loop (inference/src/main.cpp:183-197) for slots 0..n_seqs-1:
+ * feeds tokens_in[i] (or, if NULL, the slot's previous greedy pick), appends it to the cache,
+ * returns the greedy pick in next_tokens[i] and optionally fp32 logits[n_seqs, vocab]. */
+int tffn_decode_step(tffn_session* s, const int32_t* tokens_in, int n_seqs, int32_t* next_tokens, float* logits);
+/* `steps` greedy steps back to back with no host round trip (each step feeds the previous
+ * pick); tokens_out[steps, n_seqs] (host) may be NULL. Asynchronous part ends before return. */
+int tffn_decode_run(tffn_session* s, int n_seqs, int steps, int32_t* tokens_out);
+/* Device status word (0 = none) and kernel launches issued by the session so far. */
+int tffn_session_status(tffn_session* s);
+uint64_t tffn_session_launch_count(const tffn_session* s);
+/* the stream the session launches on (a cudaStream_t) */
+void* tffn_session_stream(const tffn_session* s);
+
+/* ---- kernel-level entry points used by the tests ---------------------------------------- */
+/* out[T,N] = X[T,K] * W[N,K]^T on the tensor-core GEMM of the batched path (bf16 bits in,
+ * fp32 out, host pointers); splits = 0 lets the launcher choose the K split.
+ * Stands in for gemm_bf16 (inference/src/backend/cuda_ops.cu:18-29). */
+int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits);
+/* Runs a kernel that waits on a barrier nothing signals; returns the device status it
+ * recorded (expected: 5). Proves that a wait that runs out returns instead of hanging. */
+int tffn_op_wait_selftest(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

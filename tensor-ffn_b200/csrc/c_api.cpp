@@ -1,0 +1,335 @@
+// The C ABI (include/tffn.h): translates exceptions into status codes and keeps the last
+// message per thread. No torch types, plain pointers and sizes only.
+#include "../../include/tffn.h"
+#include "engine.h"
+#include <cstring>
+#include <memory>
+#include <vector>
+
+using namespace tffn;
+
+struct tffn_model { Model* m; };
+struct tffn_expert { Expert* e; };
+struct tffn_session { Session* s; };
+struct tffn_tokenizer { Tokenizer t; };
+
+static thread_local std::string g_last_error;
+
+template <typename F>
+static int guard(F&& f) {
+    try {
+        f();
+        return TFFN_OK;
+    } catch (const Error& e) {
+        g_last_error = e.what();
+        return e.code;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return TFFN_ERR_INVALID;
+    } catch (...) {
+        g_last_error = "unknown error";
+        return TFFN_ERR_INVALID;
+    }
+}
+static void need(bool ok, const char* what) {
+    if (!ok) throw Error(kErrInvalid, what);
+}
+
+extern "C" {
+
+const char* tffn_last_error(void) { return g_last_error.c_str(); }
+int tffn_version(void) { return 100; }
+int tffn_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int tffn_config_read(const char* model_dir, tffn_config* out) {
+    return guard([&] {
+        need(model_dir && out, "NULL argument");
+        Config c = read_config(model_dir);
+        out->hidden_size = c.hidden_size; out->intermediate_size = c.intermediate_size; out->num_layers = c.num_layers;
+        out->num_heads = c.num_heads; out->num_kv_heads = c.num_kv_heads; out->head_dim = c.head_dim;
+        out->vocab_size = c.vocab_size; out->max_position_embeddings = c.max_seq_len;
+        out->rms_norm_eps = c.rms_norm_eps; out->rope_theta = c.rope_theta;
+        out->eos_token_id = c.eos_token_id; out->bos_token_id = c.bos_token_id; out->tie_embeddings = c.tie_embeddings;
+    });
+}
+
+int tffn_expert_probe(const char* path, uint32_t* version, uint32_t* num_layers, uint32_t* hidden, uint32_t* intermediate) {
+    return guard([&] {
+        need(path, "NULL path");
+        ExpertFile f(path);
+        if (version) *version = f.hdr.version;
+        if (num_layers) *num_layers = f.hdr.num_layers;
+        if (hidden) *hidden = f.hdr.hidden;
+        if (intermediate) *intermediate = f.hdr.intermediate;
+    });
+}
+
+int tffn_expert_write(const char* path, uint32_t num_layers, uint32_t hidden, uint32_t intermediate, const float* const* mats) {
+    return guard([&] {
+        need(path && mats && num_layers && hidden && intermediate, "bad argument");
+        write_expert(path, num_layers, hidden, intermediate, mats);
+    });
+}
+
+int tffn_safetensors_probe(const char* model_dir, const char* name, int32_t* num_shards, int32_t* num_tensors, char* dtype_out,
+                           uint64_t* nbytes_out) {
+    return guard([&] {
+        need(model_dir, "NULL directory");
+        SafeTensorsDir d(model_dir);
+        if (num_shards) *num_shards = (int32_t)d.num_shards();
+        if (num_tensors) *num_tensors = (int32_t)d.num_tensors();
+        if (name) {
+            const TensorInfo& ti = d.get(name);
+            if (dtype_out) {
+                strncpy(dtype_out, ti.dtype.c_str(), 7);
+                dtype_out[7] = 0;
+            }
+            if (nbytes_out) *nbytes_out = ti.nbytes;
+        }
+    });
+}
+
+int tffn_tokenizer_load(const char* model_dir, tffn_tokenizer** out) {
+    return guard([&] {
+        need(model_dir && out, "NULL argument");
+        std::unique_ptr<tffn_tokenizer> t(new tffn_tokenizer());
+        t->t.load(model_dir);
+        *out = t.release();
+    });
+}
+void tffn_tokenizer_free(tffn_tokenizer* t) { delete t; }
+int tffn_tokenizer_encode(const tffn_tokenizer* t, const char* text, uint32_t* ids, int cap) {
+    int n = 0;
+    int rc = guard([&] {
+        need(t && text, "NULL argument");
+        auto v = t->t.encode(text);
+        n = (int)v.size();
+        for (int i = 0; i < n && i < cap && ids; ++i) ids[i] = v[i];
+    });
+    return rc < 0 ? rc : n;
+}
+int tffn_tokenizer_decode(const tffn_tokenizer* t, const uint32_t* ids, int n, char* out, int cap) {
+    int len = 0;
+    int rc = guard([&] {
+        need(t && (ids || n == 0) && n >= 0, "bad argument");
+        std::string s = t->t.decode(std::vector<uint32_t>(ids, ids + n));
+        len = (int)s.size();
+        if (out && cap > 0) {
+            int m = len < cap - 1 ? len : cap - 1;
+            memcpy(out, s.data(), m);
+            out[m] = 0;
+        }
+    });
+    return rc < 0 ? rc : len;
+}
+int tffn_tokenizer_token_id(const tffn_tokenizer* t, const char* token, uint32_t* id) {
+    return guard([&] {
+        need(t && token && id, "NULL argument");
+        *id = t->t.get_id(token);
+    });
+}
+int tffn_tokenizer_special(const tffn_tokenizer* t, uint32_t* eos, uint32_t* bos, uint32_t* pad) {
+    return guard([&] {
+        need(t, "NULL tokenizer");
+        if (eos) *eos = t->t.eos_id;
+        if (bos) *bos = t->t.bos_id;
+        if (pad) *pad = t->t.pad_id;
+    });
+}
+
+int tffn_model_load(const char* model_dir, int device, int tp_rank, int tp_size, tffn_model** out) {
+    return guard([&] {
+        need(model_dir && out, "NULL argument");
+        std::unique_ptr<Model> m(Model::load(model_dir, device, tp_rank, tp_size));
+        *out = new tffn_model{m.release()};
+    });
+}
+void tffn_model_free(tffn_model* m) {
+    if (!m) return;
+    delete m->m;
+    delete m;
+}
+int tffn_model_config(const tffn_model* m, tffn_config* out) {
+    return guard([&] {
+        need(m && out, "NULL argument");
+        const Config& c = m->m->cfg;
+        out->hidden_size = c.hidden_size; out->intermediate_size = c.intermediate_size; out->num_layers = c.num_layers;
+        out->num_heads = c.num_heads; out->num_kv_heads = c.num_kv_heads; out->head_dim = c.head_dim;
+        out->vocab_size = c.vocab_size; out->max_position_embeddings = c.max_seq_len;
+        out->rms_norm_eps = c.rms_norm_eps; out->rope_theta = c.rope_theta;
+        out->eos_token_id = c.eos_token_id; out->bos_token_id = c.bos_token_id; out->tie_embeddings = c.tie_embeddings;
+    });
+}
+uint64_t tffn_model_weight_bytes(const tffn_model* m, int with_expert) {
+    if (!m) return 0;
+    const Config& c = m->m->cfg;
+    uint64_t b = m->m->weight_bytes_base;
+    if (with_expert) b += (uint64_t)c.num_layers * 3 * c.hidden_size * c.intermediate_size * 2;
+    return b;
+}
+
+int tffn_expert_load(const tffn_model* m, const char* path, float scale, tffn_expert** out) {
+    return guard([&] {
+        need(m && path && out, "NULL argument");
+        std::unique_ptr<Expert> e(Expert::load(m->m, path, scale));
+        *out = new tffn_expert{e.release()};
+    });
+}
+int tffn_expert_set_scale(tffn_expert* e, float scale) {
+    return guard([&] {
+        need(e, "NULL expert");
+        e->e->scale = scale;
+    });
+}
+float tffn_expert_get_scale(const tffn_expert* e) { return e ? e->e->scale : 0.f; }
+void tffn_expert_free(tffn_expert* e) {
+    if (!e) return;
+    delete e->e;
+    delete e;
+}
+
+int tffn_session_create(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
+                        tffn_session** out) {
+    return guard([&] {
+        need(m && out, "NULL argument");
+        std::unique_ptr<Session> s(new Session(m->m, expert ? expert->e : nullptr, max_batch, max_seq, (cudaStream_t)cuda_stream));
+        *out = new tffn_session{s.release()};
+    });
+}
+void tffn_session_free(tffn_session* s) {
+    if (!s) return;
+    delete s->s;
+    delete s;
+}
+int tffn_session_reset(tffn_session* s, int slot) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->reset(slot);
+    });
+}
+int tffn_session_seq_len(const tffn_session* s, int slot) {
+    if (!s || slot < 0) return TFFN_ERR_INVALID;
+    int n = -1;
+    int rc = guard([&] { n = s->s->seq_len(slot); });
+    return rc < 0 ? rc : n;
+}
+int tffn_session_set_launch_mode(tffn_session* s, int mode) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_launch_mode(mode);
+    });
+}
+int tffn_session_set_bs1_path(tffn_session* s, int enable) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_bs1_path(enable != 0);
+    });
+}
+int tffn_session_capture_hidden(tffn_session* s, int max_rows) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->capture_hidden(max_rows);
+    });
+}
+int tffn_session_get_hidden(tffn_session* s, int layer, uint16_t* dst, int max_rows) {
+    int rows = 0;
+    int rc = guard([&] {
+        need(s, "NULL session");
+        rows = s->s->get_hidden(layer, dst, max_rows);
+    });
+    return rc < 0 ? rc : rows;
+}
+int tffn_prefill(tffn_session* s, const int32_t* tokens, const int32_t* seq_lens, int n_seqs, int32_t* next_tokens,
+                 float* logits_last) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->prefill(tokens, seq_lens, n_seqs, next_tokens, logits_last);
+    });
+}
+int tffn_forward(tffn_session* s, int slot, const int32_t* tokens, int T, float* logits) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->forward(slot, tokens, T, logits);
+    });
+}
+int tffn_decode_step(tffn_session* s, const int32_t* tokens_in, int n_seqs, int32_t* next_tokens, float* logits) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->decode_step(tokens_in, n_seqs, next_tokens, logits);
+    });
+}
+int tffn_decode_run(tffn_session* s, int n_seqs, int steps, int32_t* tokens_out) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->decode_run(n_seqs, steps, tokens_out);
+    });
+}
+int tffn_session_status(tffn_session* s) {
+    int st = 0;
+    int rc = guard([&] {
+        need(s, "NULL session");
+        st = s->s->status();
+    });
+    return rc < 0 ? rc : st;
+}
+uint64_t tffn_session_launch_count(const tffn_session* s) { return s ? s->s->launch_count() : 0; }
+void* tffn_session_stream(const tffn_session* s) { return s ? (void*)s->s->stream() : nullptr; }
+
+int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits) {
+    return guard([&] {
+        need(X && W && out && T > 0 && N > 0 && K > 0 && K % 8 == 0, "bad GEMM arguments");
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
+        TFFN_CUDA(cudaSetDevice(device));
+        cudaDeviceProp prop;
+        TFFN_CUDA(cudaGetDeviceProperties(&prop, device));
+        const int rows = T < 256 ? 256 : T;
+        DeviceBuffer dx, dw, dout, part, cnt, status;
+        dx.alloc((size_t)rows * K * 2);
+        dw.alloc((size_t)N * K * 2);
+        dout.alloc((size_t)T * N * 4);
+        part.alloc((size_t)64 << 20);
+        cnt.alloc(8192 * 4);
+        status.alloc(4);
+        TFFN_CUDA(cudaMemcpy(dx.p, X, (size_t)T * K * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(dw.p, W, (size_t)N * K * 2, cudaMemcpyHostToDevice));
+        GemmCall g;
+        memset(&g, 0, sizeof g);
+        g.op[0] = {dw.as<bf16>(), K, dx.as<bf16>(), K, K};
+        g.N = N; g.T = T; g.mode = GEMM_STORE_F32; g.alpha = 1.f; g.out = dout.p; g.ldo = N; g.x_rows_alloc = rows;
+        GemmWorkspace ws{part.as<float>(), part.bytes / 4, cnt.as<int>(), 8192, status.as<int>(), prop.multiProcessorCount};
+        int rc = launch_gemm(g, ws, 0, splits);
+        if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");
+        if (rc != 0) cuda_check((cudaError_t)rc, "tensor-core GEMM launch", __FILE__, __LINE__);
+        TFFN_CUDA(cudaDeviceSynchronize());
+        int st = 0;
+        TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
+        if (st) throw Error(kErrDevice, "GEMM kernel reported device status " + std::to_string(st));
+        TFFN_CUDA(cudaMemcpy(out, dout.p, (size_t)T * N * 4, cudaMemcpyDeviceToHost));
+    });
+}
+
+int tffn_op_wait_selftest(int device) {
+    int st = 0;
+    int rc = guard([&] {
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
+        TFFN_CUDA(cudaSetDevice(device));
+        DeviceBuffer status;
+        status.alloc(4);
+        launch_wait_selftest(status.as<int>(), 0);
+        TFFN_CUDA(cudaGetLastError());
+        TFFN_CUDA(cudaDeviceSynchronize());
+        TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
+    });
+    return rc < 0 ? rc : st;
+}
+
+}  // extern "C"

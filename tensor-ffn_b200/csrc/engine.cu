@@ -1,0 +1,767 @@
+#include "engine.h"
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+
+namespace tffn {
+
+void cuda_check(cudaError_t e, const char* what, const char* file, int line) {
+    if (e == cudaSuccess) return;
+    char buf[512];
+    snprintf(buf, sizeof buf, "CUDA error %s:%d — %s (%s)", file, line, cudaGetErrorString(e), what);
+    throw Error(kErrCuda, buf);
+}
+
+void DeviceBuffer::alloc(size_t n) {
+    release();
+    if (n == 0) return;
+    TFFN_CUDA(cudaMalloc(&p, n));
+    bytes = n;
+    TFFN_CUDA(cudaMemset(p, 0, n));
+}
+void DeviceBuffer::release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    bytes = 0;
+}
+
+namespace {
+
+void upload(DeviceBuffer& dst, const void* src, size_t bytes) {
+    dst.alloc(bytes);
+    TFFN_CUDA(cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice));
+}
+
+// one block: publish the picks as the next step's inputs, advance the sequence lengths
+__global__ void k_decode_advance(const int* __restrict__ picks, int n, int* __restrict__ dec_tokens, int* __restrict__ seq_len,
+                                 int* __restrict__ ring, int* __restrict__ step_counter) {
+    const int st = *step_counter;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        dec_tokens[i] = picks[i];
+        seq_len[i] += 1;
+        if (ring) ring[(size_t)st * n + i] = picks[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *step_counter = st + 1;
+}
+
+__global__ void k_copy_rows_bf16(const bf16* __restrict__ src, bf16* __restrict__ dst, size_t n16) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n16) ((uint4*)dst)[i] = ((const uint4*)src)[i];
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ Model
+Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size) {
+    if (tp_size != 1 || tp_rank != 0) throw Error(kErrUnsupported, "tensor parallel loading is not available: tp_size must be 1");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
+    if (device < 0 || device >= ndev) throw Error(kErrInvalid, "device index out of range");
+    TFFN_CUDA(cudaSetDevice(device));
+    std::unique_ptr<Model> m(new Model());
+    m->device = device;
+    cudaDeviceProp prop;
+    TFFN_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10) throw Error(kErrUnsupported, "this library is built for sm_100a (B200) only");
+    m->num_sms = prop.multiProcessorCount;
+    m->cfg = read_config(dir);
+    const Config& c = m->cfg;
+    const size_t H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
+    const size_t nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    if (!(hd == 64 || hd == 128)) throw Error(kErrUnsupported, "head_dim must be 64 or 128");
+    if (H % 8 || I % 8) throw Error(kErrUnsupported, "hidden and intermediate sizes must be multiples of 8");
+    if (nh / nkv > 8) throw Error(kErrUnsupported, "more than 8 query heads per kv head");
+
+    SafeTensorsDir st(dir);
+    upload(m->embed, st.bf16("model.embed_tokens.weight", V * H), V * H * 2);
+    m->layers.resize(c.num_layers);
+    const size_t nq = nh * hd, nk = nkv * hd, nqkv = nq + 2 * nk;
+    DeviceBuffer gate_tmp, up_tmp;
+    gate_tmp.alloc(I * H * 2);
+    up_tmp.alloc(I * H * 2);
+    for (int l = 0; l < c.num_layers; ++l) {
+        LayerWeights& ly = m->layers[l];
+        const std::string p = "model.layers." + std::to_string(l) + ".";
+        ly.wqkv.alloc(nqkv * H * 2);
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.weight", nq * H), nq * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + nq * H, st.bf16(p + "self_attn.k_proj.weight", nk * H), nk * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + (nq + nk) * H, st.bf16(p + "self_attn.v_proj.weight", nk * H), nk * H * 2, cudaMemcpyHostToDevice));
+        if (st.has(p + "self_attn.q_proj.bias")) {  // same test as inference/src/model/qwen.cu:99
+            ly.has_bias = true;
+            ly.bqkv.alloc(nqkv * 2);
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.bias", nq), nq * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq, st.bf16(p + "self_attn.k_proj.bias", nk), nk * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq + nk, st.bf16(p + "self_attn.v_proj.bias", nk), nk * 2, cudaMemcpyHostToDevice));
+        }
+        upload(ly.wo, st.bf16(p + "self_attn.o_proj.weight", H * nq), H * nq * 2);
+        upload(ly.attn_norm, st.bf16(p + "input_layernorm.weight", H), H * 2);
+        upload(ly.ffn_norm, st.bf16(p + "post_attention_layernorm.weight", H), H * 2);
+        TFFN_CUDA(cudaMemcpy(gate_tmp.p, st.bf16(p + "mlp.gate_proj.weight", I * H), I * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(up_tmp.p, st.bf16(p + "mlp.up_proj.weight", I * H), I * H * 2, cudaMemcpyHostToDevice));
+        upload(ly.ffn.down, st.bf16(p + "mlp.down_proj.weight", H * I), H * I * 2);
+        ly.ffn.packed.alloc(I * 3 * H * 2);
+        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), ly.ffn.down.as<bf16>(), ly.ffn.packed.as<bf16>(), (int)I, (int)H, 0);
+        TFFN_CUDA(cudaGetLastError());
+        TFFN_CUDA(cudaDeviceSynchronize());
+    }
+    upload(m->final_norm, st.bf16("model.norm.weight", H), H * 2);
+    if (c.tie_embeddings) {
+        m->lm_head = m->embed.as<bf16>();
+    } else {
+        upload(m->lm_head_own, st.bf16("lm_head.weight", V * H), V * H * 2);
+        m->lm_head = m->lm_head_own.as<bf16>();
+    }
+    m->bs1_ok = bs1_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
+    const uint64_t per_layer = (nqkv * H + H * nq + 3 * I * H) * 2 + 2 * H * 2 + (uint64_t)(m->layers[0].has_bias ? nqkv * 2 : 0);
+    m->weight_bytes_base = per_layer * c.num_layers + V * H * 2 + H * 2;
+    return m.release();
+}
+
+// ------------------------------------------------------------------------------------------ Expert
+Expert* Expert::load(const Model* m, const std::string& path, float scale) {
+    if (!m) throw Error(kErrInvalid, "model is NULL");
+    TFFN_CUDA(cudaSetDevice(m->device));
+    ExpertFile ef(path);
+    const Config& c = m->cfg;
+    if ((int)ef.hdr.num_layers != c.num_layers || (int)ef.hdr.hidden != c.hidden_size ||
+        (int)ef.hdr.intermediate != c.intermediate_size) {
+        char buf[256];
+        snprintf(buf, sizeof buf, "Expert shape mismatch: checkpoint=%u×%u×%u, model=%d×%d×%d", ef.hdr.num_layers,
+                 ef.hdr.hidden, ef.hdr.intermediate, c.num_layers, c.hidden_size, c.intermediate_size);
+        throw Error(kErrShape, buf);
+    }
+    std::unique_ptr<Expert> e(new Expert());
+    e->model = m;
+    e->scale = scale;
+    const size_t H = c.hidden_size, I = c.intermediate_size, n = H * I;
+    e->layers.resize(c.num_layers);
+    DeviceBuffer stage, gate_tmp, up_tmp;
+    stage.alloc(n * 4);
+    gate_tmp.alloc(n * 2);
+    up_tmp.alloc(n * 2);
+    for (int l = 0; l < c.num_layers; ++l) {
+        FfnWeights& f = e->layers[l];
+        f.down.alloc(n * 2);
+        f.packed.alloc(n * 3 * 2);
+        bf16* dst[3] = {gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>()};
+        for (int k = 0; k < 3; ++k) {
+            TFFN_CUDA(cudaMemcpy(stage.p, ef.matrix(l, k), n * 4, cudaMemcpyHostToDevice));
+            launch_cast_f32_bf16(stage.as<float>(), dst[k], n, 0);
+            TFFN_CUDA(cudaGetLastError());
+            TFFN_CUDA(cudaDeviceSynchronize());
+        }
+        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>(), f.packed.as<bf16>(), (int)I, (int)H, 0);
+        TFFN_CUDA(cudaGetLastError());
+        TFFN_CUDA(cudaDeviceSynchronize());
+    }
+    e->weight_bytes = (uint64_t)c.num_layers * 3 * n * 2;
+    return e.release();
+}
+
+// ------------------------------------------------------------------------------------------ Session
+Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream)
+    : m_(m), e_(e), max_batch_(max_batch), max_seq_(max_seq), stream_(stream) {
+    if (!m) throw Error(kErrInvalid, "model is NULL");
+    if (e && e->model != m) throw Error(kErrInvalid, "expert was loaded for a different model");
+    if (max_batch < 1 || max_batch > 4096) throw Error(kErrInvalid, "max_batch must be in [1, 4096]");
+    if (max_seq < 2) throw Error(kErrInvalid, "max_seq must be at least 2");
+    TFFN_CUDA(cudaSetDevice(m->device));
+    if (!stream_) {
+        TFFN_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+        own_stream_ = true;
+    }
+    const Config& c = m->cfg;
+    const size_t H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
+    const size_t nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim, L = c.num_layers;
+    const size_t nqkv = (nh + 2 * nkv) * hd;
+    max_pages_per_seq_ = (max_seq + kPageTokens - 1) / kPageTokens;
+    num_pages_ = max_batch * max_pages_per_seq_;
+    const size_t layer_stride = (size_t)num_pages_ * nkv * kPageTokens * hd;
+    k_pool_.alloc(L * layer_stride * 2);
+    v_pool_.alloc(L * layer_stride * 2);
+    h_block_table_.assign((size_t)max_batch * max_pages_per_seq_, -1);
+    block_table_.alloc(h_block_table_.size() * 4);
+    TFFN_CUDA(cudaMemcpy(block_table_.p, h_block_table_.data(), h_block_table_.size() * 4, cudaMemcpyHostToDevice));
+    h_seq_len_.assign(max_batch, 0);
+    h_pages_used_.assign(max_batch, 0);
+    seq_len_dev_.alloc((size_t)max_batch * 4);
+    free_pages_.resize(num_pages_);
+    for (int i = 0; i < num_pages_; ++i) free_pages_[i] = num_pages_ - 1 - i;  // pop_back hands out 0,1,2,...
+    kv_.k_pool = k_pool_.as<bf16>();
+    kv_.v_pool = v_pool_.as<bf16>();
+    kv_.block_table = block_table_.as<int>();
+    kv_.max_pages_per_seq = max_pages_per_seq_;
+    kv_.num_pages = num_pages_;
+    kv_.layer_stride = layer_stride;
+    kv_.nkv = (int)nkv;
+    kv_.hd = (int)hd;
+
+    // RoPE tables in float, as the reference builds them on the host (inference/src/model/qwen.cu:120-132)
+    {
+        const int half = (int)hd / 2;
+        std::vector<float> cs((size_t)max_seq * half), sn((size_t)max_seq * half);
+        for (int pos = 0; pos < max_seq; ++pos)
+            for (int i = 0; i < half; ++i) {
+                float freq = 1.f / powf(c.rope_theta, (float)(2 * i) / (float)hd);
+                cs[(size_t)pos * half + i] = cosf(pos * freq);
+                sn[(size_t)pos * half + i] = sinf(pos * freq);
+            }
+        upload(rope_cos_, cs.data(), cs.size() * 4);
+        upload(rope_sin_, sn.data(), sn.size() * 4);
+    }
+
+    cap_tokens_ = H <= 2048 ? 4096 : 2048;
+    if (cap_tokens_ < ((max_batch + 255) / 256) * 256) cap_tokens_ = ((max_batch + 255) / 256) * 256;
+    const size_t T = cap_tokens_;
+    tokens_.alloc(T * 4);
+    tok_seq_.alloc(T * 4);
+    tok_pos_.alloc(T * 4);
+    row_idx_.alloc(T * 4);
+    picks_.alloc(T * 4);
+    dec_tokens_.alloc((size_t)max_batch * 4);
+    {
+        std::vector<int> id(T);
+        for (size_t i = 0; i < T; ++i) id[i] = (int)i;
+        upload(identity_, id.data(), T * 4);
+    }
+    h_.alloc(T * H * 2);
+    xn_.alloc(T * H * 2);
+    qkv_.alloc(T * nqkv * 4);
+    q_.alloc(T * nh * hd * 4);
+    ctx_.alloc(T * nh * hd * 2);
+    act_b_.alloc(T * I * 2);
+    if (e_) act_e_.alloc(T * I * 2);
+    xn_last_.alloc(T * H * 2);
+    ensure_logits(std::max<size_t>(256, max_batch));
+    gemm_partials_.alloc((size_t)64 << 20);
+    gemm_counters_.alloc(8192 * 4);
+    attn_partials_.alloc((size_t)32 << 20);
+    attn_counters_.alloc(16384 * 4);
+    status_.alloc(4);
+    step_counter_.alloc(4);
+    TFFN_CUDA(cudaMallocHost(&h_status_, 4));
+    *h_status_ = 0;
+
+    bs1_h_.alloc(H * 2);
+    bs1_q_.alloc(nh * hd * 4);
+    bs1_ctx_.alloc(nh * hd * 2);
+    bs1_part_.alloc(bs1_ffn_part_floats((int)H, m->num_sms) * 4);
+    bs1_tickets_.alloc(256 * 4);
+    bs1_lm_val_.alloc((size_t)m->num_sms * 2 * 4);
+    bs1_lm_idx_.alloc((size_t)m->num_sms * 2 * 4);
+    (void)V;
+}
+
+Session::~Session() {
+    cudaSetDevice(m_->device);
+    cudaStreamSynchronize(stream_);
+    if (bs1_graph_) cudaGraphExecDestroy(bs1_graph_);
+    if (h_status_) cudaFreeHost(h_status_);
+    if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
+    if (own_stream_) cudaStreamDestroy(stream_);
+}
+
+int32_t* Session::pinned_i32(size_t n) {
+    if (n > h_pinned_cap_) {
+        if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
+        h_pinned_i32_ = nullptr;
+        size_t cap = std::max<size_t>(n, 4096);
+        TFFN_CUDA(cudaMallocHost(&h_pinned_i32_, cap * 4));
+        h_pinned_cap_ = cap;
+    }
+    return h_pinned_i32_;
+}
+
+GemmWorkspace Session::gemm_ws() const {
+    GemmWorkspace w;
+    w.partials = gemm_partials_.as<float>();
+    w.partial_floats = gemm_partials_.bytes / 4;
+    w.counters = gemm_counters_.as<int>();
+    w.num_counters = (int)(gemm_counters_.bytes / 4);
+    w.status = status_.as<int>();
+    w.num_sms = m_->num_sms;
+    return w;
+}
+AttnWorkspace Session::attn_ws() const {
+    AttnWorkspace w;
+    w.partials = attn_partials_.as<float>();
+    w.partial_floats = attn_partials_.bytes / 4;
+    w.counters = attn_counters_.as<int>();
+    w.num_counters = (int)(attn_counters_.bytes / 4);
+    return w;
+}
+
+void Session::ensure_logits(size_t rows) {
+    if (rows <= logits_rows_) return;
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    logits_.alloc(rows * (size_t)m_->cfg.vocab_size * 4);
+    logits_rows_ = rows;
+    if (bs1_graph_) {  // the captured step holds the old pointer
+        cudaGraphExecDestroy(bs1_graph_);
+        bs1_graph_ = nullptr;
+    }
+}
+void Session::ensure_ring(int entries) {
+    if (entries <= out_ring_cap_) return;
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    out_ring_.alloc((size_t)entries * 4);
+    out_ring_cap_ = entries;
+    if (bs1_graph_) {
+        cudaGraphExecDestroy(bs1_graph_);
+        bs1_graph_ = nullptr;
+    }
+}
+
+void Session::reset(int slot) {
+    if (slot < -1 || slot >= max_batch_) throw Error(kErrInvalid, "slot out of range");
+    TFFN_CUDA(cudaSetDevice(m_->device));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    const int s0 = slot < 0 ? 0 : slot, s1 = slot < 0 ? max_batch_ : slot + 1;
+    for (int s = s0; s < s1; ++s) {
+        for (int p = h_pages_used_[s] - 1; p >= 0; --p) {
+            int& e = h_block_table_[(size_t)s * max_pages_per_seq_ + p];
+            if (e >= 0) free_pages_.push_back(e);
+            e = -1;
+        }
+        h_pages_used_[s] = 0;
+        h_seq_len_[s] = 0;
+    }
+    table_dirty_ = true;
+    flush_tables();
+    TFFN_CUDA(cudaMemcpyAsync(seq_len_dev_.p, h_seq_len_.data(), (size_t)max_batch_ * 4, cudaMemcpyHostToDevice, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Session::ensure_pages(int slot, int new_len) {
+    if (new_len > max_seq_) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "KV cache overflow: slot %d would hold %d tokens, capacity %d — increase --max-seq", slot,
+                 new_len, max_seq_);
+        throw Error(kErrCapacity, buf);
+    }
+    const int need = (new_len + kPageTokens - 1) / kPageTokens;
+    while (h_pages_used_[slot] < need) {
+        if (free_pages_.empty()) throw Error(kErrCapacity, "KV page pool exhausted");
+        const int pg = free_pages_.back();
+        free_pages_.pop_back();
+        h_block_table_[(size_t)slot * max_pages_per_seq_ + h_pages_used_[slot]] = pg;
+        h_pages_used_[slot]++;
+        table_dirty_ = true;
+    }
+}
+void Session::flush_tables() {
+    if (!table_dirty_) return;
+    // the host vector may change again before the copy runs, so stage it in pinned memory
+    int32_t* pin = pinned_i32(h_block_table_.size());
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    memcpy(pin, h_block_table_.data(), h_block_table_.size() * 4);
+    TFFN_CUDA(cudaMemcpyAsync(block_table_.p, pin, h_block_table_.size() * 4, cudaMemcpyHostToDevice, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    table_dirty_ = false;
+}
+
+void Session::set_launch_mode(int mode) {
+    if (mode < 0 || mode > 2) throw Error(kErrInvalid, "launch mode must be 0, 1 or 2");
+    launch_mode_ = mode;
+}
+
+void Session::capture_hidden(int max_rows) {
+    if (max_rows < 0) throw Error(kErrInvalid, "max_rows must be >= 0");
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    hidden_rows_cap_ = max_rows;
+    hidden_rows_ = 0;
+    if (max_rows > 0) hidden_.alloc((size_t)m_->cfg.num_layers * max_rows * m_->cfg.hidden_size * 2);
+    else hidden_.release();
+}
+int Session::get_hidden(int layer, uint16_t* dst, int max_rows) {
+    if (layer < 0 || layer >= m_->cfg.num_layers || !dst) throw Error(kErrInvalid, "bad layer or destination");
+    const int rows = std::min(hidden_rows_, max_rows);
+    if (rows <= 0) return 0;
+    const size_t H = m_->cfg.hidden_size;
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    TFFN_CUDA(cudaMemcpy(dst, hidden_.as<bf16>() + (size_t)layer * hidden_rows_cap_ * H, (size_t)rows * H * 2, cudaMemcpyDeviceToHost));
+    return rows;
+}
+
+int Session::status() {
+    TFFN_CUDA(cudaMemcpyAsync(h_status_, status_.p, 4, cudaMemcpyDeviceToHost, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    return *h_status_;
+}
+void Session::check_status() {
+    const int st = status();
+    if (st != 0) {
+        TFFN_CUDA(cudaMemsetAsync(status_.p, 0, 4, stream_));
+        char buf[128];
+        snprintf(buf, sizeof buf, "a kernel reported device status %d (1-3: a bounded wait ran out, 4: index out of range)", st);
+        throw Error(kErrDevice, buf);
+    }
+}
+
+// ---------------------------------------------------------------- batched path (tensor-core GEMMs)
+void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx) {
+    const Config& c = m_->cfg;
+    const int H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
+    const int nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    const int nqkv = (nh + 2 * nkv) * hd;
+    const int* tokens = decode ? dec_tokens_.as<int>() : tokens_.as<int>();
+    const int* tok_seq = decode ? identity_.as<int>() : tok_seq_.as<int>();
+    const int* tok_pos = decode ? seq_len_dev_.as<int>() : tok_pos_.as<int>();
+    int* status = status_.as<int>();
+    const GemmWorkspace gws = gemm_ws();
+    auto gemm = [&](const GemmCall& call) {
+        int rc = launch_gemm(call, gws, stream_);
+        if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");
+        if (rc != 0) cuda_check((cudaError_t)rc, "tensor-core GEMM launch", __FILE__, __LINE__);
+        launches_++;
+    };
+    launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_);
+    launches_++;
+    for (int l = 0; l < c.num_layers; ++l) {
+        const LayerWeights& ly = m_->layers[l];
+        launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        GemmCall g;
+        memset(&g, 0, sizeof g);
+        g.x_rows_alloc = cap_tokens_;
+        g.T = T;
+        g.alpha = 1.f;
+        // q|k|v rows in one GEMM, fp32 out
+        g.op[0] = {ly.wqkv.as<bf16>(), H, xn_.as<bf16>(), H, H};
+        g.op[1] = {nullptr, 0, nullptr, 0, 0};
+        g.N = nqkv;
+        g.mode = GEMM_STORE_F32;
+        g.out = qkv_.p;
+        g.ldo = nqkv;
+        gemm(g);
+        const bf16* b = ly.has_bias ? ly.bqkv.as<bf16>() : nullptr;
+        launch_qkv_post(qkv_.as<float>(), b, b ? b + nh * hd : nullptr, b ? b + (nh + nkv) * hd : nullptr, rope_cos_.as<float>(),
+                        rope_sin_.as<float>(), tok_seq, tok_pos, q_.as<float>(), kv_, l, T, nh, max_seq_, status, stream_);
+        launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
+                         status, stream_);
+        // o_proj + residual
+        g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
+        g.N = H;
+        g.mode = GEMM_RESIDUAL;
+        g.out = h_.p;
+        g.ldo = H;
+        gemm(g);
+        launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        launches_ += 4;
+        // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records
+        auto swiglu = [&](const FfnWeights& f, bf16* act) {
+            const bf16* rec = f.packed.as<bf16>();
+            g.op[0] = {rec, (int64_t)3 * H, xn_.as<bf16>(), H, H};
+            g.op[1] = {rec + H, (int64_t)3 * H, xn_.as<bf16>(), H, H};
+            g.N = I;
+            g.mode = GEMM_SWIGLU;
+            g.out = act;
+            g.ldo = I;
+            gemm(g);
+        };
+        swiglu(ly.ffn, act_b_.as<bf16>());
+        if (e_) swiglu(e_->layers[l], act_e_.as<bf16>());
+        // down projections of base and expert into two accumulators, summed in fp32, + residual
+        g.op[0] = {ly.ffn.down.as<bf16>(), I, act_b_.as<bf16>(), I, I};
+        if (e_) {
+            g.op[1] = {e_->layers[l].down.as<bf16>(), I, act_e_.as<bf16>(), I, I};
+            g.alpha = e_->scale;
+        } else {
+            g.op[1] = {nullptr, 0, nullptr, 0, 0};
+        }
+        g.N = H;
+        g.mode = GEMM_RESIDUAL;
+        g.out = h_.p;
+        g.ldo = H;
+        gemm(g);
+        g.alpha = 1.f;
+        if (hidden_rows_cap_ > 0) {
+            const int rows = std::min(T, hidden_rows_cap_);
+            const size_t n16 = (size_t)rows * H / 8;
+            k_copy_rows_bf16<<<(unsigned)((n16 + 255) / 256), 256, 0, stream_>>>(
+                h_.as<bf16>(), hidden_.as<bf16>() + (size_t)l * hidden_rows_cap_ * H, n16);
+            hidden_rows_ = rows;
+            launches_++;
+        }
+    }
+    if (n_logit_rows > 0) {
+        const int* rows = logit_rows_are_all ? nullptr : row_idx_.as<int>();
+        launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_);
+        GemmCall g;
+        memset(&g, 0, sizeof g);
+        g.x_rows_alloc = cap_tokens_;
+        g.T = n_logit_rows;
+        g.alpha = 1.f;
+        g.op[0] = {m_->lm_head, H, xn_last_.as<bf16>(), H, H};
+        g.N = V;
+        g.mode = GEMM_STORE_F32;
+        g.out = logits_.p;
+        g.ldo = V;
+        gemm(g);
+        launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_);
+        launches_ += 2;
+    }
+    TFFN_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------- batch-1 path
+Bs1Ctx Session::bs1_ctx(bool want_logits) const {
+    const Config& c = m_->cfg;
+    Bs1Ctx x;
+    memset(&x, 0, sizeof x);
+    x.H = c.hidden_size; x.I = c.intermediate_size; x.nh = c.num_heads; x.nkv = c.num_kv_heads; x.hd = c.head_dim;
+    x.V = c.vocab_size;
+    x.eps = c.rms_norm_eps;
+    x.expert_scale = e_ ? e_->scale : 0.f;
+    x.rope_cos = rope_cos_.as<float>();
+    x.rope_sin = rope_sin_.as<float>();
+    x.max_pos = max_seq_;
+    x.h = bs1_h_.as<bf16>();
+    x.q = bs1_q_.as<float>();
+    x.ctx = bs1_ctx_.as<bf16>();
+    x.token = dec_tokens_.as<int>();
+    x.seq_len = seq_len_dev_.as<int>();
+    x.slot = 0;
+    x.ffn_part = bs1_part_.as<float>();
+    x.tickets = bs1_tickets_.as<int>();
+    x.lm_val = bs1_lm_val_.as<float>();
+    x.lm_idx = bs1_lm_idx_.as<int>();
+    x.logits = want_logits ? logits_.as<float>() : nullptr;
+    x.out_tokens = out_ring_.as<int>();
+    x.step_counter = step_counter_.as<int>();
+    x.status = status_.as<int>();
+    x.num_sms = m_->num_sms;
+    return x;
+}
+
+void Session::launch_bs1_step(bool want_logits, bool pdl) {
+    const Config& c = m_->cfg;
+    const Bs1Ctx x = bs1_ctx(want_logits);
+    for (int l = 0; l < c.num_layers; ++l) {
+        const LayerWeights& lw = m_->layers[l];
+        Bs1Layer ly;
+        ly.wqkv = lw.wqkv.as<bf16>();
+        ly.bqkv = lw.has_bias ? lw.bqkv.as<bf16>() : nullptr;
+        ly.wo = lw.wo.as<bf16>();
+        ly.attn_norm = lw.attn_norm.as<bf16>();
+        ly.ffn_norm = lw.ffn_norm.as<bf16>();
+        ly.ffn_base = lw.ffn.packed.as<bf16>();
+        ly.ffn_expert = e_ ? e_->layers[l].packed.as<bf16>() : nullptr;
+        launch_bs1_qkv(x, ly, m_->embed.as<bf16>(), kv_, l, l == 0, stream_, pdl);
+        launch_attention(x.q, kv_, l, identity_.as<int>(), seq_len_dev_.as<int>(), x.ctx, 1, c.num_heads, max_seq_, attn_ws(),
+                         m_->num_sms, status_.as<int>(), stream_);
+        launch_bs1_oproj(x, ly, stream_, pdl);
+        launch_bs1_ffn(x, ly, stream_, pdl);
+    }
+    launch_bs1_lmhead(x, m_->final_norm.as<bf16>(), m_->lm_head, stream_, pdl);
+    launches_ += (uint64_t)c.num_layers * 4 + 1;
+}
+
+void Session::run_bs1(bool want_logits) {
+    if (launch_mode_ == 2) {
+        if (!bs1_graph_ || bs1_graph_logits_ != want_logits) {
+            if (bs1_graph_) {
+                cudaGraphExecDestroy(bs1_graph_);
+                bs1_graph_ = nullptr;
+            }
+            cudaGraph_t graph = nullptr;
+            const uint64_t before = launches_;
+            TFFN_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+            launch_bs1_step(want_logits, true);
+            cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
+            launches_ = before;
+            TFFN_CUDA(ce);
+            TFFN_CUDA(cudaGraphInstantiate(&bs1_graph_, graph, 0));
+            cudaGraphDestroy(graph);
+            bs1_graph_logits_ = want_logits;
+        }
+        TFFN_CUDA(cudaGraphLaunch(bs1_graph_, stream_));
+        launches_ += (uint64_t)m_->cfg.num_layers * 4 + 1;
+    } else {
+        launch_bs1_step(want_logits, launch_mode_ >= 1);
+    }
+    TFFN_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------- public operations
+void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs, int32_t* next_tokens, float* logits_last) {
+    if (!tokens || !seq_lens || n_seqs < 1 || n_seqs > max_batch_) throw Error(kErrInvalid, "bad prefill arguments");
+    TFFN_CUDA(cudaSetDevice(m_->device));
+    const int V = m_->cfg.vocab_size;
+    size_t total = 0;
+    for (int s = 0; s < n_seqs; ++s) {
+        if (seq_lens[s] < 1) throw Error(kErrInvalid, "every prompt needs at least one token");
+        total += seq_lens[s];
+    }
+    for (size_t i = 0; i < total; ++i)
+        if (tokens[i] < 0 || tokens[i] >= V) throw Error(kErrInvalid, "token id out of range");
+    for (int s = 0; s < n_seqs; ++s) ensure_pages(s, h_seq_len_[s] + seq_lens[s]);
+    flush_tables();
+    ensure_logits(std::max<size_t>(256, n_seqs));
+    // flatten (slot, position) in slot order and cut into chunks of at most cap_tokens_ rows
+    std::vector<int> f_tok(total), f_seq(total), f_pos(total), f_last(total, -1);
+    {
+        size_t o = 0;
+        for (int s = 0; s < n_seqs; ++s)
+            for (int i = 0; i < seq_lens[s]; ++i, ++o) {
+                f_tok[o] = tokens[o];
+                f_seq[o] = s;
+                f_pos[o] = h_seq_len_[s] + i;
+                if (i == seq_lens[s] - 1) f_last[o] = s;
+            }
+    }
+    for (size_t c0 = 0; c0 < total; c0 += cap_tokens_) {
+        const int T = (int)std::min<size_t>(cap_tokens_, total - c0);
+        int32_t* pin = pinned_i32((size_t)T * 4);
+        std::vector<int> last_rows, last_slots;
+        int max_ctx = 1;
+        for (int i = 0; i < T; ++i) {
+            pin[i] = f_tok[c0 + i];
+            pin[T + i] = f_seq[c0 + i];
+            pin[2 * T + i] = f_pos[c0 + i];
+            max_ctx = std::max(max_ctx, f_pos[c0 + i] + 1);
+            if (f_last[c0 + i] >= 0) {
+                last_rows.push_back(i);
+                last_slots.push_back(f_last[c0 + i]);
+            }
+        }
+        for (size_t i = 0; i < last_rows.size(); ++i) pin[3 * T + i] = last_rows[i];
+        TFFN_CUDA(cudaMemcpyAsync(tokens_.p, pin, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(tok_seq_.p, pin + T, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * T, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
+        if (!last_rows.empty())
+            TFFN_CUDA(cudaMemcpyAsync(row_idx_.p, pin + 3 * T, last_rows.size() * 4, cudaMemcpyHostToDevice, stream_));
+        run_batched(T, (int)last_rows.size(), false, false, max_ctx);
+        if (!last_rows.empty()) {
+            std::vector<int> picks(last_rows.size());
+            TFFN_CUDA(cudaMemcpyAsync(picks.data(), picks_.p, picks.size() * 4, cudaMemcpyDeviceToHost, stream_));
+            TFFN_CUDA(cudaStreamSynchronize(stream_));
+            for (size_t i = 0; i < last_rows.size(); ++i) {
+                if (next_tokens) next_tokens[last_slots[i]] = picks[i];
+                int32_t* one = pinned_i32(4);
+                one[0] = picks[i];
+                TFFN_CUDA(cudaMemcpyAsync(dec_tokens_.as<int>() + last_slots[i], one, 4, cudaMemcpyHostToDevice, stream_));
+                if (logits_last)
+                    TFFN_CUDA(cudaMemcpyAsync(logits_last + (size_t)last_slots[i] * V, logits_.as<float>() + i * (size_t)V,
+                                              (size_t)V * 4, cudaMemcpyDeviceToHost, stream_));
+                TFFN_CUDA(cudaStreamSynchronize(stream_));
+            }
+        } else {
+            TFFN_CUDA(cudaStreamSynchronize(stream_));
+        }
+    }
+    for (int s = 0; s < n_seqs; ++s) h_seq_len_[s] += seq_lens[s];
+    TFFN_CUDA(cudaMemcpyAsync(seq_len_dev_.p, h_seq_len_.data(), (size_t)max_batch_ * 4, cudaMemcpyHostToDevice, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    check_status();
+}
+
+void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
+    if (!tokens || T < 1 || slot < 0 || slot >= max_batch_) throw Error(kErrInvalid, "bad forward arguments");
+    TFFN_CUDA(cudaSetDevice(m_->device));
+    const int V = m_->cfg.vocab_size;
+    for (int i = 0; i < T; ++i)
+        if (tokens[i] < 0 || tokens[i] >= V) throw Error(kErrInvalid, "token id out of range");
+    ensure_pages(slot, h_seq_len_[slot] + T);
+    flush_tables();
+    const int chunk_cap = std::min(cap_tokens_, 512);  // bounds the all-row logits buffer
+    if (logits) ensure_logits(std::min(T, chunk_cap));
+    int last_pick = 0;
+    for (int c0 = 0; c0 < T; c0 += chunk_cap) {
+        const int n = std::min(chunk_cap, T - c0);
+        int32_t* pin = pinned_i32((size_t)n * 3);
+        for (int i = 0; i < n; ++i) {
+            pin[i] = tokens[c0 + i];
+            pin[n + i] = slot;
+            pin[2 * n + i] = h_seq_len_[slot] + c0 + i;
+        }
+        TFFN_CUDA(cudaMemcpyAsync(tokens_.p, pin, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(tok_seq_.p, pin + n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+        if (logits) {
+            run_batched(n, n, true, false, h_seq_len_[slot] + c0 + n);
+            TFFN_CUDA(cudaMemcpyAsync(logits + (size_t)c0 * V, logits_.p, (size_t)n * V * 4, cudaMemcpyDeviceToHost, stream_));
+            TFFN_CUDA(cudaMemcpyAsync(pin, picks_.as<int>() + (n - 1), 4, cudaMemcpyDeviceToHost, stream_));
+            TFFN_CUDA(cudaStreamSynchronize(stream_));
+            last_pick = pin[0];
+        } else {
+            run_batched(n, 0, true, false, h_seq_len_[slot] + c0 + n);
+            TFFN_CUDA(cudaStreamSynchronize(stream_));
+        }
+    }
+    h_seq_len_[slot] += T;
+    int32_t* pin = pinned_i32(4);
+    pin[0] = last_pick;
+    TFFN_CUDA(cudaMemcpyAsync(dec_tokens_.as<int>() + slot, pin, 4, cudaMemcpyHostToDevice, stream_));
+    TFFN_CUDA(cudaMemcpyAsync(seq_len_dev_.p, h_seq_len_.data(), (size_t)max_batch_ * 4, cudaMemcpyHostToDevice, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    check_status();
+}
+
+void Session::decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_tokens, float* logits) {
+    if (n_seqs < 1 || n_seqs > max_batch_) throw Error(kErrInvalid, "n_seqs out of range");
+    TFFN_CUDA(cudaSetDevice(m_->device));
+    const int V = m_->cfg.vocab_size;
+    for (int s = 0; s < n_seqs; ++s) ensure_pages(s, h_seq_len_[s] + 1);
+    flush_tables();
+    int32_t* pin = pinned_i32((size_t)std::max(n_seqs, 4));
+    if (tokens_in) {
+        for (int s = 0; s < n_seqs; ++s) {
+            if (tokens_in[s] < 0 || tokens_in[s] >= V) throw Error(kErrInvalid, "token id out of range");
+            pin[s] = tokens_in[s];
+        }
+        TFFN_CUDA(cudaMemcpyAsync(dec_tokens_.p, pin, (size_t)n_seqs * 4, cudaMemcpyHostToDevice, stream_));
+    }
+    TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
+    ensure_ring(n_seqs);
+    if (logits) ensure_logits(std::max<size_t>(256, n_seqs));
+    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok;
+    if (bs1) {
+        run_bs1(logits != nullptr);
+    } else {
+        int max_ctx = 1;
+        for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + 1);
+        run_batched(n_seqs, n_seqs, true, true, max_ctx);
+        k_decode_advance<<<1, 256, 0, stream_>>>(picks_.as<int>(), n_seqs, dec_tokens_.as<int>(),
+                                                                 seq_len_dev_.as<int>(), out_ring_.as<int>(), step_counter_.as<int>());
+        launches_++;
+    }
+    TFFN_CUDA(cudaMemcpyAsync(pin, dec_tokens_.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, stream_));
+    if (logits) TFFN_CUDA(cudaMemcpyAsync(logits, logits_.p, (size_t)n_seqs * V * 4, cudaMemcpyDeviceToHost, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    if (next_tokens)
+        for (int s = 0; s < n_seqs; ++s) next_tokens[s] = pin[s];
+    for (int s = 0; s < n_seqs; ++s) h_seq_len_[s] += 1;
+    check_status();
+}
+
+void Session::decode_run(int n_seqs, int steps, int32_t* tokens_out) {
+    if (n_seqs < 1 || n_seqs > max_batch_ || steps < 1) throw Error(kErrInvalid, "bad decode_run arguments");
+    TFFN_CUDA(cudaSetDevice(m_->device));
+    for (int s = 0; s < n_seqs; ++s) ensure_pages(s, h_seq_len_[s] + steps);
+    flush_tables();
+    ensure_ring(n_seqs * steps);
+    TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
+    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok;
+    int max_ctx = 1;
+    for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + steps);
+    for (int it = 0; it < steps; ++it) {
+        if (bs1) {
+            run_bs1(false);
+        } else {
+            run_batched(n_seqs, n_seqs, true, true, max_ctx);
+            k_decode_advance<<<1, 256, 0, stream_>>>(picks_.as<int>(), n_seqs, dec_tokens_.as<int>(),
+                                                                     seq_len_dev_.as<int>(), out_ring_.as<int>(),
+                                                                     step_counter_.as<int>());
+            launches_++;
+        }
+    }
+    if (tokens_out)
+        TFFN_CUDA(cudaMemcpyAsync(tokens_out, out_ring_.p, (size_t)n_seqs * steps * 4, cudaMemcpyDeviceToHost, stream_));
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    for (int s = 0; s < n_seqs; ++s) h_seq_len_[s] += steps;
+    check_status();
+}
+
+}  // namespace tffn

@@ -1,0 +1,138 @@
+// Host-side engine: weights on the device (Model, Expert) and the per-session state
+// (paged KV cache, block tables, scratch, decode loop). C++ mirror of the reference's
+// model:: namespace (inference/include/model/qwen.h, expert.h), behind the C ABI in c_api.cpp.
+#pragma once
+#include "host_io.h"
+#include "kernels.h"
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace tffn {
+
+void cuda_check(cudaError_t e, const char* what, const char* file, int line);
+#define TFFN_CUDA(x) ::tffn::cuda_check((x), #x, __FILE__, __LINE__)
+
+struct DeviceBuffer {
+    void* p = nullptr;
+    size_t bytes = 0;
+    DeviceBuffer() = default;
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    DeviceBuffer(DeviceBuffer&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+    ~DeviceBuffer() { release(); }
+    void alloc(size_t n);  // zero-filled
+    void release();
+    template <typename T>
+    T* as() const { return (T*)p; }
+};
+
+// One FFN (base or expert) of one layer: records [I][3][H] (gate row, up row, down column) for
+// the batch-1 kernel and, as strided views of the same records, for the tensor-core GEMM;
+// plus down as [H, I] for the GEMM's K-major operand.
+struct FfnWeights {
+    DeviceBuffer packed;  // bf16 [I][3][H]
+    DeviceBuffer down;    // bf16 [H][I]
+};
+
+struct LayerWeights {
+    DeviceBuffer wqkv, bqkv, wo, attn_norm, ffn_norm;
+    bool has_bias = false;
+    FfnWeights ffn;
+};
+
+struct Model {
+    Config cfg;
+    int device = 0, num_sms = 0;
+    DeviceBuffer embed, final_norm, lm_head_own;
+    const bf16* lm_head = nullptr;
+    std::vector<LayerWeights> layers;
+    bool bs1_ok = false;
+    uint64_t weight_bytes_base = 0;  // bytes one decode step streams (every matrix once, LM head included)
+    static Model* load(const std::string& dir, int device, int tp_rank, int tp_size);
+};
+
+struct Expert {
+    const Model* model = nullptr;
+    float scale = 0.1f;
+    std::vector<FfnWeights> layers;
+    uint64_t weight_bytes = 0;
+    static Expert* load(const Model* m, const std::string& path, float scale);
+};
+
+class Session {
+public:
+    Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream);
+    ~Session();
+    void reset(int slot);
+    int seq_len(int slot) const { return h_seq_len_[slot]; }
+    void prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs, int32_t* next_tokens, float* logits_last);
+    void forward(int slot, const int32_t* tokens, int T, float* logits);
+    void decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_tokens, float* logits);
+    void decode_run(int n_seqs, int steps, int32_t* tokens_out);
+    void set_launch_mode(int mode);
+    void set_bs1_path(bool on) { use_bs1_ = on; }
+    void capture_hidden(int max_rows);
+    int get_hidden(int layer, uint16_t* dst, int max_rows);
+    int status();
+    uint64_t launch_count() const { return launches_; }
+    cudaStream_t stream() const { return stream_; }
+    const Model* model() const { return m_; }
+
+private:
+    const Model* m_;
+    const Expert* e_;
+    int max_batch_, max_seq_, max_pages_per_seq_, num_pages_;
+    int cap_tokens_;  // rows of the activation buffers
+    cudaStream_t stream_;
+    bool own_stream_ = false;
+    int launch_mode_ = 1;
+    bool use_bs1_ = true;
+    uint64_t launches_ = 0;
+
+    // paged KV cache
+    DeviceBuffer k_pool_, v_pool_, block_table_, seq_len_dev_;
+    std::vector<int> h_block_table_, h_seq_len_, free_pages_;
+    std::vector<int> h_pages_used_;  // pages mapped per slot
+    bool table_dirty_ = false;
+    KvView kv_;
+
+    // RoPE tables [max_seq, hd/2] (inference/src/model/qwen.cu:120-132)
+    DeviceBuffer rope_cos_, rope_sin_;
+
+    // token metadata and activations of the batched path
+    DeviceBuffer tokens_, tok_seq_, tok_pos_, row_idx_, picks_, identity_, dec_tokens_;
+    DeviceBuffer h_, xn_, qkv_, q_, ctx_, act_b_, act_e_, xn_last_, logits_;
+    size_t logits_rows_ = 0;
+    DeviceBuffer gemm_partials_, gemm_counters_, attn_partials_, attn_counters_;
+    DeviceBuffer status_, out_ring_, step_counter_;
+    int out_ring_cap_ = 0;
+    int* h_status_ = nullptr;  // pinned
+    int32_t* h_pinned_i32_ = nullptr;
+    size_t h_pinned_cap_ = 0;
+
+    // batch-1 path
+    DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
+    cudaGraphExec_t bs1_graph_ = nullptr;
+    bool bs1_graph_logits_ = false;
+
+    // hidden-state capture
+    DeviceBuffer hidden_;
+    int hidden_rows_cap_ = 0, hidden_rows_ = 0;
+
+    GemmWorkspace gemm_ws() const;
+    AttnWorkspace attn_ws() const;
+    void ensure_pages(int slot, int new_len);
+    void flush_tables();
+    void ensure_logits(size_t rows);
+    void ensure_ring(int entries);
+    // runs T tokens already staged in tokens_/tok_seq_/tok_pos_ (or decode state when decode=true)
+    void run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx);
+    void run_bs1(bool want_logits);
+    void launch_bs1_step(bool want_logits, bool pdl);
+    Bs1Ctx bs1_ctx(bool want_logits) const;
+    void check_status();
+    int32_t* pinned_i32(size_t n);
+};
+
+}  // namespace tffn

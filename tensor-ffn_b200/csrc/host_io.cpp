@@ -1,0 +1,373 @@
+#include "host_io.h"
+#include "json_lite.h"
+#include <algorithm>
+#include <cstring>
+#include <dirent.h>
+#include <fcntl.h>
+#include <fstream>
+#include <sstream>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+namespace tffn {
+
+std::string read_text_file(const std::string& path, bool* ok) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f) {
+        if (ok) *ok = false;
+        return std::string();
+    }
+    std::ostringstream ss;
+    ss << f.rdbuf();
+    if (ok) *ok = true;
+    return ss.str();
+}
+
+static int first_int(const JsonValue& j, const char* key, int def) {
+    const JsonValue* v = j.find(key);
+    if (!v) return def;
+    if (v->is_array() && !v->arr.empty() && v->arr[0].is_number()) return (int)v->arr[0].as_int();
+    if (v->is_number()) return (int)v->as_int();
+    return def;
+}
+
+Config read_config(const std::string& dir) {
+    bool ok;
+    std::string text = read_text_file(dir + "/config.json", &ok);
+    if (!ok) throw Error(kErrIO, "Cannot open " + dir + "/config.json");
+    JsonValue j;
+    try {
+        j = json_parse(text);
+    } catch (const std::exception& e) {
+        throw Error(kErrFormat, dir + "/config.json: " + e.what());
+    }
+    Config c;
+    c.hidden_size = (int)j.value_int("hidden_size", 896);
+    c.intermediate_size = (int)j.value_int("intermediate_size", 4864);
+    c.num_layers = (int)j.value_int("num_hidden_layers", 24);
+    c.num_heads = (int)j.value_int("num_attention_heads", 14);
+    c.num_kv_heads = (int)j.value_int("num_key_value_heads", 2);
+    c.vocab_size = (int)j.value_int("vocab_size", 151936);
+    c.max_seq_len = (int)j.value_int("max_position_embeddings", 131072);
+    c.rms_norm_eps = (float)j.value_double("rms_norm_eps", 1e-6);
+    c.rope_theta = (float)j.value_double("rope_theta", 1e6);
+    c.tie_embeddings = j.value_bool("tie_word_embeddings", true);
+    c.eos_token_id = first_int(j, "eos_token_id", 151645);
+    c.bos_token_id = first_int(j, "bos_token_id", 151643);
+    if (c.hidden_size <= 0 || c.num_heads <= 0 || c.num_kv_heads <= 0 || c.num_layers <= 0 ||
+        c.intermediate_size <= 0 || c.vocab_size <= 0)
+        throw Error(kErrFormat, "config.json: non-positive dimension");
+    if (c.hidden_size % c.num_heads != 0 || c.num_heads % c.num_kv_heads != 0)
+        throw Error(kErrFormat, "config.json: heads do not divide hidden size / kv heads do not divide heads");
+    c.head_dim = c.hidden_size / c.num_heads;
+    return c;
+}
+
+// ---------------------------------------------------------------- safetensors
+static void* map_file(const std::string& path, size_t* size, int* fd_out) {
+    int fd = ::open(path.c_str(), O_RDONLY);
+    if (fd < 0) throw Error(kErrIO, "Cannot open " + path);
+    struct stat st;
+    if (fstat(fd, &st) != 0) {
+        ::close(fd);
+        throw Error(kErrIO, "Cannot stat " + path);
+    }
+    *size = (size_t)st.st_size;
+    void* p = nullptr;
+    if (*size > 0) {
+        p = mmap(nullptr, *size, PROT_READ, MAP_PRIVATE, fd, 0);
+        if (p == MAP_FAILED) {
+            ::close(fd);
+            throw Error(kErrIO, "mmap failed for " + path);
+        }
+    }
+    *fd_out = fd;
+    return p;
+}
+
+static size_t dtype_size(const std::string& d) {
+    if (d == "BF16" || d == "F16" || d == "I16" || d == "U16") return 2;
+    if (d == "F32" || d == "I32" || d == "U32") return 4;
+    if (d == "F64" || d == "I64" || d == "U64") return 8;
+    if (d == "I8" || d == "U8" || d == "BOOL" || d == "F8_E4M3" || d == "F8_E5M2") return 1;
+    return 0;
+}
+
+SafeTensorsFile::SafeTensorsFile(const std::string& p) : path(p) {
+    map_ = map_file(p, &size_, &fd_);
+    auto bad = [&](const std::string& why) {
+        if (map_) munmap(map_, size_);
+        if (fd_ >= 0) ::close(fd_);
+        map_ = nullptr;
+        fd_ = -1;
+        throw Error(kErrFormat, p + ": " + why);
+    };
+    if (size_ < 8) bad("file shorter than the 8-byte header length");
+    const uint8_t* base = (const uint8_t*)map_;
+    uint64_t hl;
+    memcpy(&hl, base, 8);
+    if (hl > size_ - 8) bad("header length exceeds file size");
+    JsonValue header;
+    try {
+        header = json_parse((const char*)base + 8, (size_t)hl);
+    } catch (const std::exception& e) {
+        bad(std::string("header: ") + e.what());
+    }
+    if (!header.is_object()) bad("header is not an object");
+    const uint8_t* data = base + 8 + hl;
+    size_t data_size = size_ - 8 - (size_t)hl;
+    for (auto& kv : header.obj) {
+        if (kv.first == "__metadata__") continue;
+        const JsonValue& v = kv.second;
+        const JsonValue* dt = v.find("dtype");
+        const JsonValue* sh = v.find("shape");
+        const JsonValue* off = v.find("data_offsets");
+        if (!dt || !dt->is_string() || !sh || !sh->is_array() || !off || !off->is_array() || off->arr.size() != 2)
+            bad("malformed entry for " + kv.first);
+        TensorInfo ti;
+        ti.dtype = dt->str;
+        size_t elems = 1;
+        for (auto& d : sh->arr) {
+            ti.shape.push_back(d.as_int());
+            elems *= (size_t)d.as_int();
+        }
+        size_t s = (size_t)off->arr[0].as_int(), e = (size_t)off->arr[1].as_int();
+        if (e < s || e > data_size) bad("data_offsets out of range for " + kv.first);
+        size_t ds = dtype_size(ti.dtype);
+        if (ds == 0) bad("Unknown dtype: " + ti.dtype);
+        if (elems * ds != e - s) bad("shape and data_offsets disagree for " + kv.first);
+        ti.data = data + s;
+        ti.nbytes = e - s;
+        tensors.emplace(kv.first, std::move(ti));
+    }
+}
+
+SafeTensorsFile::~SafeTensorsFile() {
+    if (map_) munmap(map_, size_);
+    if (fd_ >= 0) ::close(fd_);
+}
+
+SafeTensorsDir::SafeTensorsDir(const std::string& dir) {
+    DIR* d = opendir(dir.c_str());
+    if (!d) throw Error(kErrIO, "Cannot open dir " + dir);
+    std::vector<std::string> files;
+    while (struct dirent* ent = readdir(d)) {
+        std::string name = ent->d_name;
+        const std::string suffix = ".safetensors";
+        if (name.size() > suffix.size() && name.compare(name.size() - suffix.size(), suffix.size(), suffix) == 0)
+            files.push_back(dir + "/" + name);
+    }
+    closedir(d);
+    std::sort(files.begin(), files.end());
+    if (files.empty()) throw Error(kErrIO, "No .safetensors file in " + dir);
+    try {
+        for (auto& f : files) shards_.push_back(new SafeTensorsFile(f));
+    } catch (...) {
+        for (auto* s : shards_) delete s;
+        shards_.clear();
+        throw;
+    }
+}
+SafeTensorsDir::~SafeTensorsDir() {
+    for (auto* s : shards_) delete s;
+}
+bool SafeTensorsDir::has(const std::string& name) const {
+    for (auto* s : shards_)
+        if (s->tensors.count(name)) return true;
+    return false;
+}
+const TensorInfo& SafeTensorsDir::get(const std::string& name) const {
+    for (auto* s : shards_) {
+        auto it = s->tensors.find(name);
+        if (it != s->tensors.end()) return it->second;
+    }
+    throw Error(kErrFormat, "Missing tensor: " + name);
+}
+const uint16_t* SafeTensorsDir::bf16(const std::string& name, size_t elems) const {
+    const TensorInfo& ti = get(name);
+    if (ti.dtype != "BF16") throw Error(kErrFormat, "Tensor " + name + " is " + ti.dtype + ", expected BF16");
+    if (ti.nbytes != elems * 2) throw Error(kErrShape, "Size mismatch for " + name);
+    return (const uint16_t*)ti.data;
+}
+size_t SafeTensorsDir::num_tensors() const {
+    size_t n = 0;
+    for (auto* s : shards_) n += s->tensors.size();
+    return n;
+}
+
+// ---------------------------------------------------------------- expert .bin
+ExpertFile::ExpertFile(const std::string& path) {
+    map_ = map_file(path, &size_, &fd_);
+    auto bad = [&](int code, const std::string& why) {
+        if (map_) munmap(map_, size_);
+        if (fd_ >= 0) ::close(fd_);
+        map_ = nullptr;
+        fd_ = -1;
+        throw Error(code, path + ": " + why);
+    };
+    if (size_ < 20) bad(kErrFormat, "file shorter than the 20-byte header");
+    memcpy(&hdr, map_, 20);
+    if (hdr.magic != kExpertMagic) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "Bad checkpoint magic: 0x%08x (expected 0x%08x)", hdr.magic, kExpertMagic);
+        bad(kErrFormat, buf);
+    }
+    // The version word is read but not checked by the reference (inference/src/io/checkpoint.cpp:17);
+    // the same holds here so that files from any trainer build load.
+    unsigned __int128 need = (unsigned __int128)hdr.num_layers * 3u * hdr.hidden * hdr.intermediate * 4u + 20u;
+    if (hdr.num_layers == 0 || hdr.hidden == 0 || hdr.intermediate == 0) bad(kErrFormat, "zero dimension in header");
+    if (need > (unsigned __int128)size_) bad(kErrFormat, "file is truncated (fewer bytes than the header's shape needs)");
+}
+ExpertFile::~ExpertFile() {
+    if (map_) munmap(map_, size_);
+    if (fd_ >= 0) ::close(fd_);
+}
+const float* ExpertFile::matrix(int layer, int m) const {
+    size_t per = matrix_elems();
+    return (const float*)((const uint8_t*)map_ + 20) + ((size_t)layer * 3 + m) * per;
+}
+
+void write_expert(const std::string& path, uint32_t layers, uint32_t hidden, uint32_t inter,
+                  const float* const* mats) {
+    FILE* f = fopen(path.c_str(), "wb");
+    if (!f) throw Error(kErrIO, "Cannot save checkpoint " + path);
+    uint32_t h[5] = {kExpertMagic, kExpertVersion, layers, hidden, inter};
+    bool ok = fwrite(h, 4, 5, f) == 5;
+    size_t n = (size_t)hidden * inter;
+    for (uint32_t l = 0; ok && l < layers; ++l)
+        for (int m = 0; ok && m < 3; ++m) ok = fwrite(mats[l * 3 + m], 4, n, f) == n;
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) throw Error(kErrIO, "Short write to " + path);
+}
+
+// ---------------------------------------------------------------- tokenizer
+void Tokenizer::load(const std::string& dir) {
+    bool ok;
+    std::string text = read_text_file(dir + "/tokenizer.json", &ok);
+    if (!ok) throw Error(kErrIO, "Cannot open tokenizer.json");
+    JsonValue j;
+    try {
+        j = json_parse(text);
+    } catch (const std::exception& e) {
+        throw Error(kErrFormat, std::string("tokenizer.json: ") + e.what());
+    }
+    const JsonValue* model = j.find("model");
+    const JsonValue* vocab = model ? model->find("vocab") : nullptr;
+    if (!vocab || !vocab->is_object()) throw Error(kErrFormat, "tokenizer.json: model.vocab missing");
+    token_to_id_.reserve(vocab->obj.size() * 2);
+    for (auto& kv : vocab->obj) {
+        uint32_t id = (uint32_t)kv.second.as_int();
+        token_to_id_[kv.first] = id;
+        id_to_token_[id] = kv.first;
+    }
+    if (const JsonValue* ml = model->find("merges")) {
+        for (auto& m : ml->arr) {
+            std::string a, b;
+            if (m.is_string()) {
+                size_t sp = m.str.find(' ');
+                if (sp == std::string::npos) continue;
+                a = m.str.substr(0, sp);
+                b = m.str.substr(sp + 1);
+            } else if (m.is_array() && m.arr.size() == 2) {
+                a = m.arr[0].str;
+                b = m.arr[1].str;
+            } else {
+                continue;
+            }
+            auto ia = token_to_id_.find(a), ib = token_to_id_.find(b);
+            if (ia == token_to_id_.end() || ib == token_to_id_.end()) continue;
+            uint64_t key = (uint64_t)ia->second << 32 | ib->second;
+            if (!merge_rank_.count(key)) merge_rank_[key] = (uint32_t)merges_.size();
+            merges_.push_back({ia->second, ib->second});
+        }
+    }
+    if (const JsonValue* at = j.find("added_tokens")) {
+        for (auto& t : at->arr) {
+            const JsonValue* c = t.find("content");
+            const JsonValue* id = t.find("id");
+            if (!c || !id) continue;
+            token_to_id_[c->str] = (uint32_t)id->as_int();
+            id_to_token_[(uint32_t)id->as_int()] = c->str;
+        }
+    }
+    std::string g = read_text_file(dir + "/generation_config.json", &ok);
+    if (ok) {
+        try {
+            JsonValue gj = json_parse(g);
+            eos_id = (uint32_t)first_int(gj, "eos_token_id", (int)eos_id);
+            bos_id = (uint32_t)first_int(gj, "bos_token_id", (int)bos_id);
+        } catch (const std::exception&) {
+        }
+    }
+    pad_id = bos_id;
+}
+
+std::vector<uint32_t> Tokenizer::encode(const std::string& text) const {
+    std::vector<uint32_t> ids;
+    if (text.empty()) return ids;
+    ids.reserve(text.size());
+    for (unsigned char c : text) {
+        auto it = token_to_id_.find(std::string(1, (char)c));
+        if (it != token_to_id_.end()) {
+            ids.push_back(it->second);
+        } else {
+            char hex[8];
+            snprintf(hex, sizeof hex, "<0x%02X>", c);
+            auto it2 = token_to_id_.find(hex);
+            if (it2 != token_to_id_.end()) ids.push_back(it2->second);
+        }
+    }
+    bool changed = true;
+    while (changed && ids.size() > 1) {
+        changed = false;
+        uint32_t best_rank = UINT32_MAX;
+        size_t best_pos = 0;
+        for (size_t i = 0; i + 1 < ids.size(); ++i) {
+            auto it = merge_rank_.find((uint64_t)ids[i] << 32 | ids[i + 1]);
+            if (it != merge_rank_.end() && it->second < best_rank) {
+                best_rank = it->second;
+                best_pos = i;
+            }
+        }
+        if (best_rank != UINT32_MAX) {
+            auto& pr = merges_[best_rank];
+            auto il = id_to_token_.find(pr.first), ir = id_to_token_.find(pr.second);
+            if (il == id_to_token_.end() || ir == id_to_token_.end()) break;
+            auto it = token_to_id_.find(il->second + ir->second);
+            if (it != token_to_id_.end()) {
+                ids[best_pos] = it->second;
+                ids.erase(ids.begin() + best_pos + 1);
+                changed = true;
+            }
+        }
+    }
+    return ids;
+}
+
+std::string Tokenizer::decode(const std::vector<uint32_t>& ids) const {
+    std::string joined;
+    for (uint32_t id : ids) {
+        auto it = id_to_token_.find(id);
+        if (it != id_to_token_.end()) joined += it->second;
+    }
+    std::string out;
+    for (size_t i = 0; i < joined.size();) {
+        if ((unsigned char)joined[i] == 0xC4 && i + 1 < joined.size() && (unsigned char)joined[i + 1] == 0xA0) {
+            out += ' ';
+            i += 2;
+        } else {
+            out += joined[i++];
+        }
+    }
+    return out;
+}
+
+uint32_t Tokenizer::get_id(const std::string& token) const {
+    auto it = token_to_id_.find(token);
+    if (it != token_to_id_.end()) return it->second;
+    fprintf(stderr, "Warning: special token '%s' not found in vocab.\n", token.c_str());
+    return 0;
+}
+
+}  // namespace tffn

@@ -1,0 +1,126 @@
+// Launchers of the device kernels. Host code (model.cu / session.cu) calls only these.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace tffn {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kPageTokens = 32;  // tokens per KV page
+
+// ------------------------------------------------------------------ tensor-core GEMM (batched path)
+// out[t, n] = epilogue( sum_k X0[t,k] W0[n,k] , sum_k X1[t,k] W1[n,k] )
+enum GemmMode : int {
+    GEMM_STORE_F32 = 0,   // out fp32  = a0 (+ alpha * a1)
+    GEMM_STORE_BF16 = 1,  // out bf16  = bf16(a0 (+ alpha * a1))
+    GEMM_RESIDUAL = 2,    // out bf16 += a0 (+ alpha * a1), i.e. out = bf16(float(out) + sum)
+    GEMM_SWIGLU = 3,      // out bf16  = bf16(silu(bf16(a0)) * bf16(a1))   (a0 gate rows, a1 up rows)
+};
+struct GemmOperand {
+    const bf16* W;  // [N, K] row-major, row stride ldw elements
+    int64_t ldw;
+    const bf16* X;  // [T, K] row-major, row stride ldx elements
+    int64_t ldx;
+    int K;          // 0 = operand unused
+};
+struct GemmCall {
+    GemmOperand op[2];
+    int N, T;
+    int mode;
+    float alpha;
+    void* out;
+    int64_t ldo;
+    int x_rows_alloc;  // rows that exist in the X buffers (>= T); the tensor map covers them
+};
+struct GemmWorkspace {
+    float* partials;        // split-K partial tiles
+    size_t partial_floats;  // capacity
+    int* counters;          // one ticket per output tile, zero on entry and on exit
+    int num_counters;
+    int* status;            // device status word
+    int num_sms;
+};
+// returns cudaError (launch) or -1000 if the tensor maps could not be encoded
+int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, int force_splits = 0);
+
+// ------------------------------------------------------------------ paged KV cache view
+struct KvView {
+    bf16* k_pool;            // [L][pages][nkv][kPageTokens][hd]
+    bf16* v_pool;
+    const int* block_table;  // [max_batch][max_pages_per_seq]
+    int max_pages_per_seq;
+    int num_pages;           // pages per layer
+    size_t layer_stride;     // elements between layers of a pool
+    int nkv, hd;
+};
+
+// ------------------------------------------------------------------ row kernels of the batched path
+void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s);
+void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s);
+// qkv fp32 [T, (nh+2nkv)*hd] -> bf16 round, bias (bf16 add), RoPE, q fp32 [T, nh*hd], K/V into pages
+void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
+                     const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
+                     int T, int nh, int max_pos, int* status, cudaStream_t s);
+// logits fp32 [R, V] -> argmax (lowest index among maxima)
+void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s);
+
+// ------------------------------------------------------------------ attention over the paged cache
+struct AttnWorkspace {
+    float* partials;  // [T*nkv][splits][G*(hd+2)]
+    size_t partial_floats;
+    int* counters;    // [T*nkv]
+    int num_counters;
+};
+// one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t]
+void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s);
+
+// ------------------------------------------------------------------ batch-1 fused decode kernels
+struct Bs1Layer {
+    const bf16 *wqkv, *bqkv;  // [(nh+2nkv)*hd, H] rows q|k|v ; bias or null
+    const bf16 *wo;           // [H, nh*hd]
+    const bf16 *attn_norm, *ffn_norm;
+    const bf16 *ffn_base;     // [I][3][H]: gate row, up row, down column (= row of down^T) per intermediate index
+    const bf16 *ffn_expert;   // same layout or null
+};
+struct Bs1Ctx {
+    int H, I, nh, nkv, hd, V;
+    float eps, expert_scale;
+    const float *rope_cos, *rope_sin;
+    int max_pos;
+    bf16* h;          // [H] residual stream
+    float* q;         // [nh*hd]
+    bf16* ctx;        // [nh*hd]
+    int* token;       // device: current input token (slot 0)
+    int* seq_len;     // device: cached tokens of the slot = position of the new token
+    int slot;
+    float* ffn_part;  // [ffn_grid][H] per-CTA partial sums + group partials
+    int* tickets;     // zeroed tickets
+    float* lm_val;    // [lm_grid] candidates
+    int* lm_idx;
+    float* logits;    // optional fp32 [V] or null
+    int* out_tokens;  // device ring of picks, or null
+    int* step_counter;
+    int* status;
+    int num_sms;
+};
+bool bs1_supported(int H, int I, int hd, int nh, int nkv);
+size_t bs1_ffn_part_floats(int H, int num_sms);
+void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvView kv, int layer, bool first, cudaStream_t s,
+                    bool pdl);
+void launch_bs1_oproj(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl);
+void launch_bs1_ffn(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl);
+void launch_bs1_lmhead(const Bs1Ctx& c, const bf16* final_norm, const bf16* lm_head, cudaStream_t s, bool pdl);
+
+// fp32 -> bf16 (RNE) on device, used by the expert loader (inference/src/io/checkpoint.cpp:33-62)
+void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s);
+// pack gate/up/down^T rows into the [I][3][H] record layout of the batch-1 FFN kernel
+void launch_pack_ffn(const bf16* gate, const bf16* up, const bf16* down, bf16* packed, int I, int H, cudaStream_t s);
+
+// a kernel whose only job is to wait on an mbarrier nothing signals, for the bounded-wait test
+void launch_wait_selftest(int* status, cudaStream_t s);
+
+}  // namespace tffn

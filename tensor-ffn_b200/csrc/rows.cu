@@ -1,0 +1,205 @@
+// Row-wise kernels of the batched path and load-time helpers. Each states the reference
+// kernel whose arithmetic (and rounding points) it reproduces.
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tffn {
+
+namespace {
+
+// h[t,:] = table[tokens[t],:]  (k_embed, inference/src/model/qwen.cu:216-220); ids are bounds-checked.
+__global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ h, int T,
+                             int H, int V, int* status) {
+    int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) {
+        if (threadIdx.x == 0) dev_fail(status, DEV_ERR_BOUNDS);
+        tok = 0;
+    }
+    const uint4* src = (const uint4*)(table + (size_t)tok * H);
+    uint4* dst = (uint4*)(h + (size_t)t * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w))  (k_rmsnorm, inference/src/backend/cuda_ops.cu:75-96)
+__global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                      bf16* __restrict__ out, int H, float eps,
+                                                      const int* __restrict__ row_idx) {
+    const int r = blockIdx.x;
+    const int src_row = row_idx ? row_idx[r] : r;
+    const uint4* xr = (const uint4*)(x + (size_t)src_row * H);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H / 8; i += 128) {
+        uint4 v = xr[i];
+        uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float a = bf16_lo(u[j]), b = bf16_hi(u[j]);
+            ss += a * a + b * b;
+        }
+    }
+    __shared__ float red[4];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = red[0] + red[1] + red[2] + red[3];
+    const float rinv = rsqrtf(ss / (float)H + eps);
+    const uint4* wr = (const uint4*)w;
+    uint4* orow = (uint4*)(out + (size_t)r * H);
+    for (int i = threadIdx.x; i < H / 8; i += 128) {
+        uint4 v = xr[i], g = __ldg(wr + i);
+        uint32_t u[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w}, o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float a = bf16_lo(u[j]) * rinv * bf16_lo(gw[j]);
+            float b = bf16_hi(u[j]) * rinv * bf16_hi(gw[j]);
+            o[j] = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
+        }
+        orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// After the fused q|k|v GEMM (fp32 accumulators): round to bf16, add the bias in bf16
+// (k_add_bias, qwen.cu:223-226), rotate q and k in fp32 at the token's position
+// (k_rope, qwen.cu:232-244), keep q in fp32, round k to bf16 into its page, store v as bf16
+// (qwen.cu:339-346). grid (T, nh + 2*nkv), block hd/2: thread i owns the pair (i, i + hd/2).
+__global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict__ bq, const bf16* __restrict__ bk,
+                           const bf16* __restrict__ bv, const float* __restrict__ rope_cos,
+                           const float* __restrict__ rope_sin, const int* __restrict__ tok_seq,
+                           const int* __restrict__ tok_pos, float* __restrict__ q_out, KvView kv, int layer, int nh,
+                           int max_pos, int* status) {
+    const int t = blockIdx.x, head = blockIdx.y, i = threadIdx.x;
+    const int hd = kv.hd, half = hd >> 1, nkv = kv.nkv;
+    const int nq = nh * hd, nk = nkv * hd, ntot = nq + 2 * nk;
+    const int pos = tok_pos[t], seq = tok_seq[t];
+    const float* row = qkv + (size_t)t * ntot;
+    int col0;
+    const bf16* bias;
+    int kind;  // 0 q, 1 k, 2 v
+    int hh;
+    if (head < nh) { kind = 0; hh = head; col0 = head * hd; bias = bq ? bq + head * hd : nullptr; }
+    else if (head < nh + nkv) { kind = 1; hh = head - nh; col0 = nq + hh * hd; bias = bk ? bk + hh * hd : nullptr; }
+    else { kind = 2; hh = head - nh - nkv; col0 = nq + nk + hh * hd; bias = bv ? bv + hh * hd : nullptr; }
+    float x0 = bf16_round(row[col0 + i]), x1 = bf16_round(row[col0 + i + half]);
+    if (bias) {
+        x0 = bf16_round(x0 + __bfloat162float(bias[i]));
+        x1 = bf16_round(x1 + __bfloat162float(bias[i + half]));
+    }
+    if (pos < 0 || pos >= max_pos) {
+        if (i == 0) dev_fail(status, DEV_ERR_BOUNDS);
+        return;
+    }
+    if (kind != 2) {
+        const float c = rope_cos[(size_t)pos * half + i], s = rope_sin[(size_t)pos * half + i];
+        const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
+        x0 = r0;
+        x1 = r1;
+    }
+    if (kind == 0) {
+        float* qo = q_out + (size_t)t * nq + hh * hd;
+        qo[i] = x0;
+        qo[i + half] = x1;
+        return;
+    }
+    const int pg = kv.block_table[(size_t)seq * kv.max_pages_per_seq + pos / kPageTokens];
+    if (pg < 0 || pg >= kv.num_pages) {
+        if (i == 0) dev_fail(status, DEV_ERR_BOUNDS);
+        return;
+    }
+    bf16* pool = (kind == 1 ? kv.k_pool : kv.v_pool) + (size_t)layer * kv.layer_stride;
+    bf16* dst = pool + (((size_t)pg * nkv + hh) * kPageTokens + pos % kPageTokens) * hd;
+    dst[i] = __float2bfloat16_rn(x0);
+    dst[i + half] = __float2bfloat16_rn(x1);
+}
+
+// greedy pick: first index of the strict maximum (sample(), inference/src/main.cpp:45-51)
+__global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    const float* row = logits + (size_t)blockIdx.x * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += 1024) {
+        float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    // NaN-free inputs assumed; if every value is -inf the lowest index 0 wins below
+    __shared__ float sv[32];
+    __shared__ int si[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x];
+        bi = si[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+}
+
+__global__ void k_cast_f32_bf16(const float* __restrict__ src, bf16* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// packed[i][0][:] = gate[i,:], packed[i][1][:] = up[i,:], packed[i][2][h] = down[h, i]
+__global__ void k_pack_ffn(const bf16* __restrict__ gate, const bf16* __restrict__ up, const bf16* __restrict__ down,
+                           bf16* __restrict__ packed, int I, int H) {
+    const int i = blockIdx.x;
+    bf16* rec = packed + (size_t)i * 3 * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        rec[h] = gate[(size_t)i * H + h];
+        rec[H + h] = up[(size_t)i * H + h];
+        rec[2 * H + h] = down[(size_t)h * I + i];
+    }
+}
+
+__global__ void k_wait_selftest(int* status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        // nothing ever arrives on this barrier: the bounded wait must give up and report
+        for (uint32_t i = 0; i < (1u << 16); ++i)
+            if (mbar_try_wait(&bar, 0)) return;
+        dev_fail(status, DEV_ERR_TEST_WAIT);
+    }
+}
+
+}  // namespace
+
+void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s) {
+    k_embed_rows<<<T, 128, 0, s>>>(tokens, table, h, T, H, V, status);
+}
+void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s) {
+    k_rmsnorm_rows<<<T, 128, 0, s>>>(x, w, out, H, eps, row_idx);
+}
+void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
+                     const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
+                     int T, int nh, int max_pos, int* status, cudaStream_t s) {
+    dim3 grid(T, nh + 2 * kv.nkv);
+    k_qkv_post<<<grid, kv.hd / 2, 0, s>>>(qkv, bq, bk, bv, rope_cos, rope_sin, tok_seq, tok_pos, q_out, kv, layer, nh,
+                                         max_pos, status);
+}
+void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s) {
+    k_argmax_rows<<<R, 1024, 0, s>>>(logits, V, out);
+}
+void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s) {
+    int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    k_cast_f32_bf16<<<blocks, 256, 0, s>>>(src, dst, n);
+}
+void launch_pack_ffn(const bf16* gate, const bf16* up, const bf16* down, bf16* packed, int I, int H, cudaStream_t s) {
+    k_pack_ffn<<<I, 256, 0, s>>>(gate, up, down, packed, I, H);
+}
+void launch_wait_selftest(int* status, cudaStream_t s) { k_wait_selftest<<<1, 32, 0, s>>>(status); }
+
+}  // namespace tffn

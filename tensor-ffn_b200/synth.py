@@ -29,8 +29,8 @@ EXPERT_MAGIC = 0x45585054
 
 SHAPES = {
     # name: hidden, layers, q heads, kv heads, intermediate, vocab, tied
-    "tiny": dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-                 intermediate_size=256, vocab_size=512, tie_word_embeddings=True),
+    "tiny": dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                 intermediate_size=512, vocab_size=1024, tie_word_embeddings=True),
     "tiny128": dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
                     intermediate_size=384, vocab_size=640, tie_word_embeddings=False),
     "0.5b": dict(hidden_size=896, num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2,
