@@ -137,6 +137,14 @@ int tffn_decode_run(tffn_session* s, int n_seqs, int steps, int32_t* tokens_out)
 /* Device status word (0 = none) and kernel launches issued by the session so far. */
 int tffn_session_status(tffn_session* s);
 uint64_t tffn_session_launch_count(const tffn_session* s);
+/* Per-kernel timing for benchmarks: while enabled, every kernel launch of the session is
+ * bracketed by CUDA events on the session's stream (this serialises kernels that would
+ * otherwise overlap, so never time throughput with it on). tffn_session_profile_read returns the
+ * number of kernel classes and fills ms[i] (device time) and launches[i] for i < cap;
+ * tffn_profile_class_name(i) names class i. No counterpart in the reference. */
+int tffn_session_profile(tffn_session* s, int enable);
+int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int cap);
+const char* tffn_profile_class_name(int cls);
 /* the stream the session launches on (a cudaStream_t) */
 void* tffn_session_stream(const tffn_session* s);
 

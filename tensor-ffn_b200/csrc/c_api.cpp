@@ -271,6 +271,21 @@ int tffn_decode_run(tffn_session* s, int n_seqs, int steps, int32_t* tokens_out)
         s->s->decode_run(n_seqs, steps, tokens_out);
     });
 }
+int tffn_session_profile(tffn_session* s, int enable) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_profile(enable != 0);
+    });
+}
+int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int cap) {
+    int n = 0;
+    int rc = guard([&] {
+        need(s, "NULL session");
+        n = s->s->read_profile(ms, launches, cap);
+    });
+    return rc < 0 ? rc : n;
+}
+const char* tffn_profile_class_name(int cls) { return kclass_name(cls); }
 int tffn_session_status(tffn_session* s) {
     int st = 0;
     int rc = guard([&] {

@@ -561,7 +561,7 @@ namespace {
 template <typename Kern, typename... Args>
 void launch_pdl(Kern k, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
     cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof cfg);
+    cfg = cudaLaunchConfig_t{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;

@@ -258,6 +258,8 @@ Session::~Session() {
     cudaSetDevice(m_->device);
     cudaStreamSynchronize(stream_);
     if (bs1_graph_) cudaGraphExecDestroy(bs1_graph_);
+    prof_resolve();
+    for (cudaEvent_t e : prof_free_) cudaEventDestroy(e);
     if (h_status_) cudaFreeHost(h_status_);
     if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
     if (own_stream_) cudaStreamDestroy(stream_);
@@ -400,6 +402,67 @@ void Session::check_status() {
     }
 }
 
+// ---------------------------------------------------------------- per-launch profile
+const char* kclass_name(int c) {
+    static const char* names[KC_COUNT] = {"embed_rows", "rmsnorm_rows", "gemm_tc:qkv", "qkv_post", "attn_decode",
+                                          "gemm_tc:o_proj", "gemm_tc:gate_up_swiglu", "gemm_tc:down", "gemm_tc:lm_head",
+                                          "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead"};
+    return (c >= 0 && c < KC_COUNT) ? names[c] : "?";
+}
+void Session::set_profile(bool on) {
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    prof_resolve();
+    profile_ = on;
+    if (on) {
+        memset(prof_ms_, 0, sizeof prof_ms_);
+        memset(prof_n_, 0, sizeof prof_n_);
+    }
+}
+void Session::prof_begin(int cls) {
+    if (!profile_) return;
+    if (prof_recs_.size() >= 8192) {
+        TFFN_CUDA(cudaStreamSynchronize(stream_));
+        prof_resolve();
+    }
+    ProfRec r;
+    r.cls = cls;
+    for (cudaEvent_t* e : {&r.a, &r.b}) {
+        if (!prof_free_.empty()) {
+            *e = prof_free_.back();
+            prof_free_.pop_back();
+        } else {
+            TFFN_CUDA(cudaEventCreate(e));
+        }
+    }
+    TFFN_CUDA(cudaEventRecord(r.a, stream_));
+    prof_recs_.push_back(r);
+}
+void Session::prof_end() {
+    if (!profile_) return;
+    TFFN_CUDA(cudaEventRecord(prof_recs_.back().b, stream_));
+}
+void Session::prof_resolve() {
+    for (auto& r : prof_recs_) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            prof_ms_[r.cls] += ms;
+            prof_n_[r.cls] += 1;
+        }
+        prof_free_.push_back(r.a);
+        prof_free_.push_back(r.b);
+    }
+    prof_recs_.clear();
+}
+int Session::read_profile(float* ms, int* counts, int cap) {
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    prof_resolve();
+    for (int i = 0; i < KC_COUNT && i < cap; ++i) {
+        if (ms) ms[i] = prof_ms_[i];
+        if (counts) counts[i] = prof_n_[i];
+    }
+    return KC_COUNT;
+}
+
 // ---------------------------------------------------------------- batched path (tensor-core GEMMs)
 void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx) {
     const Config& c = m_->cfg;
@@ -411,17 +474,23 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     const int* tok_pos = decode ? seq_len_dev_.as<int>() : tok_pos_.as<int>();
     int* status = status_.as<int>();
     const GemmWorkspace gws = gemm_ws();
-    auto gemm = [&](const GemmCall& call) {
+    auto gemm = [&](const GemmCall& call, int cls) {
+        prof_begin(cls);
         int rc = launch_gemm(call, gws, stream_);
+        prof_end();
         if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");
         if (rc != 0) cuda_check((cudaError_t)rc, "tensor-core GEMM launch", __FILE__, __LINE__);
         launches_++;
     };
+    prof_begin(KC_EMBED);
     launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_);
+    prof_end();
     launches_++;
     for (int l = 0; l < c.num_layers; ++l) {
         const LayerWeights& ly = m_->layers[l];
+        prof_begin(KC_RMSNORM);
         launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
         g.x_rows_alloc = cap_tokens_;
@@ -434,20 +503,26 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.mode = GEMM_STORE_F32;
         g.out = qkv_.p;
         g.ldo = nqkv;
-        gemm(g);
+        gemm(g, KC_GEMM_QKV);
         const bf16* b = ly.has_bias ? ly.bqkv.as<bf16>() : nullptr;
+        prof_begin(KC_QKV_POST);
         launch_qkv_post(qkv_.as<float>(), b, b ? b + nh * hd : nullptr, b ? b + (nh + nkv) * hd : nullptr, rope_cos_.as<float>(),
                         rope_sin_.as<float>(), tok_seq, tok_pos, q_.as<float>(), kv_, l, T, nh, max_seq_, status, stream_);
+        prof_end();
+        prof_begin(KC_ATTENTION);
         launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
                          status, stream_);
+        prof_end();
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
         g.N = H;
         g.mode = GEMM_RESIDUAL;
         g.out = h_.p;
         g.ldo = H;
-        gemm(g);
+        gemm(g, KC_GEMM_OPROJ);
+        prof_begin(KC_RMSNORM);
         launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        prof_end();
         launches_ += 4;
         // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records
         auto swiglu = [&](const FfnWeights& f, bf16* act) {
@@ -458,7 +533,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
             g.mode = GEMM_SWIGLU;
             g.out = act;
             g.ldo = I;
-            gemm(g);
+            gemm(g, KC_GEMM_GATEUP);
         };
         swiglu(ly.ffn, act_b_.as<bf16>());
         if (e_) swiglu(e_->layers[l], act_e_.as<bf16>());
@@ -474,7 +549,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.mode = GEMM_RESIDUAL;
         g.out = h_.p;
         g.ldo = H;
-        gemm(g);
+        gemm(g, KC_GEMM_DOWN);
         g.alpha = 1.f;
         if (hidden_rows_cap_ > 0) {
             const int rows = std::min(T, hidden_rows_cap_);
@@ -487,7 +562,9 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     }
     if (n_logit_rows > 0) {
         const int* rows = logit_rows_are_all ? nullptr : row_idx_.as<int>();
+        prof_begin(KC_RMSNORM);
         launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_);
+        prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
         g.x_rows_alloc = cap_tokens_;
@@ -498,8 +575,10 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.mode = GEMM_STORE_F32;
         g.out = logits_.p;
         g.ldo = V;
-        gemm(g);
+        gemm(g, KC_GEMM_LMHEAD);
+        prof_begin(KC_ARGMAX);
         launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_);
+        prof_end();
         launches_ += 2;
     }
     TFFN_CUDA(cudaGetLastError());
@@ -548,18 +627,28 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
         ly.ffn_norm = lw.ffn_norm.as<bf16>();
         ly.ffn_base = lw.ffn.packed.as<bf16>();
         ly.ffn_expert = e_ ? e_->layers[l].packed.as<bf16>() : nullptr;
+        prof_begin(KC_BS1_QKV);
         launch_bs1_qkv(x, ly, m_->embed.as<bf16>(), kv_, l, l == 0, stream_, pdl);
+        prof_end();
+        prof_begin(KC_ATTENTION);
         launch_attention(x.q, kv_, l, identity_.as<int>(), seq_len_dev_.as<int>(), x.ctx, 1, c.num_heads, max_seq_, attn_ws(),
                          m_->num_sms, status_.as<int>(), stream_);
+        prof_end();
+        prof_begin(KC_BS1_OPROJ);
         launch_bs1_oproj(x, ly, stream_, pdl);
+        prof_end();
+        prof_begin(KC_BS1_FFN);
         launch_bs1_ffn(x, ly, stream_, pdl);
+        prof_end();
     }
+    prof_begin(KC_BS1_LMHEAD);
     launch_bs1_lmhead(x, m_->final_norm.as<bf16>(), m_->lm_head, stream_, pdl);
+    prof_end();
     launches_ += (uint64_t)c.num_layers * 4 + 1;
 }
 
 void Session::run_bs1(bool want_logits) {
-    if (launch_mode_ == 2) {
+    if (launch_mode_ == 2 && !profile_) {
         if (!bs1_graph_ || bs1_graph_logits_ != want_logits) {
             if (bs1_graph_) {
                 cudaGraphExecDestroy(bs1_graph_);

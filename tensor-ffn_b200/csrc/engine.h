@@ -60,8 +60,18 @@ struct Expert {
     static Expert* load(const Model* m, const std::string& path, float scale);
 };
 
+// kernel classes of the per-launch profile (tffn_session_profile_*)
+enum KClass : int {
+    KC_EMBED = 0, KC_RMSNORM, KC_GEMM_QKV, KC_QKV_POST, KC_ATTENTION, KC_GEMM_OPROJ, KC_GEMM_GATEUP, KC_GEMM_DOWN,
+    KC_GEMM_LMHEAD, KC_ARGMAX, KC_ADVANCE, KC_BS1_QKV, KC_BS1_OPROJ, KC_BS1_FFN, KC_BS1_LMHEAD, KC_COUNT
+};
+const char* kclass_name(int c);
+
 class Session {
 public:
+    void set_profile(bool on);
+    // accumulated device time (ms) and launches per class since set_profile(true); returns KC_COUNT
+    int read_profile(float* ms, int* counts, int cap);
     Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream);
     ~Session();
     void reset(int slot);
@@ -115,6 +125,17 @@ private:
     DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
     cudaGraphExec_t bs1_graph_ = nullptr;
     bool bs1_graph_logits_ = false;
+
+    // per-launch profile: event pairs around every kernel, resolved in read_profile
+    bool profile_ = false;
+    struct ProfRec { int cls; cudaEvent_t a, b; };
+    std::vector<ProfRec> prof_recs_;
+    std::vector<cudaEvent_t> prof_free_;
+    float prof_ms_[KC_COUNT] = {0};
+    int prof_n_[KC_COUNT] = {0};
+    void prof_begin(int cls);
+    void prof_end();
+    void prof_resolve();
 
     // hidden-state capture
     DeviceBuffer hidden_;

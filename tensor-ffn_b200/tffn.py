@@ -80,6 +80,9 @@ _SIGS = {
     "tffn_forward": (_i, [_vp, _i, _vp, _i, _vp]),
     "tffn_decode_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "tffn_decode_run": (_i, [_vp, _i, _i, _vp]),
+    "tffn_session_profile": (_i, [_vp, _i]),
+    "tffn_session_profile_read": (_i, [_vp, _vp, _vp, _i]),
+    "tffn_profile_class_name": (_cp, [_i]),
     "tffn_session_status": (_i, [_vp]),
     "tffn_session_launch_count": (ctypes.c_uint64, [_vp]),
     "tffn_session_stream": (_vp, [_vp]),
@@ -302,6 +305,16 @@ class Session:
         out = np.empty((steps, n_seqs), dtype=np.int32) if want_tokens else None
         _check(_L.tffn_decode_run(self._h, n_seqs, steps, _ptr(out)))
         return out
+
+    def profile(self, on: bool):
+        _check(_L.tffn_session_profile(self._h, int(on)))
+
+    def profile_read(self) -> dict:
+        """kernel class -> (device ms, launches) accumulated since profile(True)"""
+        ms = np.zeros(64, dtype=np.float32)
+        n = np.zeros(64, dtype=np.int32)
+        k = _check(_L.tffn_session_profile_read(self._h, ms.ctypes.data, n.ctypes.data, 64))
+        return {_L.tffn_profile_class_name(i).decode(): (float(ms[i]), int(n[i])) for i in range(k) if n[i] > 0}
 
     def status(self) -> int:
         return _check(_L.tffn_session_status(self._h))

@@ -1,0 +1,131 @@
+"""-m gpu: BASELINE.json configs[0] at full size — Qwen2.5-0.5B shape, bf16, batch 1, 128-token
+prompt then 128 greedy tokens, with and without the expert — against (a) the reference's own code
+(oracle/_ref/ref_driver, when it was built) and (b) the CPU oracle, teacher-forced on the
+reference's token stream. Bars from BASELINE: per-layer hidden states and logits within
+max|a-b| / max|b| <= 2e-2, top-1 agreement >= 99 %.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DRIVER = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+P, N = 128, 128
+TOL = 2e-2
+
+
+def bf16_to_f32(u):
+    return (u.astype(np.uint32) << 16).view(np.float32)
+
+
+def rel(a, b):
+    return float(np.abs(a - b).max() / np.abs(b).max())
+
+
+@pytest.fixture(scope="module")
+def full_model():
+    sys.path.insert(0, ROOT)
+    import bench
+    import tffn
+    d, ep, cfg = bench.ensure_model("0.5b")
+    m = tffn.qwen_load(d)
+    return d, ep, cfg, m
+
+
+def _reference_run(d, ep, toks, expert, tmpdir):
+    tf = os.path.join(tmpdir, "tok.i32")
+    np.asarray(toks, dtype=np.int32).tofile(tf)
+    out = os.path.join(tmpdir, "ref")
+    cmd = [DRIVER, "--model", d, "--max-seq", str(P + N + 8), "--tokens", tf, "--prompt-len", str(P), "--new", str(N),
+           "--out", out, "--hidden"]
+    if expert:
+        cmd += ["--expert", ep, "--expert-scale", "0.1"]
+    subprocess.check_call(cmd)
+    return out
+
+
+@pytest.mark.parametrize("expert", [False, True], ids=["base", "expert"])
+def test_config0_against_reference_and_oracle(full_model, expert, tmp_path):
+    import oracle
+    import synth
+    import tffn
+    d, ep, cfg, m = full_model
+    V, H, L = cfg["vocab_size"], cfg["hidden_size"], cfg["num_hidden_layers"]
+    prompt = synth.prompts(1, P, 0)[0]
+    e = tffn.checkpoint_load(ep, m, 0.1) if expert else None
+    s = tffn.Session(m, e, max_batch=1, max_seq=P + N + 8)
+    have_ref = os.path.exists(DRIVER)
+    if have_ref:
+        pre = _reference_run(d, ep, prompt, expert, str(tmp_path))
+        ref_logits = np.fromfile(pre + ".logits.f32", dtype=np.float32).reshape(1 + N, V)
+        ref_picks = np.fromfile(pre + ".tokens.i32", dtype=np.int32)
+        ref_hidden = np.fromfile(pre + ".hidden.bf16", dtype=np.uint16).reshape(L, P, H)
+        stream_tokens = ref_picks[:N]  # the reference's own greedy stream is the teacher
+    else:
+        o0 = oracle.Oracle(d, P + N + 8, ep if expert else None, 0.1)
+        stream_tokens = o0.generate(prompt, N)
+
+    # ours: prompt through the tensor-core path (hidden states captured), then the fused batch-1
+    # kernels one teacher-forced token at a time
+    s.capture_hidden(P)
+    nxt, lg_last = s.prefill([prompt], want_logits=True)
+    hidden = [bf16_to_f32(s.get_hidden(l, P)) for l in range(L)]
+    s.capture_hidden(0)
+    ours = [lg_last[0].copy()]
+    for t in stream_tokens:
+        _, lg = s.decode_step([int(t)], want_logits=True)
+        ours.append(lg[0].copy())
+    ours = np.array(ours)
+    assert s.status() == 0
+
+    # CPU oracle on the same stream
+    o = oracle.Oracle(d, P + N + 8, ep if expert else None, 0.1)
+    r = o.forward(prompt, want_hidden=True, last_only=True)
+    orc = [r["logits"][0]] + [o.forward([int(t)])["logits"][0] for t in stream_tokens]
+    orc = np.array(orc)
+    report = {"ours_vs_oracle_logits": rel(ours, orc),
+              "ours_vs_oracle_hidden_max": max(rel(hidden[l], bf16_to_f32(r["hidden"][l])) for l in range(L)),
+              "ours_vs_oracle_top1": float((ours.argmax(-1) == orc.argmax(-1)).mean())}
+    if have_ref:
+        report.update({
+            "ours_vs_reference_logits": rel(ours, ref_logits),
+            "ours_vs_reference_hidden_max": max(rel(hidden[l], bf16_to_f32(ref_hidden[l])) for l in range(L)),
+            "ours_vs_reference_top1": float((ours.argmax(-1) == ref_logits.argmax(-1)).mean()),
+            "oracle_vs_reference_logits": rel(orc, ref_logits),
+            "oracle_vs_reference_top1": float((orc.argmax(-1) == ref_logits.argmax(-1)).mean()),
+        })
+    print("PARITY", "expert" if expert else "base", report)
+    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+    with open(os.path.join(ROOT, "gpurun_out", f"parity_config0_{'expert' if expert else 'base'}.json"), "w") as f:
+        import json
+        json.dump(report, f)
+    assert report["ours_vs_oracle_logits"] <= TOL
+    assert report["ours_vs_oracle_hidden_max"] <= TOL
+    assert report["ours_vs_oracle_top1"] >= 0.99
+    if have_ref:
+        assert report["ours_vs_reference_logits"] <= TOL
+        assert report["ours_vs_reference_hidden_max"] <= TOL
+        assert report["ours_vs_reference_top1"] >= 0.99
+
+
+def test_batched_decode_matches_bs1_tokens_fullsize(full_model):
+    """data-parallel invariance at full size: a sequence decoded alone (fused batch-1 kernels) and
+    inside a batch of 8 (tensor-core path) yields logits within tolerance at every step"""
+    import synth
+    import tffn
+    d, ep, cfg, m = full_model
+    e = tffn.checkpoint_load(ep, m, 0.1)
+    prompts = [synth.prompts(1, 64, 300 + i)[0] for i in range(8)]
+    forced = synth.prompts(8, 8, 77)
+    sb = tffn.Session(m, e, max_batch=8, max_seq=128)
+    sb.prefill(prompts)
+    batch = [sb.decode_step(forced[:, k], want_logits=True)[1].copy() for k in range(8)]
+    s1 = tffn.Session(m, e, max_batch=1, max_seq=128)
+    s1.prefill([prompts[3]])
+    for k in range(8):
+        _, lg = s1.decode_step([int(forced[3, k])], want_logits=True)
+        assert rel(lg[0], batch[k][3]) <= TOL
