@@ -200,19 +200,26 @@ bool dispatch_g(int G, dim3 grid, cudaStream_t s, const float* q, const KvView& 
 
 }  // namespace
 
-void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
-                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s) {
-    const int G = nh / kv.nkv;
-    const int units = T * kv.nkv;
+int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
+    const int G = nh / nkv;
+    const int units = T * nkv;
     int splits = 1;
     if (units < 2 * num_sms) {
         splits = (2 * num_sms + units - 1) / units;
         const int max_splits = (max_ctx + 2 * kPageTokens - 1) / (2 * kPageTokens);  // at least 64 rows per split
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
-        while (splits > 1 && ((size_t)units * splits * G * (kv.hd + 2) > ws.partial_floats || units > ws.num_counters))
+        while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))
             --splits;
     }
+    return splits;
+}
+
+void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s) {
+    const int G = nh / kv.nkv;
+    const int units = T * kv.nkv;
+    const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
     dim3 grid(units, splits);
     bool ok = false;
     if (kv.hd == 64) ok = dispatch_g<64>(G, grid, s, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);

@@ -319,6 +319,7 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
         memset(&g, 0, sizeof g);
         g.op[0] = {dw.as<bf16>(), K, dx.as<bf16>(), K, K};
         g.N = N; g.T = T; g.mode = GEMM_STORE_F32; g.alpha = 1.f; g.out = dout.p; g.ldo = N; g.x_rows_alloc = rows;
+        cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
         GemmWorkspace ws{part.as<float>(), part.bytes / 4, cnt.as<int>(), 8192, status.as<int>(), prop.multiProcessorCount};
         int rc = launch_gemm(g, ws, 0, splits);
         if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");

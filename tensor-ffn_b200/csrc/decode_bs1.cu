@@ -224,18 +224,24 @@ struct FfnSmem {
     size_t stage_bytes;
     size_t ring_off, part_off, bar_off, total;
 };
+// A stage is always consumed by the same warp (record r -> warp r % kFfnWarps, stage r % stages),
+// which needs stages % kFfnWarps == 0: with one parity bit per barrier a warp may only wait for
+// the NEXT phase of a stage, never for one two phases ahead of another warp's use.
+// The per-warp partial sums reuse the ring once every record has been consumed.
 __host__ __device__ inline FfnSmem ffn_smem_layout(int H, bool expert) {
     FfnSmem s;
     s.stage_bytes = (size_t)H * 2 * 3 * (expert ? 2 : 1);
     const size_t part = (size_t)kFfnWarps * H * 4;
     const size_t budget = 200 * 1024;
-    int st = (int)((budget - part) / s.stage_bytes);
-    if (st > 16) st = 16;
-    if (st < 2) st = 2;
+    int st = (int)(budget / s.stage_bytes) / kFfnWarps * kFfnWarps;
+    if (st > 32) st = 32;
+    if (st < kFfnWarps) st = kFfnWarps;
     s.stages = st;
     s.ring_off = 0;
-    s.part_off = (s.stage_bytes * st + 127) / 128 * 128;
-    s.bar_off = s.part_off + part;
+    s.part_off = 0;
+    size_t ring = s.stage_bytes * st;
+    if (ring < part) ring = part;
+    s.bar_off = (ring + 127) / 128 * 128;
     s.total = s.bar_off + (size_t)st * 16 + 64;
     return s;
 }
@@ -349,7 +355,10 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
-    // fold the consumer warps of this CTA (fixed order)
+    // fold the consumer warps of this CTA (fixed order); the partial sums reuse the ring, so
+    // every consumer must be done reading it first
+    constexpr int NT = kFfnWarps * 32;
+    asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
     const int nchunk = H >> 3;
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
@@ -360,7 +369,6 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
             dst[1] = make_float4(acc[j * 8 + 4], acc[j * 8 + 5], acc[j * 8 + 6], acc[j * 8 + 7]);
         }
     }
-    constexpr int NT = kFfnWarps * 32;
     asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
     float* my_part = c.ffn_part + (size_t)blockIdx.x * H;
     for (int col = threadIdx.x; col < H; col += NT) {
@@ -412,7 +420,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
 // ------------------------------------------------------------------------------------------ LM head + argmax
 constexpr int kLmWarps = 8;
 constexpr int kLmThreads = (kLmWarps + 1) * 32;
-constexpr int kLmRowsPerStage = 8;
+constexpr int kLmRowsPerStage = 4;
 
 struct LmSmem {
     int stages;
@@ -421,9 +429,9 @@ struct LmSmem {
 __host__ __device__ inline LmSmem lm_smem_layout(int H) {
     LmSmem s;
     s.stage_bytes = (size_t)kLmRowsPerStage * H * 2;
-    int st = (int)((192 * 1024) / s.stage_bytes);
-    if (st > 16) st = 16;
-    if (st < 2) st = 2;
+    int st = (int)((192 * 1024) / s.stage_bytes) / kLmWarps * kLmWarps;  // stages % warps == 0, see ffn_smem_layout
+    if (st > 32) st = 32;
+    if (st < kLmWarps) st = kLmWarps;
     s.stages = st;
     s.bar_off = (s.stage_bytes * st + 127) / 128 * 128;
     s.total = s.bar_off + (size_t)st * 16 + 64 + kLmWarps * 8;
@@ -591,6 +599,19 @@ inline int nch_of(int H) { return (H / 8 + 31) / 32; }
         default: break;                   \
     }
 
+int bs1_prepare(int H, bool expert) {
+    // the larger of the two FFN layouts covers sessions with and without an expert
+    const size_t ffn = ffn_smem_layout(H, expert).total > ffn_smem_layout(H, false).total ? ffn_smem_layout(H, expert).total
+                                                                                          : ffn_smem_layout(H, false).total;
+    const size_t lm = lm_smem_layout(H).total;
+    cudaError_t e1 = cudaSuccess, e2 = cudaSuccess;
+    TFFN_NCH_SWITCH(H, {
+        e1 = cudaFuncSetAttribute(k_bs1_ffn<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ffn);
+        e2 = cudaFuncSetAttribute(k_bs1_lmhead<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lm);
+    });
+    return e1 != cudaSuccess ? (int)e1 : (int)e2;
+}
+
 void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvView kv, int layer, bool first,
                     cudaStream_t s, bool pdl) {
     const int units = (c.nh + 2 * c.nkv) * (c.hd / 2);
@@ -605,28 +626,14 @@ void launch_bs1_ffn(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pd
     const FfnSmem L = ffn_smem_layout(c.H, ly.ffn_expert != nullptr);
     int G = c.num_sms < c.I ? c.num_sms : c.I;
     dim3 grid(G), block(kFfnThreads);
-    TFFN_NCH_SWITCH(c.H, {
-        static size_t configured = 0;
-        if (configured < L.total) {
-            cudaFuncSetAttribute(k_bs1_ffn<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
-            configured = L.total;
-        }
-        launch_pdl(k_bs1_ffn<NCH>, grid, block, L.total, s, pdl, c, ly);
-    });
+    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_ffn<NCH>, grid, block, L.total, s, pdl, c, ly));
 }
 void launch_bs1_lmhead(const Bs1Ctx& c, const bf16* final_norm, const bf16* lm_head, cudaStream_t s, bool pdl) {
     const LmSmem L = lm_smem_layout(c.H);
     int G = c.num_sms;
     if (G > c.V) G = c.V;
     dim3 grid(G), block(kLmThreads);
-    TFFN_NCH_SWITCH(c.H, {
-        static size_t configured = 0;
-        if (configured < L.total) {
-            cudaFuncSetAttribute(k_bs1_lmhead<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
-            configured = L.total;
-        }
-        launch_pdl(k_bs1_lmhead<NCH>, grid, block, L.total, s, pdl, c, final_norm, lm_head);
-    });
+    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_lmhead<NCH>, grid, block, L.total, s, pdl, c, final_norm, lm_head));
 }
 
 }  // namespace tffn

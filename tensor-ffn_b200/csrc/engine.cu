@@ -244,6 +244,8 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     TFFN_CUDA(cudaMallocHost(&h_status_, 4));
     *h_status_ = 0;
 
+    cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
+    if (m->bs1_ok) cuda_check((cudaError_t)bs1_prepare((int)H, true), "bs1_prepare", __FILE__, __LINE__);
     bs1_h_.alloc(H * 2);
     bs1_q_.alloc(nh * hd * 4);
     bs1_ctx_.alloc(nh * hd * 2);
@@ -257,7 +259,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
 Session::~Session() {
     cudaSetDevice(m_->device);
     cudaStreamSynchronize(stream_);
-    if (bs1_graph_) cudaGraphExecDestroy(bs1_graph_);
+    drop_graphs();
     prof_resolve();
     for (cudaEvent_t e : prof_free_) cudaEventDestroy(e);
     if (h_status_) cudaFreeHost(h_status_);
@@ -300,20 +302,14 @@ void Session::ensure_logits(size_t rows) {
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     logits_.alloc(rows * (size_t)m_->cfg.vocab_size * 4);
     logits_rows_ = rows;
-    if (bs1_graph_) {  // the captured step holds the old pointer
-        cudaGraphExecDestroy(bs1_graph_);
-        bs1_graph_ = nullptr;
-    }
+    drop_graphs();  // captured steps hold the old pointer
 }
 void Session::ensure_ring(int entries) {
     if (entries <= out_ring_cap_) return;
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     out_ring_.alloc((size_t)entries * 4);
     out_ring_cap_ = entries;
-    if (bs1_graph_) {
-        cudaGraphExecDestroy(bs1_graph_);
-        bs1_graph_ = nullptr;
-    }
+    drop_graphs();
 }
 
 void Session::reset(int slot) {
@@ -673,6 +669,55 @@ void Session::run_bs1(bool want_logits) {
     TFFN_CUDA(cudaGetLastError());
 }
 
+void Session::drop_graphs() {
+    if (bs1_graph_) cudaGraphExecDestroy(bs1_graph_);
+    bs1_graph_ = nullptr;
+    for (auto& kv : dec_graphs_) cudaGraphExecDestroy(kv.second.exec);
+    dec_graphs_.clear();
+}
+
+// one decode step of n_seqs slots on the tensor-core path, then publish picks / advance lengths
+void Session::run_decode_batched(int n_seqs, int max_ctx) {
+    auto body = [&] {
+        run_batched(n_seqs, n_seqs, true, true, max_ctx);
+        prof_begin(KC_ADVANCE);
+        k_decode_advance<<<1, 256, 0, stream_>>>(picks_.as<int>(), n_seqs, dec_tokens_.as<int>(), seq_len_dev_.as<int>(),
+                                                 out_ring_.as<int>(), step_counter_.as<int>());
+        prof_end();
+        launches_++;
+    };
+    if (launch_mode_ != 2 || profile_ || hidden_rows_cap_ > 0) {
+        body();
+        return;
+    }
+    const Config& c = m_->cfg;
+    const int splits = attention_splits(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms);
+    const auto key = std::make_pair(n_seqs, splits);
+    auto it = dec_graphs_.find(key);
+    if (it == dec_graphs_.end()) {
+        cudaGraph_t graph = nullptr;
+        const uint64_t before = launches_;
+        TFFN_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+        try {
+            body();
+        } catch (...) {
+            cudaStreamEndCapture(stream_, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
+        const uint64_t n_launch = launches_ - before;
+        launches_ = before;
+        TFFN_CUDA(ce);
+        cudaGraphExec_t exec = nullptr;
+        TFFN_CUDA(cudaGraphInstantiate(&exec, graph, 0));
+        cudaGraphDestroy(graph);
+        it = dec_graphs_.emplace(key, DecGraph{exec, n_launch}).first;
+    }
+    TFFN_CUDA(cudaGraphLaunch(it->second.exec, stream_));
+    launches_ += it->second.launches;
+}
+
 // ---------------------------------------------------------------- public operations
 void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs, int32_t* next_tokens, float* logits_last) {
     if (!tokens || !seq_lens || n_seqs < 1 || n_seqs > max_batch_) throw Error(kErrInvalid, "bad prefill arguments");
@@ -811,10 +856,7 @@ void Session::decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_to
     } else {
         int max_ctx = 1;
         for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + 1);
-        run_batched(n_seqs, n_seqs, true, true, max_ctx);
-        k_decode_advance<<<1, 256, 0, stream_>>>(picks_.as<int>(), n_seqs, dec_tokens_.as<int>(),
-                                                                 seq_len_dev_.as<int>(), out_ring_.as<int>(), step_counter_.as<int>());
-        launches_++;
+        run_decode_batched(n_seqs, max_ctx);
     }
     TFFN_CUDA(cudaMemcpyAsync(pin, dec_tokens_.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, stream_));
     if (logits) TFFN_CUDA(cudaMemcpyAsync(logits, logits_.p, (size_t)n_seqs * V * 4, cudaMemcpyDeviceToHost, stream_));
@@ -839,11 +881,7 @@ void Session::decode_run(int n_seqs, int steps, int32_t* tokens_out) {
         if (bs1) {
             run_bs1(false);
         } else {
-            run_batched(n_seqs, n_seqs, true, true, max_ctx);
-            k_decode_advance<<<1, 256, 0, stream_>>>(picks_.as<int>(), n_seqs, dec_tokens_.as<int>(),
-                                                                     seq_len_dev_.as<int>(), out_ring_.as<int>(),
-                                                                     step_counter_.as<int>());
-            launches_++;
+            run_decode_batched(n_seqs, max_ctx);
         }
     }
     if (tokens_out)

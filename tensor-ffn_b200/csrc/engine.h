@@ -5,6 +5,7 @@
 #include "host_io.h"
 #include "kernels.h"
 #include <cstdint>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -125,6 +126,11 @@ private:
     DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
     cudaGraphExec_t bs1_graph_ = nullptr;
     bool bs1_graph_logits_ = false;
+    // batched decode steps captured per (sequences, attention splits)
+    struct DecGraph { cudaGraphExec_t exec; uint64_t launches; };
+    std::map<std::pair<int, int>, DecGraph> dec_graphs_;
+    void run_decode_batched(int n_seqs, int max_ctx);
+    void drop_graphs();
 
     // per-launch profile: event pairs around every kernel, resolved in read_profile
     bool profile_ = false;

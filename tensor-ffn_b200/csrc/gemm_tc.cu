@@ -19,6 +19,9 @@
 #include "kernels.h"
 #include "ptx.cuh"
 #include <cstdio>
+#include <cstring>
+#include <functional>
+#include <unordered_map>
 
 namespace tffn {
 
@@ -247,8 +250,40 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// 2-D bf16 tensor [rows, cols] with a row stride, box = box_rows x 64 columns, 128-byte swizzle
+struct TmapKey {
+    const void* ptr;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows;
+    bool operator==(const TmapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (k.rows * 1000003u) ^ (k.cols * 7919u) ^ (k.ld << 20) ^ k.box_rows;
+    }
+};
+
+bool encode_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows);
+
+// Encoding a tensor map costs microseconds of host time; the same (buffer, shape, box) recurs on
+// every step, so encoded maps are kept per thread (a session is used by one thread at a time).
 bool make_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
+    static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+    TmapKey key{ptr, rows, cols, ld_elems, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *tm = it->second;
+        return true;
+    }
+    if (!encode_tmap(tm, ptr, rows, cols, ld_elems, box_rows)) return false;
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *tm);
+    return true;
+}
+
+// 2-D bf16 tensor [rows, cols] with a row stride, box = box_rows x 64 columns, 128-byte swizzle
+bool encode_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -308,18 +343,22 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
                           n_tiles * t_tiles > ws.num_counters))
         --splits;
     p.splits = splits;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
     dim3 grid(n_tiles, t_tiles, splits);
     k_gemm_tc<BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(p);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
+
+int gemm_prepare() {
+    cudaError_t e;
+#define TFFN_PREP(BN)                                                                                                 \
+    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES); \
+    if (e != cudaSuccess) return (int)e;
+    TFFN_PREP(16) TFFN_PREP(32) TFFN_PREP(64) TFFN_PREP(128) TFFN_PREP(256)
+#undef TFFN_PREP
+    return 0;
+}
 
 int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, int force_splits) {
     if (c.T <= 0 || c.N <= 0 || c.op[0].K <= 0) return (int)cudaErrorInvalidValue;

@@ -43,6 +43,8 @@ struct GemmWorkspace {
     int* status;            // device status word
     int num_sms;
 };
+// opt the kernels into their dynamic shared memory sizes (once per device, outside stream capture)
+int gemm_prepare();
 // returns cudaError (launch) or -1000 if the tensor maps could not be encoded
 int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, int force_splits = 0);
 
@@ -74,6 +76,8 @@ struct AttnWorkspace {
     int* counters;    // [T*nkv]
     int num_counters;
 };
+// context splits launch_attention will use (a CUDA-graph key: the grid depends on it)
+int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
 // one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t]
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s);
@@ -109,6 +113,7 @@ struct Bs1Ctx {
 };
 bool bs1_supported(int H, int I, int hd, int nh, int nkv);
 size_t bs1_ffn_part_floats(int H, int num_sms);
+int bs1_prepare(int H, bool expert);  // dynamic shared memory opt-in for this shape (outside stream capture)
 void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvView kv, int layer, bool first, cudaStream_t s,
                     bool pdl);
 void launch_bs1_oproj(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl);

@@ -129,6 +129,7 @@ def test_batched_decode_many_sequences(model_dirs, n_seqs):
     """ragged prompts in several slots, then batched decode steps; every sequence vs its own oracle run"""
     import synth
     m, e, s, o, cfg = _mk(model_dirs, "mini05", True, max_batch=n_seqs, max_seq=128)
+    s.set_launch_mode(2)  # batched decode steps replayed from a CUDA graph
     V = cfg["vocab_size"]
     lens = [5 + (7 * i) % 23 for i in range(n_seqs)]
     prompts = [synth.prompts(1, lens[i], 100 + i, V)[0] for i in range(n_seqs)]
@@ -152,8 +153,9 @@ def test_batched_decode_many_sequences(model_dirs, n_seqs):
 def test_decode_run_is_deterministic_and_matches_stepwise(model_dirs):
     """device-resident multi-step decode == step-by-step decode, bit-identical tokens, both paths"""
     import synth
-    for n_seqs in (1, 4):
+    for n_seqs, mode in ((1, 1), (4, 1), (1, 2), (4, 2)):
         m, e, s, o, cfg = _mk(model_dirs, "tiny", True, max_batch=4, max_seq=128)
+        s.set_launch_mode(mode)
         prompts = [synth.prompts(1, 11 + i, 200 + i, cfg["vocab_size"])[0] for i in range(n_seqs)]
         s.prefill(prompts)
         a = s.decode_run(n_seqs, 10)
