@@ -153,6 +153,13 @@ void* tffn_session_stream(const tffn_session* s);
  * fp32 out, host pointers); splits = 0 lets the launcher choose the K split.
  * Stands in for gemm_bf16 (inference/src/backend/cuda_ops.cu:18-29). */
 int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits);
+/* The fused batch-1 SwiGLU kernel alone (host pointers, bf16 bits): h_out = bf16(h + FFN(rmsnorm(h)))
+ * with FFN = base + expert_scale * expert (packed_expert may be NULL). packed_* use the record
+ * layout [I][3][H] = gate row, up row, down column per intermediate index. Stands in for the FFN
+ * part of qwen_forward (inference/src/model/qwen.cu:422-447) and expert_forward_layer
+ * (inference/src/model/expert.cu:44-59) at T = 1. */
+int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
+                       const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out);
 /* Runs a kernel that waits on a barrier nothing signals; returns the device status it
  * recorded (expected: 5). Proves that a wait that runs out returns instead of hanging. */
 int tffn_op_wait_selftest(int device);

@@ -332,6 +332,49 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
     });
 }
 
+int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
+                       const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out) {
+    return guard([&] {
+        need(h_in && norm_w && packed_base && h_out && H > 0 && I > 0, "bad arguments");
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
+        TFFN_CUDA(cudaSetDevice(device));
+        if (H % 8 || H > 2048) throw Error(kErrUnsupported, "the batch-1 FFN kernel needs hidden % 8 == 0 and hidden <= 2048");
+        cudaDeviceProp prop;
+        TFFN_CUDA(cudaGetDeviceProperties(&prop, device));
+        cuda_check((cudaError_t)bs1_prepare(H, true), "bs1_prepare", __FILE__, __LINE__);
+        DeviceBuffer dh, dw, db, de, part, tickets, status;
+        dh.alloc((size_t)H * 2);
+        dw.alloc((size_t)H * 2);
+        db.alloc((size_t)I * 3 * H * 2);
+        TFFN_CUDA(cudaMemcpy(dh.p, h_in, (size_t)H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(dw.p, norm_w, (size_t)H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(db.p, packed_base, (size_t)I * 3 * H * 2, cudaMemcpyHostToDevice));
+        if (packed_expert) {
+            de.alloc((size_t)I * 3 * H * 2);
+            TFFN_CUDA(cudaMemcpy(de.p, packed_expert, (size_t)I * 3 * H * 2, cudaMemcpyHostToDevice));
+        }
+        part.alloc(bs1_ffn_part_floats(H, prop.multiProcessorCount) * 4);
+        tickets.alloc(256 * 4);
+        status.alloc(4);
+        Bs1Ctx x;
+        memset(&x, 0, sizeof x);
+        x.H = H; x.I = I; x.eps = eps; x.expert_scale = expert_scale;
+        x.h = dh.as<bf16>(); x.ffn_part = part.as<float>(); x.tickets = tickets.as<int>(); x.status = status.as<int>();
+        x.num_sms = prop.multiProcessorCount;
+        Bs1Layer ly;
+        memset(&ly, 0, sizeof ly);
+        ly.ffn_norm = dw.as<bf16>(); ly.ffn_base = db.as<bf16>(); ly.ffn_expert = packed_expert ? de.as<bf16>() : nullptr;
+        launch_bs1_ffn(x, ly, 0, false);
+        TFFN_CUDA(cudaGetLastError());
+        TFFN_CUDA(cudaDeviceSynchronize());
+        int st = 0;
+        TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
+        if (st) throw Error(kErrDevice, "FFN kernel reported device status " + std::to_string(st));
+        TFFN_CUDA(cudaMemcpy(h_out, dh.p, (size_t)H * 2, cudaMemcpyDeviceToHost));
+    });
+}
+
 int tffn_op_wait_selftest(int device) {
     int st = 0;
     int rc = guard([&] {

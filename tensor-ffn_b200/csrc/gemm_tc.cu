@@ -8,9 +8,10 @@
 //   warp 0   TMA producer: 128x64 weight box + BNx64 activation box per stage, 128-byte swizzle
 //   warp 1   allocates TMEM, issues tcgen05.mma (one thread), commits stages back to the producer
 //   warps 2-5 epilogue: tcgen05.ld the fp32 accumulators (lane = weight row, column = token),
-//            apply the epilogue and store; with split-K they write partial tiles and the last
-//            CTA to arrive (a ticket, no spinning) sums all partials in split order, so the
-//            result does not depend on scheduling.
+//            apply the epilogue and store. With split-K the splits of a tile are one thread-block
+//            cluster: partial tiles stay in shared memory and are summed across the cluster over
+//            distributed shared memory in rank order, so the result does not depend on
+//            scheduling and no partial sum touches HBM.
 // Two operand pairs can be accumulated into two TMEM regions (gate|up for the SwiGLU epilogue,
 // base|expert for the down projection) and are combined in fp32 in the epilogue.
 // It replaces the reference's cublasGemmEx wrappers (inference/src/backend/cuda_ops.cu:18-43)
@@ -39,8 +40,6 @@ struct GemmDev {
     float alpha;
     void* out;
     long long ldo;
-    float* ws;
-    int* counters;
     int* status;
 };
 
@@ -49,7 +48,12 @@ struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+    // BN <= 64 (decode): 4 stages keep a CTA under half an SM's shared memory, so two CTAs (or two
+    // tiles' splits) are resident per SM and the weight stream has 2 x 64 KB in flight per SM
+    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 4);
+    // split-K parks [accs][BN][128] fp32 partials in the stage memory
+    static constexpr bool SPLIT_OK_DUAL = 2 * BN * BM * 4 <= STAGES * STAGE_BYTES;
+    static constexpr bool SPLIT_OK_SINGLE = BN * BM * 4 <= STAGES * STAGE_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {16..256}
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -77,7 +81,7 @@ __device__ __forceinline__ void epilogue_apply(const GemmDev& p, int n, int t, f
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1) k_gemm_tc(const __grid_constant__ GemmDev p) {
+__global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(const __grid_constant__ GemmDev p) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -85,7 +89,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_gemm_tc(const __grid_consta
     uint64_t* empty = full + Cfg::STAGES;
     uint64_t* acc_full = empty + Cfg::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
-    int* s_flag = (int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
@@ -166,8 +169,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_gemm_tc(const __grid_consta
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        if (ok && n_iters > 0) {
-            if (p.splits == 1) {
+        const bool dual = p.kblocks[1] > 0;
+        if (p.splits == 1) {
+            if (ok && n_iters > 0) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     if (t0 + c0 >= p.T) break;
@@ -178,57 +182,70 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_gemm_tc(const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         epilogue_apply(p, n, t0 + c0 + j, has0 ? __uint_as_float(v0[j]) : 0.f,
-                                       has1 ? __uint_as_float(v1[j]) : 0.f, p.kblocks[1] > 0);
+                                       has1 ? __uint_as_float(v1[j]) : 0.f, dual);
                 }
-            } else {
-                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                float* mine = p.ws + ((size_t)tile * p.splits + blockIdx.z) * (size_t)(2 * BN * BM);
+            }
+        } else {
+            // split-K: park this CTA's partial tile in its own shared memory (the pipeline stages are
+            // free: every load was consumed by an MMA that has completed); layout [acc][column][row]
+            float* red = (float*)smem;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (t0 + c0 >= p.T) break;
-                    uint32_t v0[16], v1[16];
-                    if (has0) tmem_ld16(lane_addr + c0, v0);
-                    if (has1) tmem_ld16(lane_addr + BN + c0, v1);
-                    tc_wait_ld();
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= p.T) break;
+                uint32_t v0[16], v1[16];
+                const bool live = ok && n_iters > 0;
+                if (live && has0) tmem_ld16(lane_addr + c0, v0);
+                if (live && has1) tmem_ld16(lane_addr + BN + c0, v1);
+                tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        mine[(size_t)(c0 + j) * BM + row] = has0 ? __uint_as_float(v0[j]) : 0.f;
-                        if (p.kblocks[1] > 0) mine[(size_t)(BN + c0 + j) * BM + row] = has1 ? __uint_as_float(v1[j]) : 0.f;
-                    }
-                }
-            }
-        }
-        if (p.splits > 1) {
-            // ticket: the last split of this tile to get here reduces (bar.sync over the 4 epilogue warps)
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
-                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                int old = atomicAdd(&p.counters[tile], 1);
-                *s_flag = (old == p.splits - 1) ? 1 : 0;
-                if (old == p.splits - 1) p.counters[tile] = 0;  // ready for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*s_flag) {
-                __threadfence();
-                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                const float* base = p.ws + (size_t)tile * p.splits * (size_t)(2 * BN * BM);
-                const bool dual = p.kblocks[1] > 0;
-                for (int c = 0; c < BN; ++c) {
-                    if (t0 + c >= p.T) break;
-                    float a0 = 0.f, a1 = 0.f;
-                    for (int z = 0; z < p.splits; ++z) {
-                        const float* part = base + (size_t)z * (2 * BN * BM);
-                        a0 += __ldcg(part + (size_t)c * BM + row);
-                        if (dual) a1 += __ldcg(part + (size_t)(BN + c) * BM + row);
-                    }
-                    epilogue_apply(p, n, t0 + c, a0, a1, dual);
+                for (int j = 0; j < 16; ++j) {
+                    red[(size_t)(c0 + j) * BM + row] = (live && has0) ? __uint_as_float(v0[j]) : 0.f;
+                    if (dual) red[(size_t)(BN + c0 + j) * BM + row] = (live && has1) ? __uint_as_float(v1[j]) : 0.f;
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (p.splits > 1) {
+        // The splits of one output tile form a thread-block cluster (1,1,splits). After the cluster
+        // barrier every CTA sums, over all splits in rank order, the columns it owns (column % splits
+        // == rank) straight out of its peers' shared memory, and applies the epilogue. A second
+        // barrier keeps every CTA's shared memory alive until its peers have finished reading it.
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int q = warp & 3;
+            const int row = q * 32 + lane;
+            const int n = n0 + row;
+            const bool dual = p.kblocks[1] > 0;
+            const uint32_t rank = cluster_ctarank();
+            const uint32_t red_local = smem_u32(smem);
+            uint32_t peer[8];
+#pragma unroll
+            for (int z = 0; z < 8; ++z) peer[z] = (z < p.splits) ? map_shared_rank(red_local, (uint32_t)z) : 0u;
+            for (int c = (int)rank; c < BN; c += p.splits) {
+                if (t0 + c >= p.T) break;
+                float v0[8], v1[8];
+#pragma unroll
+                for (int z = 0; z < 8; ++z) {
+                    v0[z] = 0.f;
+                    v1[z] = 0.f;
+                    if (z < p.splits) {
+                        v0[z] = ld_shared_cluster_f32(peer[z] + (uint32_t)(((size_t)c * BM + row) * 4));
+                        if (dual) v1[z] = ld_shared_cluster_f32(peer[z] + (uint32_t)(((size_t)(BN + c) * BM + row) * 4));
+                    }
+                }
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int z = 0; z < 8; ++z) {
+                    a0 += v0[z];
+                    a1 += v1[z];
+                }
+                epilogue_apply(p, n, t0 + c, a0, a1, dual);
+            }
+        }
+        cluster_sync_all();
+    }
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
@@ -320,32 +337,37 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     p.alpha = c.alpha;
     p.out = c.out;
     p.ldo = c.ldo;
-    p.ws = ws.partials;
-    p.counters = ws.counters;
     p.status = ws.status;
     const int n_tiles = (c.N + BM - 1) / BM, t_tiles = (c.T + BN - 1) / BN;
     const int total_kb = p.kblocks[0] + p.kblocks[1];
+    const int tiles = n_tiles * t_tiles;
+    const bool dual = p.kblocks[1] > 0;
+    const bool split_ok = dual ? Cfg::SPLIT_OK_DUAL : Cfg::SPLIT_OK_SINGLE;
+    // K splits = cluster size (1, 2, 4 or 8): grow while all CTAs stay co-resident (two per SM for
+    // the decode tile sizes) and every split keeps at least two k-blocks
     int splits = 1;
     if (force_splits > 0) {
         splits = force_splits;
-    } else {
-        // enough CTAs to cover the SMs, at least 4 k-blocks of work per split
-        const int tiles = n_tiles * t_tiles;
-        if (tiles < ws.num_sms) {
-            splits = (ws.num_sms + tiles - 1) / tiles;
-            if (splits > total_kb / 4) splits = total_kb / 4;
-        }
+    } else if (split_ok) {
+        const int resident = ws.num_sms * ((BN <= 64) ? 2 : 1);
+        while (splits < 8 && tiles * splits * 2 <= resident && total_kb / (splits * 2) >= 2) splits *= 2;
     }
-    if (splits > total_kb) splits = total_kb;
-    if (splits < 1) splits = 1;
-    const size_t per_tile = (size_t)2 * BN * BM;
-    while (splits > 1 && ((size_t)n_tiles * t_tiles * splits * per_tile > ws.partial_floats ||
-                          n_tiles * t_tiles > ws.num_counters))
-        --splits;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return (int)cudaErrorInvalidValue;
+    if (splits > 1 && (!split_ok || splits > total_kb)) return (int)cudaErrorInvalidValue;
     p.splits = splits;
-    dim3 grid(n_tiles, t_tiles, splits);
-    k_gemm_tc<BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(p);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3(n_tiles, t_tiles, splits);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = splits > 1 ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, k_gemm_tc<BN>, p);
 }
 
 }  // namespace

@@ -87,6 +87,7 @@ _SIGS = {
     "tffn_session_launch_count": (ctypes.c_uint64, [_vp]),
     "tffn_session_stream": (_vp, [_vp]),
     "tffn_op_gemm": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "tffn_op_swiglu_bs1": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
     "tffn_op_wait_selftest": (_i, [_i]),
 }
 for _name, (_res, _args) in _SIGS.items():
@@ -334,6 +335,24 @@ def op_gemm(X: np.ndarray, W: np.ndarray, splits: int = 0, device: int = 0) -> n
     N = W.shape[0]
     out = np.empty((T, N), dtype=np.float32)
     _check(_L.tffn_op_gemm(device, X.ctypes.data, W.ctypes.data, out.ctypes.data, T, N, K, splits))
+    return out
+
+
+def pack_ffn(gate: np.ndarray, up: np.ndarray, down: np.ndarray) -> np.ndarray:
+    """gate, up [I,H], down [H,I] (bf16 bits) -> records [I][3][H]: gate row, up row, down column"""
+    return np.ascontiguousarray(np.stack([gate, up, down.T], axis=1))
+
+
+def op_swiglu_bs1(h, norm_w, packed_base, packed_expert=None, expert_scale=0.1, eps=1e-6, device: int = 0):
+    """fused batch-1 FFN kernel: bf16 bits in, new residual stream (bf16 bits) out"""
+    h = np.ascontiguousarray(h, dtype=np.uint16)
+    w = np.ascontiguousarray(norm_w, dtype=np.uint16)
+    pb = np.ascontiguousarray(packed_base, dtype=np.uint16)
+    pe = None if packed_expert is None else np.ascontiguousarray(packed_expert, dtype=np.uint16)
+    I, _, H = pb.shape
+    out = np.empty(H, dtype=np.uint16)
+    _check(_L.tffn_op_swiglu_bs1(device, h.ctypes.data, w.ctypes.data, pb.ctypes.data, _ptr(pe), expert_scale, eps, H, I,
+                                 out.ctypes.data))
     return out
 
 
