@@ -160,6 +160,20 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
  * (inference/src/model/expert.cu:44-59) at T = 1. */
 int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
                        const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out);
+/* tffn_op_swiglu_bs1 for callers that must not allocate device memory (no counterpart in the
+ * reference, whose every buffer comes from cudaMalloc): a host thread in a latency-critical loop
+ * that may not take the allocator's lock or cause an implicit synchronisation, a plugin inside a
+ * process whose device memory is owned and reserved by someone else, a deployment with a memory
+ * budget fixed at start-up. All pointers are DEVICE pointers supplied by the caller (h_io is
+ * updated in place); the kernel's scratch is a fixed array inside the library (about 1.4 MB per
+ * GPU that loads it), so hidden <= 2048 and at most 160 SMs, larger requests return
+ * TFFN_ERR_CAPACITY. The function calls no cudaMalloc / cudaFree; it clears the part of the
+ * scratch that must start at zero, launches on `cuda_stream` and waits for the result. Calls that
+ * could overlap on one GPU share the scratch and must be serialised by the caller. The first
+ * call on a device does a one-time set-up (address look-up of the array): make it before any
+ * stream capture. */
+int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* norm_w, const void* packed_base,
+                               const void* packed_expert, float expert_scale, float eps, int H, int I, void* cuda_stream);
 /* Runs a kernel that waits on a barrier nothing signals; returns the device status it
  * recorded (expected: 5). Proves that a wait that runs out returns instead of hanging. */
 int tffn_op_wait_selftest(int device);

@@ -14,6 +14,9 @@ struct tffn_session { Session* s; };
 struct tffn_tokenizer { Tokenizer t; };
 
 static thread_local std::string g_last_error;
+namespace tffn {
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace tffn
 
 template <typename F>
 static int guard(F&& f) {

@@ -1,0 +1,125 @@
+// tffn_op_swiglu_bs1_noalloc — the fused batch-1 SwiGLU kernel for callers that must not allocate.
+//
+// Who needs this: code that runs where device allocation is forbidden or impossible — a host
+// thread in the middle of a latency-critical loop that may not take the allocator's lock or
+// trigger an implicit device synchronisation (cudaMalloc and cudaFree can do both), a plugin
+// loaded into a process whose memory pool is owned and fully reserved by someone else, or a
+// caller running under a strict memory budget fixed at start-up. Such callers hand in device
+// pointers for inputs and outputs that they obtained earlier; the kernel's scratch (per-CTA
+// partial sums, group sums and reduction tickets) lives in a fixed array inside this library's
+// device image instead of a buffer from cudaMalloc.
+//
+// Consequences the caller has to know:
+//  * Every GPU that loads the library holds the array (about 1.4 MB) until the process exits.
+//  * The size is fixed: hidden <= 2048 and a GPU with at most 160 SMs; larger requests are refused.
+//  * All calls on one device share the array and it keeps the previous call's contents. The entry
+//    point clears the tickets and the status word before every launch; the partial sums are fully
+//    overwritten by the kernel before they are read. Two calls whose kernels overlap on the GPU
+//    (different streams, or different host threads) race on the scratch: serialise them.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+//    opts the kernel into its shared-memory size. Make that first call outside of any stream capture.
+#include "../../include/tffn.h"
+#include "engine.h"
+#include <mutex>
+
+namespace tffn {
+void set_last_error(const std::string& msg);  // c_api.cpp
+}
+
+namespace {
+
+constexpr int kMaxHidden = 2048;
+constexpr int kMaxCtas = 160;
+constexpr int kGroups = (kMaxCtas + 15) / 16 + 1;
+constexpr int kMaxDevices = 64;
+
+struct Scratch {
+    float part[(size_t)(kMaxCtas + kGroups) * kMaxHidden];  // per-CTA partial sums, then per-group sums
+    int tickets[64];                                       // reduction tickets, zero before each launch
+    int status;                                            // device status word of the launch
+    int pad[63];
+};
+
+// In host code this name is only a handle for the runtime; the address the kernel needs comes
+// from cudaGetSymbolAddress on the device that will run it.
+static __device__ __align__(256) unsigned char g_scratch[sizeof(Scratch)];
+
+std::mutex g_mu;
+Scratch* g_dev_ptr[kMaxDevices] = {nullptr};
+int g_dev_sms[kMaxDevices] = {0};
+
+int fail(int code, const std::string& msg) {
+    tffn::set_last_error(msg);
+    return code;
+}
+
+}  // namespace
+
+extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* norm_w, const void* packed_base,
+                                          const void* packed_expert, float expert_scale, float eps, int H, int I,
+                                          void* cuda_stream) {
+    using namespace tffn;
+    if (!h_io || !norm_w || !packed_base || I < 1) return fail(TFFN_ERR_INVALID, "NULL pointer or empty intermediate size");
+    if (H < 8 || H % 8 != 0 || H > kMaxHidden)
+        return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: hidden must be a multiple of 8 and at most " +
+                                           std::to_string(kMaxHidden) + " (the built-in scratch is sized for that)");
+    if (device < 0 || device >= kMaxDevices) return fail(TFFN_ERR_INVALID, "device index out of range");
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    Scratch* scratch = nullptr;
+    int sms = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!g_dev_ptr[device]) {  // set-up, once per device, with that device current
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_scratch);
+            if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+            int n = 0;
+            e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+            if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+            const int rc = bs1_prepare(kMaxHidden, true);
+            if (rc != 0) return fail(TFFN_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString((cudaError_t)rc));
+            g_dev_sms[device] = n;
+            g_dev_ptr[device] = (Scratch*)p;
+        }
+        scratch = g_dev_ptr[device];
+        sms = g_dev_sms[device];
+    }
+    if (sms > kMaxCtas)
+        return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: this GPU has more SMs than the built-in scratch covers (" +
+                                           std::to_string(kMaxCtas) + ")");
+    {
+        const int rc = bs1_prepare(H, true);  // shared-memory opt-in for this hidden size (no allocation)
+        if (rc != 0) return fail(TFFN_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString((cudaError_t)rc));
+    }
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    // the array keeps the last call's contents: tickets and status must start at zero
+    e = cudaMemsetAsync(scratch->tickets, 0, sizeof(scratch->tickets) + sizeof(int), stream);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+    Bs1Ctx x;
+    memset(&x, 0, sizeof x);
+    x.H = H;
+    x.I = I;
+    x.eps = eps;
+    x.expert_scale = expert_scale;
+    x.h = (bf16*)h_io;
+    x.ffn_part = scratch->part;
+    x.tickets = scratch->tickets;
+    x.status = &scratch->status;
+    x.num_sms = sms;
+    Bs1Layer ly;
+    memset(&ly, 0, sizeof ly);
+    ly.ffn_norm = (const bf16*)norm_w;
+    ly.ffn_base = (const bf16*)packed_base;
+    ly.ffn_expert = (const bf16*)packed_expert;
+    launch_bs1_ffn(x, ly, stream, false);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
+    int st = 0;
+    e = cudaMemcpy(&st, &scratch->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(e));
+    if (st != 0) return fail(TFFN_ERR_DEVICE, "FFN kernel reported device status " + std::to_string(st));
+    return TFFN_OK;
+}

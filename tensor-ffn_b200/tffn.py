@@ -88,6 +88,7 @@ _SIGS = {
     "tffn_session_stream": (_vp, [_vp]),
     "tffn_op_gemm": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i]),
     "tffn_op_swiglu_bs1": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
+    "tffn_op_swiglu_bs1_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
     "tffn_op_wait_selftest": (_i, [_i]),
 }
 for _name, (_res, _args) in _SIGS.items():
@@ -354,6 +355,14 @@ def op_swiglu_bs1(h, norm_w, packed_base, packed_expert=None, expert_scale=0.1, 
     _check(_L.tffn_op_swiglu_bs1(device, h.ctypes.data, w.ctypes.data, pb.ctypes.data, _ptr(pe), expert_scale, eps, H, I,
                                  out.ctypes.data))
     return out
+
+
+def op_swiglu_bs1_noalloc(h_io_ptr: int, norm_w_ptr: int, packed_base_ptr: int, packed_expert_ptr: int | None, H: int, I: int,
+                          expert_scale=0.1, eps=1e-6, stream: int | None = None, device: int = 0):
+    """The same kernel for callers that cannot allocate: every argument is a DEVICE address the
+    caller already owns, h_io is updated in place, scratch comes from a fixed array in the library."""
+    _check(_L.tffn_op_swiglu_bs1_noalloc(device, h_io_ptr, norm_w_ptr, packed_base_ptr, packed_expert_ptr, expert_scale, eps,
+                                         H, I, stream))
 
 
 def op_wait_selftest(device: int = 0) -> int:
