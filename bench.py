@@ -132,6 +132,28 @@ def kernel_bytes(cfg: dict, with_expert: bool, n_seqs: int, ctx: float) -> dict:
     return b
 
 
+def dp_sequence_ids(rank: int, seqs_per_rank: int) -> list[int]:
+    """Data-parallel sharding: rank r owns the global sequences [r*n, (r+1)*n); no sequence is shared
+    and nothing is exchanged on the data path."""
+    return list(range(rank * seqs_per_rank, (rank + 1) * seqs_per_rank))
+
+
+def dp_prompts(rank: int, seqs_per_rank: int, prompt_len: int):
+    import synth
+    ids = dp_sequence_ids(rank, seqs_per_rank)
+    return synth.prompts(len(ids), prompt_len, 1, first_seq=ids[0])
+
+
+def reduce_max(dist, x: float, device: str) -> float:
+    """max over ranks of a per-rank device time (the job is as slow as its slowest rank)"""
+    if dist is None:
+        return x
+    import torch
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def run_ours(a):
     import torch
     import synth
@@ -155,11 +177,7 @@ def run_ours(a):
         torch.cuda.synchronize()
 
     def max_over_ranks(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return reduce_max(dist, x, "cuda")
 
     if rank == 0:
         ensure_model(a.shape)
@@ -171,7 +189,8 @@ def run_ours(a):
     model = tffn.qwen_load(d, device=local)
     expert = tffn.checkpoint_load(ep, model, 0.1)
     sess = tffn.Session(model, expert, max_batch=n, max_seq=max_seq, stream=stream.cuda_stream)
-    prompts = synth.prompts(n, a.prompt, 1000 + rank)  # distinct sequences on every rank
+    sess.set_launch_mode(a.launch_mode)
+    prompts = dp_prompts(rank, n, a.prompt)  # distinct sequences on every rank
     prompt_list = [prompts[i] for i in range(n)]
 
     uuid = None
@@ -228,21 +247,23 @@ def run_ours(a):
                      "peak": peak, "unit": "GB/s", "frac": step_bytes / 1e9 / (ms / K / 1e3) / peak}
 
     # ---- end to end through the C ABI with host buffers (e2e)
-    sess.qwen_reset()
-    nxt, _ = sess.prefill(prompt_list)
-    for _ in range(W):
-        nxt, _ = sess.decode_step(nxt)
-    barrier()
-    e0.record(stream)
-    w0 = time.perf_counter()
-    for _ in range(K):
-        nxt, _ = sess.decode_step(nxt)  # host int32[n] in, host int32[n] out, every step
-    e1.record(stream)
-    barrier()
-    wall_ms = (time.perf_counter() - w0) * 1e3
-    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
-    e2e = {"value": world * n * K / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n * world,
-           "d2h_bytes_per_step": 4 * n * world, "ms_per_step": e2e_ms / K}
+    e2e = None
+    if not a.no_e2e:
+        sess.qwen_reset()
+        nxt, _ = sess.prefill(prompt_list)
+        for _ in range(W):
+            nxt, _ = sess.decode_step(nxt)
+        barrier()
+        e0.record(stream)
+        w0 = time.perf_counter()
+        for _ in range(K):
+            nxt, _ = sess.decode_step(nxt)  # host int32[n] in, host int32[n] out, every step
+        e1.record(stream)
+        barrier()
+        wall_ms = (time.perf_counter() - w0) * 1e3
+        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
+        e2e = {"value": world * n * K / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n * world,
+               "d2h_bytes_per_step": 4 * n * world, "ms_per_step": e2e_ms / K}
 
     # ---- batch 1 (configs[0]) on the same weights: 128-token prompt, greedy decode
     bs1 = None
@@ -380,6 +401,7 @@ def main():
     ap.add_argument("--bs1-steps", type=int, default=128)
     ap.add_argument("--launch-mode", type=int, default=2)
     ap.add_argument("--no-bs1", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-prompt", type=int, default=64)
     ap.add_argument("--cpu-tokens", type=int, default=128)

@@ -153,6 +153,13 @@ void* tffn_session_stream(const tffn_session* s);
  * fp32 out, host pointers); splits = 0 lets the launcher choose the K split.
  * Stands in for gemm_bf16 (inference/src/backend/cuda_ops.cu:18-29). */
 int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits);
+/* Same, and additionally returns 64 device timestamps (globaltimer, ns) per CTA in trace[trace_ctas*64]
+ * (CTA order: split-major, then token tile, then row tile): 0 start, 1 weight boxes requested,
+ * 2 dependency wait over, 3 last MMA issued, 4 accumulator complete, 5 epilogue done, 6 cluster
+ * barrier passed, 7 cluster reduction done, 8 end, 16+i pipeline stage i arrived. A profiling aid with
+ * no counterpart in the reference. */
+int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits,
+                       uint64_t* trace, int trace_ctas);
 /* The fused batch-1 SwiGLU kernel alone (host pointers, bf16 bits): h_out = bf16(h + FFN(rmsnorm(h)))
  * with FFN = base + expert_scale * expert (packed_expert may be NULL). packed_* use the record
  * layout [I][3][H] = gate row, up row, down column per intermediate index. Stands in for the FFN
@@ -160,6 +167,13 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
  * (inference/src/model/expert.cu:44-59) at T = 1. */
 int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
                        const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out);
+/* Same, and additionally returns 16 device timestamps (globaltimer, ns) per CTA of a second, warm
+ * launch in trace[trace_ctas*16] (trace_ctas >= SM count): 0 start, 1 RMSNorm done, 2 first record
+ * arrived, 3 last record consumed, 4 CTA partial written, 5 group ticket taken, 6 group fold done,
+ * 7 residual updated. A profiling aid with no counterpart in the reference. */
+int tffn_op_swiglu_bs1_trace(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
+                             const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out,
+                             uint64_t* trace, int trace_ctas);
 /* tffn_op_swiglu_bs1 for callers that must not allocate device memory (no counterpart in the
  * reference, whose every buffer comes from cudaMalloc): a host thread in a latency-critical loop
  * that may not take the allocator's lock or cause an implicit synchronisation, a plugin inside a

@@ -11,6 +11,7 @@
 // no spinning), always in split order, so the result does not depend on scheduling.
 #include "kernels.h"
 #include "ptx.cuh"
+#include "launch.h"
 
 namespace tffn {
 
@@ -69,53 +70,67 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
     bool bad = false;
 
-    // the trip count is uniform across the warp (shuffles below use the full mask); rows past
-    // the end of the range, or with a bad page id, are computed on zeros and then discarded
-    for (int base = c_begin; base < c_end; base += NG) {
-        const int tok = base + grp;
-        bool valid = tok < c_end;
-        int pg = 0;
-        if (valid) {
-            pg = __ldcg(bt + tok / kPageTokens);
-            if (pg < 0 || pg >= kv.num_pages) { bad = true; valid = false; }
+    // U rows per thread group and iteration: their page lookups and 16-byte K/V loads are all in
+    // flight before the first dot product, which hides the HBM latency that a one-row loop pays
+    // per row. The trip count is uniform across the warp (the shuffles use the full mask); rows past
+    // the end of the range, or with a bad page id, are computed on zeros and then discarded.
+    constexpr int U = 4;
+    for (int base = c_begin; base < c_end; base += NG * U) {
+        int pg[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int tok = base + u * NG + grp;
+            valid[u] = tok < c_end;
+            pg[u] = valid[u] ? __ldcg(bt + tok / kPageTokens) : 0;
         }
-        uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-        if (valid) {
-            const size_t off = (((size_t)pg * nkv + kvh) * kPageTokens + tok % kPageTokens) * HD + sub * 8;
-            kk = *(const uint4*)(kpool + off);
-            vv = *(const uint4*)(vpool + off);
-        }
-        const uint32_t ku[4] = {kk.x, kk.y, kk.z, kk.w};
-        float kf[8];
+        uint4 kk[U], vv[U];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { kf[2 * j] = bf16_lo(ku[j]); kf[2 * j + 1] = bf16_hi(ku[j]); }
-        float s[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float d = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) d += qr[g][j] * kf[j];
-            s[g] = d;
+        for (int u = 0; u < U; ++u) {
+            const int tok = base + u * NG + grp;
+            if (valid[u] && (pg[u] < 0 || pg[u] >= kv.num_pages)) { bad = true; valid[u] = false; }
+            kk[u] = make_uint4(0, 0, 0, 0);
+            vv[u] = make_uint4(0, 0, 0, 0);
+            if (valid[u]) {
+                const size_t off = (((size_t)pg[u] * nkv + kvh) * kPageTokens + tok % kPageTokens) * HD + sub * 8;
+                kk[u] = __ldcg((const uint4*)(kpool + off));
+                vv[u] = __ldcg((const uint4*)(vpool + off));
+            }
         }
 #pragma unroll
-        for (int o = LPT / 2; o > 0; o >>= 1)
+        for (int u = 0; u < U; ++u) {
+            const uint32_t ku[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+            float kf[8];
 #pragma unroll
-            for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-        if (!valid) continue;
-        const uint32_t vu[4] = {vv.x, vv.y, vv.z, vv.w};
-        float vf[8];
+            for (int j = 0; j < 4; ++j) { kf[2 * j] = bf16_lo(ku[j]); kf[2 * j + 1] = bf16_hi(ku[j]); }
+            float s[G];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { vf[2 * j] = bf16_lo(vu[j]); vf[2 * j + 1] = bf16_hi(vu[j]); }
+            for (int g = 0; g < G; ++g) {
+                float d = 0.f;
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float sc = s[g] * scale;
-            const float mn = fmaxf(m[g], sc);
-            const float corr = __expf(m[g] - mn);
-            const float p = __expf(sc - mn);
-            m[g] = mn;
-            l[g] = l[g] * corr + p;
+                for (int j = 0; j < 8; ++j) d += qr[g][j] * kf[j];
+                s[g] = d;
+            }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + p * vf[j];
+            for (int o = LPT / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+            if (!valid[u]) continue;
+            const uint32_t vu[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+            float vf[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { vf[2 * j] = bf16_lo(vu[j]); vf[2 * j + 1] = bf16_hi(vu[j]); }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float sc = s[g] * scale;
+                const float mn = fmaxf(m[g], sc);
+                const float corr = __expf(m[g] - mn);
+                const float p = __expf(sc - mn);
+                m[g] = mn;
+                l[g] = l[g] * corr + p;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + p * vf[j];
+            }
         }
     }
     if (bad) dev_fail(status, DEV_ERR_BOUNDS);
@@ -163,26 +178,43 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     const float* parts = ws + (size_t)unit * splits * (size_t)(G * (HD + 2));
     for (int idx = threadIdx.x; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx % HD;
-        float M = kNegBig;
-        for (int z = 0; z < splits; ++z) M = fmaxf(M, __ldcg(parts + (size_t)z * G * (HD + 2) + g * (HD + 2)));
-        float L = 0.f, A = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float* pz = parts + (size_t)z * G * (HD + 2) + g * (HD + 2);
-            const float w = __expf(__ldcg(pz) - M);
-            L += __ldcg(pz + 1) * w;
-            A += __ldcg(pz + 2 + d) * w;
+        float M = kNegBig, L = 0.f, A = 0.f;
+        // 8 splits per round with all loads in flight; a running maximum keeps the merge exact
+        for (int z0 = 0; z0 < splits; z0 += 8) {
+            float mz[8], lz[8], az[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool live = z0 + j < splits;
+                const float* pz = parts + (size_t)(live ? z0 + j : 0) * G * (HD + 2) + g * (HD + 2);
+                mz[j] = live ? __ldcg(pz) : kNegBig;
+                lz[j] = live ? __ldcg(pz + 1) : 0.f;
+                az[j] = live ? __ldcg(pz + 2 + d) : 0.f;
+            }
+            float Mn = M;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, mz[j]);
+            const float corr = __expf(M - Mn);
+            L *= corr;
+            A *= corr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = __expf(mz[j] - Mn);
+                L += lz[j] * w;
+                A += az[j] * w;
+            }
+            M = Mn;
         }
         ctx[((size_t)t * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
     }
 }
 
 template <int HD>
-bool dispatch_g(int G, dim3 grid, cudaStream_t s, const float* q, const KvView& kv, int layer, const int* tok_seq,
+bool dispatch_g(int G, dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                 const int* tok_pos, bf16* ctx, int nh, int splits, float* ws, int* counters, int* status) {
 #define TFFN_ATTN_CASE(GG)                                                                                          \
     case GG:                                                                                                       \
-        k_attn_decode<HD, GG><<<grid, kAttnThreads, 0, s>>>(q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws,   \
-                                                            counters, status);                                    \
+        launch_k(k_attn_decode<HD, GG>, grid, dim3(kAttnThreads), 0, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, \
+                 splits, ws, counters, status);                                                                   \
         return true;
     switch (G) {
         TFFN_ATTN_CASE(1)
@@ -216,14 +248,14 @@ int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWork
 }
 
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
-                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s) {
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl) {
     const int G = nh / kv.nkv;
     const int units = T * kv.nkv;
     const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
     dim3 grid(units, splits);
     bool ok = false;
-    if (kv.hd == 64) ok = dispatch_g<64>(G, grid, s, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
-    else if (kv.hd == 128) ok = dispatch_g<128>(G, grid, s, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
+    if (kv.hd == 64) ok = dispatch_g<64>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
+    else if (kv.hd == 128) ok = dispatch_g<128>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
     (void)ok;
 }
 

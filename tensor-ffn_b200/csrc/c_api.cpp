@@ -301,6 +301,11 @@ uint64_t tffn_session_launch_count(const tffn_session* s) { return s ? s->s->lau
 void* tffn_session_stream(const tffn_session* s) { return s ? (void*)s->s->stream() : nullptr; }
 
 int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits) {
+    return tffn_op_gemm_trace(device, X, W, out, T, N, K, splits, nullptr, 0);
+}
+
+int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits,
+                       uint64_t* trace, int trace_ctas) {
     return guard([&] {
         need(X && W && out && T > 0 && N > 0 && K > 0 && K % 8 == 0, "bad GEMM arguments");
         int ndev = 0;
@@ -309,7 +314,8 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
         cudaDeviceProp prop;
         TFFN_CUDA(cudaGetDeviceProperties(&prop, device));
         const int rows = T < 256 ? 256 : T;
-        DeviceBuffer dx, dw, dout, part, cnt, status;
+        DeviceBuffer dx, dw, dout, part, cnt, status, dtrace;
+        if (trace && trace_ctas > 0) dtrace.alloc((size_t)trace_ctas * 64 * 8);
         dx.alloc((size_t)rows * K * 2);
         dw.alloc((size_t)N * K * 2);
         dout.alloc((size_t)T * N * 4);
@@ -322,6 +328,12 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
         memset(&g, 0, sizeof g);
         g.op[0] = {dw.as<bf16>(), K, dx.as<bf16>(), K, K};
         g.N = N; g.T = T; g.mode = GEMM_STORE_F32; g.alpha = 1.f; g.out = dout.p; g.ldo = N; g.x_rows_alloc = rows;
+        if (trace && trace_ctas > 0) {
+            const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+            const long long ctas = (long long)((N + 127) / 128) * ((T + bn - 1) / bn) * (splits > 0 ? splits : 8);
+            if (ctas > trace_ctas) throw Error(kErrInvalid, "trace buffer too small for this grid");
+            g.trace = dtrace.as<unsigned long long>();
+        }
         cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
         GemmWorkspace ws{part.as<float>(), part.bytes / 4, cnt.as<int>(), 8192, status.as<int>(), prop.multiProcessorCount};
         int rc = launch_gemm(g, ws, 0, splits);
@@ -332,11 +344,18 @@ int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, i
         TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
         if (st) throw Error(kErrDevice, "GEMM kernel reported device status " + std::to_string(st));
         TFFN_CUDA(cudaMemcpy(out, dout.p, (size_t)T * N * 4, cudaMemcpyDeviceToHost));
+        if (g.trace) TFFN_CUDA(cudaMemcpy(trace, dtrace.p, (size_t)trace_ctas * 64 * 8, cudaMemcpyDeviceToHost));
     });
 }
 
 int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
                        const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out) {
+    return tffn_op_swiglu_bs1_trace(device, h_in, norm_w, packed_base, packed_expert, expert_scale, eps, H, I, h_out, nullptr, 0);
+}
+
+int tffn_op_swiglu_bs1_trace(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
+                             const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out,
+                             uint64_t* trace, int trace_ctas) {
     return guard([&] {
         need(h_in && norm_w && packed_base && h_out && H > 0 && I > 0, "bad arguments");
         int ndev = 0;
@@ -365,16 +384,28 @@ int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w,
         x.H = H; x.I = I; x.eps = eps; x.expert_scale = expert_scale;
         x.h = dh.as<bf16>(); x.ffn_part = part.as<float>(); x.tickets = tickets.as<int>(); x.status = status.as<int>();
         x.num_sms = prop.multiProcessorCount;
+        DeviceBuffer dtrace;
+        if (trace && trace_ctas >= prop.multiProcessorCount) {
+            dtrace.alloc((size_t)trace_ctas * 16 * 8);
+            x.trace = dtrace.as<unsigned long long>();
+        }
         Bs1Layer ly;
         memset(&ly, 0, sizeof ly);
         ly.ffn_norm = dw.as<bf16>(); ly.ffn_base = db.as<bf16>(); ly.ffn_expert = packed_expert ? de.as<bf16>() : nullptr;
         launch_bs1_ffn(x, ly, 0, false);
+        if (x.trace) {  // a second, warm launch is the one whose timestamps are returned
+            TFFN_CUDA(cudaDeviceSynchronize());
+            TFFN_CUDA(cudaMemcpy(dh.p, h_in, (size_t)H * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemset(dtrace.p, 0, dtrace.bytes));
+            launch_bs1_ffn(x, ly, 0, false);
+        }
         TFFN_CUDA(cudaGetLastError());
         TFFN_CUDA(cudaDeviceSynchronize());
         int st = 0;
         TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
         if (st) throw Error(kErrDevice, "FFN kernel reported device status " + std::to_string(st));
         TFFN_CUDA(cudaMemcpy(h_out, dh.p, (size_t)H * 2, cudaMemcpyDeviceToHost));
+        if (x.trace) TFFN_CUDA(cudaMemcpy(trace, dtrace.p, (size_t)trace_ctas * 16 * 8, cudaMemcpyDeviceToHost));
     });
 }
 

@@ -18,12 +18,24 @@
 // Rounding points follow inference/src/model/qwen.cu:291-458 (see each kernel).
 #include "kernels.h"
 #include "ptx.cuh"
+#include "launch.h"
 
 namespace tffn {
 
 namespace {
 
-constexpr int kRowWarps = 4;  // warps per CTA in the row kernels (qkv, oproj)
+constexpr int kRowWarps = 4;
+
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// optional per-CTA phase timestamps (Bs1Ctx::trace, 16 u64 per CTA)
+#define BS1_TRACE(c, slot)                                                         \
+    do {                                                                           \
+        if ((c).trace) (c).trace[(size_t)blockIdx.x * 16 + (slot)] = gtime_ns(); \
+    } while (0)  // warps per CTA in the row kernels (qkv, oproj)
 
 // lane `lane` owns the 16-byte chunks lane, lane+32, ... of a row of H bf16 (H % 8 == 0)
 template <int NCH>
@@ -276,6 +288,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
     }
     __syncthreads();
     pdl_launch_dependents();
+    if (threadIdx.x == 0) BS1_TRACE(c, 0);
 
     if (warp == kFfnWarps) {
         // producer: the weights do not depend on the previous kernel, so no griddepcontrol.wait here
@@ -299,6 +312,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
     pdl_wait();
     RowRegs<NCH> xn;
     rmsnorm_regs<NCH>(xn, c.h, ly.ffn_norm, H, c.eps, lane);
+    if (threadIdx.x == 0) BS1_TRACE(c, 1);
     float acc[NCH * 8];
 #pragma unroll
     for (int j = 0; j < NCH * 8; ++j) acc[j] = 0.f;
@@ -309,6 +323,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         const uint32_t ph = (uint32_t)(r / L.stages) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, c.status, DEV_ERR_FULL_WAIT));
         if (!ok) break;
+        if (threadIdx.x == 0 && r == 0) BS1_TRACE(c, 2);
         const uint8_t* st = ring + (size_t)s * L.stage_bytes;
         RowRegs<NCH> wg, wu;
         load_row_smem<NCH>(wg, st, H, lane);
@@ -355,6 +370,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
+    if (threadIdx.x == 0) BS1_TRACE(c, 3);
     // fold the consumer warps of this CTA (fixed order); the partial sums reuse the ring, so
     // every consumer must be done reading it first
     constexpr int NT = kFfnWarps * 32;
@@ -377,6 +393,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         for (int w = 0; w < kFfnWarps; ++w) s += part[(size_t)w * H + col];
         my_part[col] = s;
     }
+    if (threadIdx.x == 0) BS1_TRACE(c, 4);
     // level 1: last CTA of the group folds the group's partials
     const int ngroups = (G + kFfnGroup - 1) / kFfnGroup;
     const int grp = blockIdx.x / kFfnGroup;
@@ -390,14 +407,21 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         *s_flag = last;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
+    if (threadIdx.x == 0) BS1_TRACE(c, 5);
     if (!*s_flag) return;
     __threadfence();
     float* gpart = c.ffn_part + (size_t)(G + grp) * H;
     for (int col = threadIdx.x; col < H; col += NT) {
+        float v[kFfnGroup];
+#pragma unroll
+        for (int b = 0; b < kFfnGroup; ++b)  // all loads in flight together, summed in CTA order below
+            v[b] = (g_begin + b < g_end) ? __ldcg(c.ffn_part + (size_t)(g_begin + b) * H + col) : 0.f;
         float s = 0.f;
-        for (int b = g_begin; b < g_end; ++b) s += __ldcg(c.ffn_part + (size_t)b * H + col);
+#pragma unroll
+        for (int b = 0; b < kFfnGroup; ++b) s += v[b];
         gpart[col] = s;
     }
+    if (threadIdx.x == 0) BS1_TRACE(c, 6);
     // level 2: last group folds the group sums into the residual stream
     __threadfence();
     asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
@@ -412,9 +436,16 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
     __threadfence();
     for (int col = threadIdx.x; col < H; col += NT) {
         float s = 0.f;
-        for (int g2 = 0; g2 < ngroups; ++g2) s += __ldcg(c.ffn_part + (size_t)(G + g2) * H + col);
+        for (int g0 = 0; g0 < ngroups; g0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int b = 0; b < 16; ++b) v[b] = (g0 + b < ngroups) ? __ldcg(c.ffn_part + (size_t)(G + g0 + b) * H + col) : 0.f;
+#pragma unroll
+            for (int b = 0; b < 16; ++b) s += v[b];
+        }
         c.h[col] = __float2bfloat16_rn(ld_bf16_cg(c.h + col) + s);
     }
+    if (threadIdx.x == 0) BS1_TRACE(c, 7);
 }
 
 // ------------------------------------------------------------------------------------------ LM head + argmax
@@ -566,22 +597,6 @@ size_t bs1_ffn_part_floats(int H, int num_sms) {
 
 namespace {
 
-template <typename Kern, typename... Args>
-void launch_pdl(Kern k, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
-    cudaLaunchConfig_t cfg;
-    cfg = cudaLaunchConfig_t{};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, k, args...);
-}
-
 inline int nch_of(int H) { return (H / 8 + 31) / 32; }
 
 }  // namespace
@@ -616,24 +631,24 @@ void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvVi
                     cudaStream_t s, bool pdl) {
     const int units = (c.nh + 2 * c.nkv) * (c.hd / 2);
     dim3 grid((units + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
-    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_qkv<NCH>, grid, block, 0, s, pdl, c, ly, embed, kv, layer, (int)first));
+    TFFN_NCH_SWITCH(c.H, launch_k(k_bs1_qkv<NCH>, grid, block, 0, s, pdl, c, ly, embed, kv, layer, (int)first));
 }
 void launch_bs1_oproj(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl) {
     dim3 grid((c.H + kRowWarps * 2 - 1) / (kRowWarps * 2)), block(kRowWarps * 32);
-    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_oproj<NCH>, grid, block, 0, s, pdl, c, ly));
+    TFFN_NCH_SWITCH(c.H, launch_k(k_bs1_oproj<NCH>, grid, block, 0, s, pdl, c, ly));
 }
 void launch_bs1_ffn(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl) {
     const FfnSmem L = ffn_smem_layout(c.H, ly.ffn_expert != nullptr);
     int G = c.num_sms < c.I ? c.num_sms : c.I;
     dim3 grid(G), block(kFfnThreads);
-    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_ffn<NCH>, grid, block, L.total, s, pdl, c, ly));
+    TFFN_NCH_SWITCH(c.H, launch_k(k_bs1_ffn<NCH>, grid, block, L.total, s, pdl, c, ly));
 }
 void launch_bs1_lmhead(const Bs1Ctx& c, const bf16* final_norm, const bf16* lm_head, cudaStream_t s, bool pdl) {
     const LmSmem L = lm_smem_layout(c.H);
     int G = c.num_sms;
     if (G > c.V) G = c.V;
     dim3 grid(G), block(kLmThreads);
-    TFFN_NCH_SWITCH(c.H, launch_pdl(k_bs1_lmhead<NCH>, grid, block, L.total, s, pdl, c, final_norm, lm_head));
+    TFFN_NCH_SWITCH(c.H, launch_k(k_bs1_lmhead<NCH>, grid, block, L.total, s, pdl, c, final_norm, lm_head));
 }
 
 }  // namespace tffn

@@ -470,7 +470,9 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     const int* tok_pos = decode ? seq_len_dev_.as<int>() : tok_pos_.as<int>();
     int* status = status_.as<int>();
     const GemmWorkspace gws = gemm_ws();
-    auto gemm = [&](const GemmCall& call, int cls) {
+    const bool pdl = launch_mode_ >= 1 && !profile_;
+    auto gemm = [&](GemmCall& call, int cls) {
+        call.pdl = pdl;
         prof_begin(cls);
         int rc = launch_gemm(call, gws, stream_);
         prof_end();
@@ -479,35 +481,44 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         launches_++;
     };
     prof_begin(KC_EMBED);
-    launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_);
+    launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_, false);
     prof_end();
     launches_++;
     for (int l = 0; l < c.num_layers; ++l) {
         const LayerWeights& ly = m_->layers[l];
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
         prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
         g.x_rows_alloc = cap_tokens_;
         g.T = T;
         g.alpha = 1.f;
-        // q|k|v rows in one GEMM, fp32 out
+        // q|k|v rows in one GEMM; bias, RoPE and the page writes happen in its epilogue
+        const bf16* b = ly.has_bias ? ly.bqkv.as<bf16>() : nullptr;
+        GemmQkvEpilogue qe;
+        qe.bias = b;
+        qe.rope_cos = rope_cos_.as<float>();
+        qe.rope_sin = rope_sin_.as<float>();
+        qe.tok_seq = tok_seq;
+        qe.tok_pos = tok_pos;
+        qe.q_out = q_.as<float>();
+        qe.kv = kv_;
+        qe.layer = l;
+        qe.nh = nh;
+        qe.max_pos = max_seq_;
         g.op[0] = {ly.wqkv.as<bf16>(), H, xn_.as<bf16>(), H, H};
         g.op[1] = {nullptr, 0, nullptr, 0, 0};
         g.N = nqkv;
-        g.mode = GEMM_STORE_F32;
-        g.out = qkv_.p;
+        g.mode = GEMM_QKV;
+        g.qkv = &qe;
+        g.out = nullptr;
         g.ldo = nqkv;
         gemm(g, KC_GEMM_QKV);
-        const bf16* b = ly.has_bias ? ly.bqkv.as<bf16>() : nullptr;
-        prof_begin(KC_QKV_POST);
-        launch_qkv_post(qkv_.as<float>(), b, b ? b + nh * hd : nullptr, b ? b + (nh + nkv) * hd : nullptr, rope_cos_.as<float>(),
-                        rope_sin_.as<float>(), tok_seq, tok_pos, q_.as<float>(), kv_, l, T, nh, max_seq_, status, stream_);
-        prof_end();
+        g.qkv = nullptr;
         prof_begin(KC_ATTENTION);
         launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
-                         status, stream_);
+                         status, stream_, pdl);
         prof_end();
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
@@ -517,22 +528,28 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.ldo = H;
         gemm(g, KC_GEMM_OPROJ);
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_);
+        launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
         prof_end();
-        launches_ += 4;
-        // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records
-        auto swiglu = [&](const FfnWeights& f, bf16* act) {
-            const bf16* rec = f.packed.as<bf16>();
+        launches_ += 3;
+        // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records; the expert's
+        // gate|up rides in the same launch as a second, independent problem
+        {
+            const bf16* rec = ly.ffn.packed.as<bf16>();
             g.op[0] = {rec, (int64_t)3 * H, xn_.as<bf16>(), H, H};
             g.op[1] = {rec + H, (int64_t)3 * H, xn_.as<bf16>(), H, H};
             g.N = I;
             g.mode = GEMM_SWIGLU;
-            g.out = act;
+            g.out = act_b_.p;
             g.ldo = I;
+            if (e_) {
+                const bf16* erec = e_->layers[l].packed.as<bf16>();
+                g.op2[0] = {erec, (int64_t)3 * H, xn_.as<bf16>(), H, H};
+                g.op2[1] = {erec + H, (int64_t)3 * H, xn_.as<bf16>(), H, H};
+                g.out2 = act_e_.p;
+            }
             gemm(g, KC_GEMM_GATEUP);
-        };
-        swiglu(ly.ffn, act_b_.as<bf16>());
-        if (e_) swiglu(e_->layers[l], act_e_.as<bf16>());
+            g.out2 = nullptr;
+        }
         // down projections of base and expert into two accumulators, summed in fp32, + residual
         g.op[0] = {ly.ffn.down.as<bf16>(), I, act_b_.as<bf16>(), I, I};
         if (e_) {
@@ -559,7 +576,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     if (n_logit_rows > 0) {
         const int* rows = logit_rows_are_all ? nullptr : row_idx_.as<int>();
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_);
+        launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_, pdl);
         prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
@@ -573,7 +590,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.ldo = V;
         gemm(g, KC_GEMM_LMHEAD);
         prof_begin(KC_ARGMAX);
-        launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_);
+        launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_, pdl);
         prof_end();
         launches_ += 2;
     }
@@ -628,7 +645,7 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
         prof_end();
         prof_begin(KC_ATTENTION);
         launch_attention(x.q, kv_, l, identity_.as<int>(), seq_len_dev_.as<int>(), x.ctx, 1, c.num_heads, max_seq_, attn_ws(),
-                         m_->num_sms, status_.as<int>(), stream_);
+                         m_->num_sms, status_.as<int>(), stream_, pdl);
         prof_end();
         prof_begin(KC_BS1_OPROJ);
         launch_bs1_oproj(x, ly, stream_, pdl);

@@ -31,53 +31,155 @@ namespace {
 constexpr int BM = 128;  // weight rows per tile
 constexpr int BK = 64;   // K elements per stage (128 bytes of bf16)
 constexpr int kGemmThreads = 192;
+constexpr int kMaxSplits = 16;  // cluster size; above 8 needs the non-portable opt-in (gemm_prepare)
 
 struct GemmDev {
-    CUtensorMap tmW[2];
-    CUtensorMap tmX[2];
+    CUtensorMap tmW[4];  // [problem * 2 + operand pair]
+    CUtensorMap tmX[4];
     int kblocks[2];
-    int N, T, splits, mode;
+    int N, T, splits, mode, t_tiles, stages;
+    int tile_n;          // output indices per tile: 128, or 64 for GEMM_SWIGLU (64 gate rows + 64 up rows per tile)
     float alpha;
-    void* out;
+    void* out[2];        // per problem
     long long ldo;
     int* status;
+    GemmQkvEpilogue qkv;  // GEMM_QKV only
+    unsigned long long* trace;  // optional: 64 timestamps (ns) per CTA, see GemmCall::trace
 };
+
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TFFN_TRACE(slot)                                                                                            \
+    do {                                                                                                            \
+        if (p.trace) p.trace[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 64 + (slot)] = gtime_ns(); \
+    } while (0)
 
 template <int BN>
 struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    // BN <= 64 (decode): 4 stages keep a CTA under half an SM's shared memory, so two CTAs (or two
-    // tiles' splits) are resident per SM and the weight stream has 2 x 64 KB in flight per SM
-    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 4);
-    // split-K parks [accs][BN][128] fp32 partials in the stage memory
-    static constexpr bool SPLIT_OK_DUAL = 2 * BN * BM * 4 <= STAGES * STAGE_BYTES;
-    static constexpr bool SPLIT_OK_SINGLE = BN * BM * 4 <= STAGES * STAGE_BYTES;
-    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {16..256}
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    // The ring depth is chosen at launch. A grid of at most one CTA per SM gets the deepest ring
+    // that fits (about 190 KB in flight per SM: the HBM latency under load is several microseconds,
+    // so the bytes in flight bound the stream); a larger grid of decode-sized tiles gets 4 stages
+    // so that two CTAs share an SM.
+    static constexpr int MAX_STAGES = (196 * 1024 / STAGE_BYTES) > 10 ? 10 : (196 * 1024 / STAGE_BYTES);
+    static constexpr int SHARED_STAGES = (BN <= 64) ? 4 : MAX_STAGES;
+    // the epilogue parks one fp32 plane [BN][128] in the (by then idle) stage memory
+    static_assert(BN * BM * 4 <= SHARED_STAGES * STAGE_BYTES, "plane must fit the smallest ring");
+    static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/; }
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulators, power of two
 };
 
-__device__ __forceinline__ void epilogue_apply(const GemmDev& p, int n, int t, float v0, float v1, bool has1) {
-    if (n >= p.N || t >= p.T) return;
-    size_t o = (size_t)t * (size_t)p.ldo + n;
+// ---------------------------------------------------------------------------------------------
+// Finalisation of 4 consecutive rows (n .. n+3) of one token column: the epilogues of all modes.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d) {
+    return make_uint2((uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16),
+                      (uint32_t)bf16_bits(c) | ((uint32_t)bf16_bits(d) << 16));
+}
+
+// GEMM_QKV: round to bf16, add the bias in bf16 (k_add_bias, inference/src/model/qwen.cu:223-226),
+// rotate q and k in fp32 at the token's position (k_rope, qwen.cu:232-244) — the RoPE partner rows
+// (i <-> i + hd/2) sit hd/8 lanes away in the same warp, because a warp holds all 128 rows of a
+// column — keep q in fp32, write k (rounded after the rotation) and v as bf16 into the
+// sequence's page (qwen.cu:339-346). Every lane of the warp must call it (shuffles).
+__device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, float4 v, int lane) {
+    const GemmQkvEpilogue& e = p.qkv;
+    const int hd = e.kv.hd, half = hd >> 1;
+    const int d = n % hd;  // tiles start at multiples of 128 and hd divides 128
+    const bool in_range = n < p.N;
+    float x[4] = {bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w)};
+    if (e.bias && in_range) {
+        const uint2 b = *(const uint2*)(e.bias + n);
+        x[0] = bf16_round(x[0] + bf16_lo(b.x));
+        x[1] = bf16_round(x[1] + bf16_hi(b.x));
+        x[2] = bf16_round(x[2] + bf16_lo(b.y));
+        x[3] = bf16_round(x[3] + bf16_hi(b.y));
+    }
+    float xp[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xp[j] = __shfl_xor_sync(0xffffffffu, x[j], hd >> 3);
+    (void)lane;
+    if (!in_range) return;
+    const int pos = __ldcg(e.tok_pos + t);
+    if (pos < 0 || pos >= e.max_pos) {
+        dev_fail(p.status, DEV_ERR_BOUNDS);
+        return;
+    }
+    const int nq = e.nh * hd, nk = e.kv.nkv * hd;
+    const int kind = n < nq ? 0 : (n < nq + nk ? 1 : 2);
+    float o[4] = {x[0], x[1], x[2], x[3]};
+    if (kind != 2) {
+        const int i = d % half;
+        const float4 c = *(const float4*)(e.rope_cos + (size_t)pos * half + i);
+        const float4 s = *(const float4*)(e.rope_sin + (size_t)pos * half + i);
+        const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = d < half ? x[j] * cs[j] - xp[j] * sn[j] : xp[j] * sn[j] + x[j] * cs[j];
+    }
+    if (kind == 0) {
+        *(float4*)(e.q_out + (size_t)t * nq + n) = make_float4(o[0], o[1], o[2], o[3]);
+        return;
+    }
+    const int head = kind == 1 ? (n - nq) / hd : (n - nq - nk) / hd;
+    const int seq = __ldcg(e.tok_seq + t);
+    const int pg = __ldcg(e.kv.block_table + (size_t)seq * e.kv.max_pages_per_seq + pos / kPageTokens);
+    if (pg < 0 || pg >= e.kv.num_pages) {
+        dev_fail(p.status, DEV_ERR_BOUNDS);
+        return;
+    }
+    bf16* pool = (kind == 1 ? e.kv.k_pool : e.kv.v_pool) + (size_t)e.layer * e.kv.layer_stride;
+    bf16* dst = pool + (((size_t)pg * e.kv.nkv + head) * kPageTokens + pos % kPageTokens) * hd + d;
+    *(uint2*)dst = pack_bf16x4(o[0], o[1], o[2], o[3]);
+}
+
+// STORE / RESIDUAL / SWIGLU (the SwiGLU value was formed before parking)
+__device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int n, int t, float4 v) {
+    if (n >= p.N) return;
+    const size_t o = (size_t)t * (size_t)p.ldo + n;
+    const bool vec = (n + 3 < p.N) && ((p.ldo & 3) == 0);
+    const float f[4] = {v.x, v.y, v.z, v.w};
     switch (p.mode) {
         case GEMM_STORE_F32:
-            ((float*)p.out)[o] = has1 ? v0 + p.alpha * v1 : v0;
-            break;
-        case GEMM_STORE_BF16:
-            ((bf16*)p.out)[o] = __float2bfloat16_rn(has1 ? v0 + p.alpha * v1 : v0);
+            if (vec) {
+                *(float4*)((float*)out + o) = v;
+            } else {
+                for (int j = 0; j < 4 && n + j < p.N; ++j) ((float*)out)[o + j] = f[j];
+            }
             break;
         case GEMM_RESIDUAL: {
-            bf16* h = (bf16*)p.out;
-            float d = has1 ? v0 + p.alpha * v1 : v0;
-            h[o] = __float2bfloat16_rn(__bfloat162float(h[o]) + d);
+            // h = bf16(float(h) + sum) (k_add_fp32_to_bf16, qwen.cu:282-285); h is read through L2
+            bf16* h = (bf16*)out;
+            if (vec) {
+                const uint2 old = __ldcg((const uint2*)(h + o));
+                *(uint2*)(h + o) = pack_bf16x4(bf16_lo(old.x) + f[0], bf16_hi(old.x) + f[1], bf16_lo(old.y) + f[2],
+                                               bf16_hi(old.y) + f[3]);
+            } else {
+                for (int j = 0; j < 4 && n + j < p.N; ++j) {
+                    const float old = __uint_as_float((uint32_t)__ldcg((const unsigned short*)(h + o + j)) << 16);
+                    h[o + j] = __float2bfloat16_rn(old + f[j]);
+                }
+            }
             break;
         }
-        case GEMM_SWIGLU:
-            ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul_bf16(v0, v1));
+        default:  // GEMM_STORE_BF16, GEMM_SWIGLU
+            if (vec) {
+                *(uint2*)((bf16*)out + o) = pack_bf16x4(f[0], f[1], f[2], f[3]);
+            } else {
+                for (int j = 0; j < 4 && n + j < p.N; ++j) ((bf16*)out)[o + j] = __float2bfloat16_rn(f[j]);
+            }
             break;
     }
+}
+
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 
 template <int BN>
@@ -85,22 +187,28 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    uint64_t* empty = full + Cfg::STAGES;
-    uint64_t* acc_full = empty + Cfg::STAGES;
+    const int STAGES = p.stages;
+    uint64_t* full = (uint64_t*)(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+    const int prob = blockIdx.y / p.t_tiles;  // independent problems (base / expert gate-up) share a launch
+    const int n0 = blockIdx.x * p.tile_n, t0 = (blockIdx.y % p.t_tiles) * BN;
+    const bool halves = p.mode == GEMM_SWIGLU;  // A tile = 64 gate rows over 64 up rows, one accumulator
+    void* const out = p.out[prob];
     const int total_kb = p.kblocks[0] + p.kblocks[1];
     const int kb_begin = (int)(((long long)blockIdx.z * total_kb) / p.splits);
     const int kb_end = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
     const int n_iters = kb_end - kb_begin;
     const bool has0 = kb_begin < p.kblocks[0] && n_iters > 0;
     const bool has1 = kb_end > p.kblocks[0] && p.kblocks[1] > 0 && n_iters > 0;
+    constexpr uint32_t tmem_cols = Cfg::TMEM_COLS;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) {
+        TFFN_TRACE(0);
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -108,21 +216,46 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_alloc(tmem_slot, tmem_cols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
-            prefetch_tmap(&p.tmW[0]);
-            prefetch_tmap(&p.tmX[0]);
-            for (int it = 0; it < n_iters; ++it) {
-                const int s = it % Cfg::STAGES;
-                const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+            prefetch_tmap(&p.tmW[prob * 2]);
+            prefetch_tmap(&p.tmX[prob * 2]);
+            // Weights do not depend on the previous kernel: the first ring of weight boxes is
+            // requested before griddepcontrol.wait, the activation boxes after it.
+            const int pre = n_iters < STAGES ? n_iters : STAGES;
+            for (int it = 0; it < pre; ++it) {
+                const int i = kb_begin + it;
+                const int seg = i >= p.kblocks[0] ? 1 : 0;
+                const int kb = seg ? i - p.kblocks[0] : i;
+                mbar_arrive_expect_tx(&full[it], Cfg::STAGE_BYTES);
+                if (halves) {
+                    tma_load_2d(smem + it * Cfg::STAGE_BYTES, &p.tmW[prob * 2], kb * BK, n0, &full[it]);
+                    tma_load_2d(smem + it * Cfg::STAGE_BYTES + Cfg::A_BYTES / 2, &p.tmW[prob * 2 + 1], kb * BK, n0, &full[it]);
+                } else {
+                    tma_load_2d(smem + it * Cfg::STAGE_BYTES, &p.tmW[prob * 2 + seg], kb * BK, n0, &full[it]);
+                }
+            }
+            TFFN_TRACE(1);
+            pdl_wait();
+            TFFN_TRACE(2);
+            for (int it = 0; it < pre; ++it) {
+                const int i = kb_begin + it;
+                const int seg = i >= p.kblocks[0] ? 1 : 0;
+                const int kb = seg ? i - p.kblocks[0] : i;
+                tma_load_2d(smem + it * Cfg::STAGE_BYTES + Cfg::A_BYTES, &p.tmX[prob * 2 + seg], kb * BK, t0, &full[it]);
+            }
+            for (int it = pre; it < n_iters; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, p.status, DEV_ERR_EMPTY_WAIT)) break;
                 const int i = kb_begin + it;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
@@ -130,8 +263,13 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                 uint8_t* a = smem + s * Cfg::STAGE_BYTES;
                 uint8_t* b = a + Cfg::A_BYTES;
                 mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-                tma_load_2d(a, &p.tmW[seg], kb * BK, n0, &full[s]);
-                tma_load_2d(b, &p.tmX[seg], kb * BK, t0, &full[s]);
+                if (halves) {
+                    tma_load_2d(a, &p.tmW[prob * 2], kb * BK, n0, &full[s]);
+                    tma_load_2d(a + Cfg::A_BYTES / 2, &p.tmW[prob * 2 + 1], kb * BK, n0, &full[s]);
+                } else {
+                    tma_load_2d(a, &p.tmW[prob * 2 + seg], kb * BK, n0, &full[s]);
+                }
+                tma_load_2d(b, &p.tmX[prob * 2 + seg], kb * BK, t0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -140,113 +278,134 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             bool started[2] = {false, false};
             bool ok = true;
             for (int it = 0; it < n_iters && ok; ++it) {
-                const int s = it % Cfg::STAGES;
-                const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 ok = mbar_wait(&full[s], ph, p.status, DEV_ERR_FULL_WAIT);
                 if (!ok) break;
+                if (it < 12) TFFN_TRACE(16 + it);
                 tc_fence_after();
                 const int seg = (kb_begin + it) >= p.kblocks[0] ? 1 : 0;
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                 const uint32_t b_addr = a_addr + Cfg::A_BYTES;
                 const uint32_t d = tmem_base + (uint32_t)(seg * BN);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
+                for (int k = 0; k < BK / 16; ++k)
                     umma_bf16(d, umma_desc_k128(a_addr + k * 32), umma_desc_k128(b_addr + k * 32), idesc,
                               (started[seg] || k > 0) ? 1u : 0u);
-                }
                 started[seg] = true;
+                if (it < 12) TFFN_TRACE(28 + it);
                 umma_commit(&empty[s]);
             }
+            TFFN_TRACE(3);
             umma_commit(acc_full);  // arrives when every MMA above has finished (also on the error path)
         }
     } else {
-        // epilogue warps 2..5 -> TMEM lane quarter (warp % 4)
+        // Epilogue warps 2..5 own TMEM lane quarter (warp % 4): thread = one weight row. They add up
+        // the accumulation chains, combine the two operand pairs (SwiGLU, or base + alpha * expert)
+        // and park ONE fp32 plane [column][row] in the idle stage memory.
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const int n = n0 + row;
+        pdl_wait();  // later phases read and write buffers of earlier kernels
         // every lane waits (acquire); the outcome is made warp-uniform because tcgen05.ld is .aligned
         bool ok = mbar_wait(acc_full, 0, p.status, DEV_ERR_ACC_WAIT);
         ok = __all_sync(0xffffffffu, ok);
+        if (threadIdx.x == 64) TFFN_TRACE(4);
         tc_fence_after();
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const bool dual = p.kblocks[1] > 0;
-        if (p.splits == 1) {
-            if (ok && n_iters > 0) {
+        const bool live = ok && n_iters > 0;
+        float* plane = (float*)smem;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (t0 + c0 >= p.T) break;
-                    uint32_t v0[16], v1[16];
-                    if (has0) tmem_ld16(lane_addr + c0, v0);
-                    if (has1) tmem_ld16(lane_addr + BN + c0, v1);
-                    tc_wait_ld();
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (t0 + c0 >= p.T) break;
+            uint32_t v0[16], v1[16];
+            if (live && has0) tmem_ld16(lane_addr + (uint32_t)c0, v0);
+            if (live && has1) tmem_ld16(lane_addr + (uint32_t)(BN + c0), v1);
+            tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        epilogue_apply(p, n, t0 + c0 + j, has0 ? __uint_as_float(v0[j]) : 0.f,
-                                       has1 ? __uint_as_float(v1[j]) : 0.f, dual);
-                }
-            }
-        } else {
-            // split-K: park this CTA's partial tile in its own shared memory (the pipeline stages are
-            // free: every load was consumed by an MMA that has completed); layout [acc][column][row]
-            float* red = (float*)smem;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (t0 + c0 >= p.T) break;
-                uint32_t v0[16], v1[16];
-                const bool live = ok && n_iters > 0;
-                if (live && has0) tmem_ld16(lane_addr + c0, v0);
-                if (live && has1) tmem_ld16(lane_addr + BN + c0, v1);
-                tc_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    red[(size_t)(c0 + j) * BM + row] = (live && has0) ? __uint_as_float(v0[j]) : 0.f;
-                    if (dual) red[(size_t)(BN + c0 + j) * BM + row] = (live && has1) ? __uint_as_float(v1[j]) : 0.f;
-                }
+            for (int j = 0; j < 16; ++j) {
+                const float a0 = (live && has0) ? __uint_as_float(v0[j]) : 0.f;
+                const float a1 = (live && has1) ? __uint_as_float(v1[j]) : 0.f;
+                plane[(size_t)(c0 + j) * BM + row] = dual ? a0 + p.alpha * a1 : a0;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 64) TFFN_TRACE(5);
+    // With split-K the splits of one output tile form a thread-block cluster (1,1,splits): after the
+    // cluster barrier each CTA finalises the columns it owns (column % splits == rank) by summing the
+    // parked planes of all ranks, in rank order, over distributed shared memory. Without a split
+    // the CTA finalises all columns from its own plane. Finalisation is vectorised the other way
+    // round from the TMEM layout: a warp takes one column, a lane 4 consecutive rows, so every global
+    // access is 8 or 16 bytes per lane and the RoPE partner of a row sits in the same warp.
     if (p.splits > 1) {
-        // The splits of one output tile form a thread-block cluster (1,1,splits). After the cluster
-        // barrier every CTA sums, over all splits in rank order, the columns it owns (column % splits
-        // == rank) straight out of its peers' shared memory, and applies the epilogue. A second
-        // barrier keeps every CTA's shared memory alive until its peers have finished reading it.
         cluster_sync_all();
-        if (warp >= 2) {
-            const int q = warp & 3;
-            const int row = q * 32 + lane;
-            const int n = n0 + row;
-            const bool dual = p.kblocks[1] > 0;
-            const uint32_t rank = cluster_ctarank();
-            const uint32_t red_local = smem_u32(smem);
-            uint32_t peer[8];
+        if (threadIdx.x == 64) TFFN_TRACE(6);
+    }
+    if (warp >= 2 && n_iters > 0) {
+        const int w = warp - 2;
+        const int r4 = lane * 4;
+        const int n = n0 + r4;
+        const uint32_t rank = p.splits > 1 ? cluster_ctarank() : 0u;
+        const uint32_t plane_local = smem_u32(smem);
+        uint32_t peer[kMaxSplits];
 #pragma unroll
-            for (int z = 0; z < 8; ++z) peer[z] = (z < p.splits) ? map_shared_rank(red_local, (uint32_t)z) : 0u;
-            for (int c = (int)rank; c < BN; c += p.splits) {
-                if (t0 + c >= p.T) break;
-                float v0[8], v1[8];
+        for (int z = 0; z < kMaxSplits; ++z) peer[z] = (p.splits > 1 && z < p.splits) ? map_shared_rank(plane_local, (uint32_t)z) : plane_local;
+        const int ncols = (BN - (int)rank + p.splits - 1) / p.splits;  // columns rank, rank + S, ...
+        for (int k = w; k < ncols; k += 4) {
+            const int c = (int)rank + k * p.splits;
+            const int t = t0 + c;
+            if (t >= p.T) break;  // warp-uniform
+            const uint32_t off = (uint32_t)(((size_t)c * BM + r4) * 4);
+            float4 acc;
+            if (p.splits == 1) {
+                acc = *(const float4*)(smem + off);
+            } else {
+                float4 v[kMaxSplits];
 #pragma unroll
-                for (int z = 0; z < 8; ++z) {
-                    v0[z] = 0.f;
-                    v1[z] = 0.f;
-                    if (z < p.splits) {
-                        v0[z] = ld_shared_cluster_f32(peer[z] + (uint32_t)(((size_t)c * BM + row) * 4));
-                        if (dual) v1[z] = ld_shared_cluster_f32(peer[z] + (uint32_t)(((size_t)(BN + c) * BM + row) * 4));
+                for (int z = 0; z < kMaxSplits; ++z) v[z] = (z < p.splits) ? ld_shared_cluster_v4(peer[z] + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                acc = v[0];
+#pragma unroll
+                for (int z = 1; z < kMaxSplits; ++z) {  // rank order: the sum does not depend on scheduling
+                    acc.x += v[z].x;
+                    acc.y += v[z].y;
+                    acc.z += v[z].z;
+                    acc.w += v[z].w;
+                }
+            }
+            if (p.mode == GEMM_QKV) {
+                finalize_qkv(p, n, t, acc, lane);
+            } else if (halves) {
+                // rows 0..63 of the tile hold gate, rows 64..127 up, for the same 64 output indices
+                if (lane < 16) {
+                    float4 up;
+                    if (p.splits == 1) {
+                        up = *(const float4*)(smem + off + 64 * 4);
+                    } else {
+                        up = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int z = 0; z < kMaxSplits; ++z)
+                            if (z < p.splits) {
+                                const float4 u = ld_shared_cluster_v4(peer[z] + off + 64 * 4);
+                                up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
+                            }
                     }
+                    finalize_plain(p, out, n, t,
+                                   make_float4(silu_mul_bf16(acc.x, up.x), silu_mul_bf16(acc.y, up.y), silu_mul_bf16(acc.z, up.z),
+                                               silu_mul_bf16(acc.w, up.w)));
                 }
-                float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-                for (int z = 0; z < 8; ++z) {
-                    a0 += v0[z];
-                    a1 += v1[z];
-                }
-                epilogue_apply(p, n, t0 + c, a0, a1, dual);
+            } else {
+                finalize_plain(p, out, n, t, acc);
             }
         }
-        cluster_sync_all();
     }
-    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (p.splits > 1) {
+        if (threadIdx.x == 64) TFFN_TRACE(7);
+        cluster_sync_all();  // keep this CTA's plane alive until its peers have read it
+    }
+    if (threadIdx.x == 64) TFFN_TRACE(8);
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -318,55 +477,80 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     using Cfg = GemmCfg<BN>;
     GemmDev p;
     memset(&p, 0, sizeof p);
-    for (int i = 0; i < 2; ++i) {
-        const GemmOperand& o = c.op[i];
-        p.kblocks[i] = o.K > 0 ? (o.K + BK - 1) / BK : 0;
-        if (o.K <= 0) continue;
-        if (!make_tmap(&p.tmW[i], o.W, (uint64_t)c.N, (uint64_t)o.K, (uint64_t)o.ldw, BM)) return -1000;
-        if (!make_tmap(&p.tmX[i], o.X, (uint64_t)(c.x_rows_alloc > c.T ? c.x_rows_alloc : c.T), (uint64_t)o.K,
-                       (uint64_t)o.ldx, BN))
-            return -1000;
-    }
-    if (p.kblocks[1] == 0) {  // keep the unused maps valid for prefetch
-        p.tmW[1] = p.tmW[0];
-        p.tmX[1] = p.tmX[0];
-    }
+    const int nprob = c.out2 ? 2 : 1;
+    const bool halves = c.mode == GEMM_SWIGLU;
+    p.tile_n = halves ? BM / 2 : BM;
+    if (halves && (c.op[0].K != c.op[1].K || c.op[0].X != c.op[1].X)) return (int)cudaErrorInvalidValue;
+    for (int pr = 0; pr < nprob; ++pr)
+        for (int i = 0; i < 2; ++i) {
+            const GemmOperand& o = pr ? c.op2[i] : c.op[i];
+            if (pr == 0) p.kblocks[i] = o.K > 0 ? (o.K + BK - 1) / BK : 0;
+            if (o.K <= 0) continue;
+            if (pr == 1 && (o.K + BK - 1) / BK != p.kblocks[i]) return (int)cudaErrorInvalidValue;
+            if (!make_tmap(&p.tmW[pr * 2 + i], o.W, (uint64_t)c.N, (uint64_t)o.K, (uint64_t)o.ldw, halves ? BM / 2 : BM)) return -1000;
+            if (!make_tmap(&p.tmX[pr * 2 + i], o.X, (uint64_t)(c.x_rows_alloc > c.T ? c.x_rows_alloc : c.T), (uint64_t)o.K,
+                           (uint64_t)o.ldx, BN))
+                return -1000;
+        }
+    if (halves) p.kblocks[1] = 0;  // gate and up rows share one accumulator and one pass over K
+    for (int i = 1; i < 4; ++i)  // keep unused maps valid
+        if (i >= nprob * 2 || (p.kblocks[i & 1] == 0 && !halves)) {
+            p.tmW[i] = p.tmW[0];
+            p.tmX[i] = p.tmX[0];
+        }
     p.N = c.N;
     p.T = c.T;
     p.mode = c.mode;
     p.alpha = c.alpha;
-    p.out = c.out;
+    p.out[0] = c.out;
+    p.out[1] = c.out2 ? c.out2 : c.out;
     p.ldo = c.ldo;
     p.status = ws.status;
-    const int n_tiles = (c.N + BM - 1) / BM, t_tiles = (c.T + BN - 1) / BN;
+    p.trace = c.trace;
+    if (c.mode == GEMM_QKV) {
+        if (!c.qkv || c.op[1].K > 0 || c.out2 || (c.qkv->kv.hd != 64 && c.qkv->kv.hd != 128)) return (int)cudaErrorInvalidValue;
+        p.qkv = *c.qkv;
+    }
+    const int n_tiles = (c.N + p.tile_n - 1) / p.tile_n, t_tiles = (c.T + BN - 1) / BN;
     const int total_kb = p.kblocks[0] + p.kblocks[1];
-    const int tiles = n_tiles * t_tiles;
-    const bool dual = p.kblocks[1] > 0;
-    const bool split_ok = dual ? Cfg::SPLIT_OK_DUAL : Cfg::SPLIT_OK_SINGLE;
-    // K splits = cluster size (1, 2, 4 or 8): grow while all CTAs stay co-resident (two per SM for
-    // the decode tile sizes) and every split keeps at least two k-blocks
+    const int tiles = n_tiles * t_tiles * nprob;
+    p.t_tiles = t_tiles;
+    // K splits = cluster size (1, 2, 4 or 8). One CTA sustains roughly one 64-deep k-block per
+    // 0.3 us whatever the ring depth (MMA issue, commit and barrier turn-around, measured), about
+    // 55 GB/s of weights, so a weight-streaming launch needs about as many CTAs as there are SMs:
+    // tiles are split along K until the grid fills the SMs, keeping two k-blocks per split.
     int splits = 1;
     if (force_splits > 0) {
         splits = force_splits;
-    } else if (split_ok) {
-        const int resident = ws.num_sms * ((BN <= 64) ? 2 : 1);
-        while (splits < 8 && tiles * splits * 2 <= resident && total_kb / (splits * 2) >= 2) splits *= 2;
+    } else {
+        while (splits < kMaxSplits && tiles * splits * 2 <= ws.num_sms + ws.num_sms / 8 && total_kb / (splits * 2) >= 1) splits *= 2;
     }
-    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return (int)cudaErrorInvalidValue;
-    if (splits > 1 && (!split_ok || splits > total_kb)) return (int)cudaErrorInvalidValue;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return (int)cudaErrorInvalidValue;
+    if (splits > total_kb) return (int)cudaErrorInvalidValue;
+    const bool shared_sm = tiles * splits > ws.num_sms;  // more than one CTA per SM
+    p.stages = shared_sm ? Cfg::SHARED_STAGES : Cfg::MAX_STAGES;
     p.splits = splits;
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
-    cfg.gridDim = dim3(n_tiles, t_tiles, splits);
+    cfg.gridDim = dim3(n_tiles, t_tiles * nprob, splits);
     cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = Cfg::smem_bytes(p.stages);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = splits;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = splits;
+        ++na;
+    }
+    if (c.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = splits > 1 ? 1 : 0;
+    cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, k_gemm_tc<BN>, p);
 }
 
@@ -375,7 +559,9 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
 int gemm_prepare() {
     cudaError_t e;
 #define TFFN_PREP(BN)                                                                                                 \
-    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES); \
+    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::smem_bytes(GemmCfg<BN>::MAX_STAGES)); \
+    if (e != cudaSuccess) return (int)e;                                                                             \
+    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);                     \
     if (e != cudaSuccess) return (int)e;
     TFFN_PREP(16) TFFN_PREP(32) TFFN_PREP(64) TFFN_PREP(128) TFFN_PREP(256)
 #undef TFFN_PREP

@@ -11,6 +11,17 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int kPageTokens = 32;  // tokens per KV page
 
+// ------------------------------------------------------------------ paged KV cache view
+struct KvView {
+    bf16* k_pool;            // [L][pages][nkv][kPageTokens][hd]
+    bf16* v_pool;
+    const int* block_table;  // [max_batch][max_pages_per_seq]
+    int max_pages_per_seq;
+    int num_pages;           // pages per layer
+    size_t layer_stride;     // elements between layers of a pool
+    int nkv, hd;
+};
+
 // ------------------------------------------------------------------ tensor-core GEMM (batched path)
 // out[t, n] = epilogue( sum_k X0[t,k] W0[n,k] , sum_k X1[t,k] W1[n,k] )
 enum GemmMode : int {
@@ -18,6 +29,15 @@ enum GemmMode : int {
     GEMM_STORE_BF16 = 1,  // out bf16  = bf16(a0 (+ alpha * a1))
     GEMM_RESIDUAL = 2,    // out bf16 += a0 (+ alpha * a1), i.e. out = bf16(float(out) + sum)
     GEMM_SWIGLU = 3,      // out bf16  = bf16(silu(bf16(a0)) * bf16(a1))   (a0 gate rows, a1 up rows)
+    GEMM_QKV = 4,         // q|k|v rows: bias + RoPE + page writes in the epilogue (GemmCall::qkv), no `out`
+};
+struct GemmQkvEpilogue {
+    const bf16* bias;               // [(nh+2nkv)*hd] or null
+    const float *rope_cos, *rope_sin;
+    const int *tok_seq, *tok_pos;   // per token: sequence slot and position
+    float* q_out;                   // fp32 [T, nh*hd]
+    KvView kv;
+    int layer, nh, max_pos;
 };
 struct GemmOperand {
     const bf16* W;  // [N, K] row-major, row stride ldw elements
@@ -34,6 +54,16 @@ struct GemmCall {
     void* out;
     int64_t ldo;
     int x_rows_alloc;  // rows that exist in the X buffers (>= T); the tensor map covers them
+    // optional second, independent problem of the same shape in the same launch (e.g. the expert's
+    // gate/up next to the base's): its operands and its output; out2 == nullptr means none
+    GemmOperand op2[2];
+    void* out2;
+    const GemmQkvEpilogue* qkv;  // GEMM_QKV only
+    // optional device buffer of 64 u64 per CTA: globaltimer (ns) at 0 start, 1 weight boxes requested,
+    // 2 dependency wait over, 3 last MMA issued, 4 accumulator complete, 5 epilogue/park done,
+    // 6 cluster barrier passed, 7 reduction done, 8 end, 16+i stage i arrived (i < 40)
+    unsigned long long* trace;
+    bool pdl;          // launch with programmatic dependent launch (the kernel waits before touching X / out)
 };
 struct GemmWorkspace {
     float* partials;        // split-K partial tiles
@@ -48,26 +78,18 @@ int gemm_prepare();
 // returns cudaError (launch) or -1000 if the tensor maps could not be encoded
 int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, int force_splits = 0);
 
-// ------------------------------------------------------------------ paged KV cache view
-struct KvView {
-    bf16* k_pool;            // [L][pages][nkv][kPageTokens][hd]
-    bf16* v_pool;
-    const int* block_table;  // [max_batch][max_pages_per_seq]
-    int max_pages_per_seq;
-    int num_pages;           // pages per layer
-    size_t layer_stride;     // elements between layers of a pool
-    int nkv, hd;
-};
-
 // ------------------------------------------------------------------ row kernels of the batched path
-void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s);
-void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s);
+// (pdl: launch with programmatic dependent launch; every kernel here waits before reading its inputs)
+void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s,
+                  bool pdl = false);
+void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
+                    bool pdl = false);
 // qkv fp32 [T, (nh+2nkv)*hd] -> bf16 round, bias (bf16 add), RoPE, q fp32 [T, nh*hd], K/V into pages
 void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
                      const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
-                     int T, int nh, int max_pos, int* status, cudaStream_t s);
+                     int T, int nh, int max_pos, int* status, cudaStream_t s, bool pdl = false);
 // logits fp32 [R, V] -> argmax (lowest index among maxima)
-void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s);
+void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s, bool pdl = false);
 
 // ------------------------------------------------------------------ attention over the paged cache
 struct AttnWorkspace {
@@ -80,7 +102,7 @@ struct AttnWorkspace {
 int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
 // one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t]
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
-                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s);
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl = false);
 
 // ------------------------------------------------------------------ batch-1 fused decode kernels
 struct Bs1Layer {
@@ -110,6 +132,10 @@ struct Bs1Ctx {
     int* step_counter;
     int* status;
     int num_sms;
+    // optional profiling aid for k_bs1_ffn: 16 u64 per CTA, globaltimer ns at 0 start, 1 rmsnorm done,
+    // 2 first record arrived, 3 last record consumed, 4 CTA partial written, 5 group ticket taken,
+    // 6 group fold done (last CTA of a group only), 7 residual updated (last group only)
+    unsigned long long* trace;
 };
 bool bs1_supported(int H, int I, int hd, int nh, int nkv);
 size_t bs1_ffn_part_floats(int H, int num_sms);

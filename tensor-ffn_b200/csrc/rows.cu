@@ -2,6 +2,7 @@
 // kernel whose arithmetic (and rounding points) it reproduces.
 #include "kernels.h"
 #include "ptx.cuh"
+#include "launch.h"
 
 namespace tffn {
 
@@ -10,8 +11,10 @@ namespace {
 // h[t,:] = table[tokens[t],:]  (k_embed, inference/src/model/qwen.cu:216-220); ids are bounds-checked.
 __global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ h, int T,
                              int H, int V, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
-    int tok = tokens[t];
+    int tok = __ldcg(tokens + t);
     if (tok < 0 || tok >= V) {
         if (threadIdx.x == 0) dev_fail(status, DEV_ERR_BOUNDS);
         tok = 0;
@@ -25,12 +28,14 @@ __global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restr
 __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                       bf16* __restrict__ out, int H, float eps,
                                                       const int* __restrict__ row_idx) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src_row = row_idx ? row_idx[r] : r;
     const uint4* xr = (const uint4*)(x + (size_t)src_row * H);
     float ss = 0.f;
     for (int i = threadIdx.x; i < H / 8; i += 128) {
-        uint4 v = xr[i];
+        uint4 v = __ldcg(xr + i);
         uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -47,7 +52,7 @@ __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x
     const uint4* wr = (const uint4*)w;
     uint4* orow = (uint4*)(out + (size_t)r * H);
     for (int i = threadIdx.x; i < H / 8; i += 128) {
-        uint4 v = xr[i], g = __ldg(wr + i);
+        uint4 v = __ldcg(xr + i), g = __ldg(wr + i);
         uint32_t u[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w}, o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -68,10 +73,12 @@ __global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict
                            const float* __restrict__ rope_sin, const int* __restrict__ tok_seq,
                            const int* __restrict__ tok_pos, float* __restrict__ q_out, KvView kv, int layer, int nh,
                            int max_pos, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, head = blockIdx.y, i = threadIdx.x;
     const int hd = kv.hd, half = hd >> 1, nkv = kv.nkv;
     const int nq = nh * hd, nk = nkv * hd, ntot = nq + 2 * nk;
-    const int pos = tok_pos[t], seq = tok_seq[t];
+    const int pos = __ldcg(tok_pos + t), seq = __ldcg(tok_seq + t);
     const float* row = qkv + (size_t)t * ntot;
     int col0;
     const bf16* bias;
@@ -80,7 +87,7 @@ __global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict
     if (head < nh) { kind = 0; hh = head; col0 = head * hd; bias = bq ? bq + head * hd : nullptr; }
     else if (head < nh + nkv) { kind = 1; hh = head - nh; col0 = nq + hh * hd; bias = bk ? bk + hh * hd : nullptr; }
     else { kind = 2; hh = head - nh - nkv; col0 = nq + nk + hh * hd; bias = bv ? bv + hh * hd : nullptr; }
-    float x0 = bf16_round(row[col0 + i]), x1 = bf16_round(row[col0 + i + half]);
+    float x0 = bf16_round(__ldcg(row + col0 + i)), x1 = bf16_round(__ldcg(row + col0 + i + half));
     if (bias) {
         x0 = bf16_round(x0 + __bfloat162float(bias[i]));
         x1 = bf16_round(x1 + __bfloat162float(bias[i + half]));
@@ -101,7 +108,7 @@ __global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict
         qo[i + half] = x1;
         return;
     }
-    const int pg = kv.block_table[(size_t)seq * kv.max_pages_per_seq + pos / kPageTokens];
+    const int pg = __ldcg(kv.block_table + (size_t)seq * kv.max_pages_per_seq + pos / kPageTokens);
     if (pg < 0 || pg >= kv.num_pages) {
         if (i == 0) dev_fail(status, DEV_ERR_BOUNDS);
         return;
@@ -114,11 +121,13 @@ __global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict
 
 // greedy pick: first index of the strict maximum (sample(), inference/src/main.cpp:45-51)
 __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += 1024) {
-        float v = row[i];
+        float v = __ldcg(row + i);
         if (v > best || (v == best && i < bi)) { best = v; bi = i; }
     }
     // NaN-free inputs assumed; if every value is -inf the lowest index 0 wins below
@@ -177,21 +186,22 @@ __global__ void k_wait_selftest(int* status) {
 
 }  // namespace
 
-void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s) {
-    k_embed_rows<<<T, 128, 0, s>>>(tokens, table, h, T, H, V, status);
+void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s, bool pdl) {
+    launch_k(k_embed_rows, dim3(T), dim3(128), 0, s, pdl, tokens, table, h, T, H, V, status);
 }
-void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s) {
-    k_rmsnorm_rows<<<T, 128, 0, s>>>(x, w, out, H, eps, row_idx);
+void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
+                    bool pdl) {
+    launch_k(k_rmsnorm_rows, dim3(T), dim3(128), 0, s, pdl, x, w, out, H, eps, row_idx);
 }
 void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
                      const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
-                     int T, int nh, int max_pos, int* status, cudaStream_t s) {
+                     int T, int nh, int max_pos, int* status, cudaStream_t s, bool pdl) {
     dim3 grid(T, nh + 2 * kv.nkv);
-    k_qkv_post<<<grid, kv.hd / 2, 0, s>>>(qkv, bq, bk, bv, rope_cos, rope_sin, tok_seq, tok_pos, q_out, kv, layer, nh,
-                                         max_pos, status);
+    launch_k(k_qkv_post, grid, dim3(kv.hd / 2), 0, s, pdl, qkv, bq, bk, bv, rope_cos, rope_sin, tok_seq, tok_pos, q_out, kv,
+             layer, nh, max_pos, status);
 }
-void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s) {
-    k_argmax_rows<<<R, 1024, 0, s>>>(logits, V, out);
+void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s, bool pdl) {
+    launch_k(k_argmax_rows, dim3(R), dim3(1024), 0, s, pdl, logits, V, out);
 }
 void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s) {
     int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);

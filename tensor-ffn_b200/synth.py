@@ -227,11 +227,11 @@ def write_expert(path: str, cfg: dict, seed: int = 4321, std: float = 0.02, thre
             f.truncate(max(0, os.path.getsize(path) - truncate_bytes))
 
 
-def prompts(n_seqs: int, length: int, config_idx: int = 0, vocab_limit: int = 151643) -> np.ndarray:
-    """int32 [n_seqs, length] uniform ids in [0, vocab_limit), one seed per sequence."""
+def prompts(n_seqs: int, length: int, config_idx: int = 0, vocab_limit: int = 151643, first_seq: int = 0) -> np.ndarray:
+    """int32 [n_seqs, length] uniform ids in [0, vocab_limit), one seed per (global) sequence index."""
     out = np.empty((n_seqs, length), dtype=np.int32)
     for s in range(n_seqs):
-        rng = np.random.default_rng([2025, config_idx, s])
+        rng = np.random.default_rng([2025, config_idx, first_seq + s])
         out[s] = rng.integers(0, vocab_limit, size=length, dtype=np.int32)
     return out
 

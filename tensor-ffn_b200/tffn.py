@@ -87,7 +87,9 @@ _SIGS = {
     "tffn_session_launch_count": (ctypes.c_uint64, [_vp]),
     "tffn_session_stream": (_vp, [_vp]),
     "tffn_op_gemm": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "tffn_op_gemm_trace": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i]),
     "tffn_op_swiglu_bs1": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
+    "tffn_op_swiglu_bs1_trace": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp, _vp, _i]),
     "tffn_op_swiglu_bs1_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
     "tffn_op_wait_selftest": (_i, [_i]),
 }
@@ -339,6 +341,19 @@ def op_gemm(X: np.ndarray, W: np.ndarray, splits: int = 0, device: int = 0) -> n
     return out
 
 
+def op_gemm_trace(X: np.ndarray, W: np.ndarray, splits: int = 0, max_ctas: int = 4096, device: int = 0):
+    """op_gemm plus per-CTA phase timestamps: returns (out, trace uint64 [max_ctas, 64], zeros where unused)"""
+    X = np.ascontiguousarray(X, dtype=np.uint16)
+    W = np.ascontiguousarray(W, dtype=np.uint16)
+    T, K = X.shape
+    N = W.shape[0]
+    out = np.empty((T, N), dtype=np.float32)
+    trace = np.zeros((max_ctas, 64), dtype=np.uint64)
+    _check(_L.tffn_op_gemm_trace(device, X.ctypes.data, W.ctypes.data, out.ctypes.data, T, N, K, splits, trace.ctypes.data,
+                                 max_ctas))
+    return out, trace
+
+
 def pack_ffn(gate: np.ndarray, up: np.ndarray, down: np.ndarray) -> np.ndarray:
     """gate, up [I,H], down [H,I] (bf16 bits) -> records [I][3][H]: gate row, up row, down column"""
     return np.ascontiguousarray(np.stack([gate, up, down.T], axis=1))
@@ -355,6 +370,20 @@ def op_swiglu_bs1(h, norm_w, packed_base, packed_expert=None, expert_scale=0.1, 
     _check(_L.tffn_op_swiglu_bs1(device, h.ctypes.data, w.ctypes.data, pb.ctypes.data, _ptr(pe), expert_scale, eps, H, I,
                                  out.ctypes.data))
     return out
+
+
+def op_swiglu_bs1_trace(h, norm_w, packed_base, packed_expert=None, expert_scale=0.1, eps=1e-6, max_ctas=256, device: int = 0):
+    """op_swiglu_bs1 plus per-CTA phase timestamps of a warm launch: (h_out, trace uint64 [max_ctas, 16])"""
+    h = np.ascontiguousarray(h, dtype=np.uint16)
+    w = np.ascontiguousarray(norm_w, dtype=np.uint16)
+    pb = np.ascontiguousarray(packed_base, dtype=np.uint16)
+    pe = None if packed_expert is None else np.ascontiguousarray(packed_expert, dtype=np.uint16)
+    I, _, H = pb.shape
+    out = np.empty(H, dtype=np.uint16)
+    trace = np.zeros((max_ctas, 16), dtype=np.uint64)
+    _check(_L.tffn_op_swiglu_bs1_trace(device, h.ctypes.data, w.ctypes.data, pb.ctypes.data, _ptr(pe), expert_scale, eps, H, I,
+                                       out.ctypes.data, trace.ctypes.data, max_ctas))
+    return out, trace
 
 
 def op_swiglu_bs1_noalloc(h_io_ptr: int, norm_w_ptr: int, packed_base_ptr: int, packed_expert_ptr: int | None, H: int, I: int,

@@ -27,7 +27,7 @@ def test_gemm_matches_numpy(T, N, K):
     assert err < 2e-5, err  # fp32 accumulation of exact bf16 products
 
 
-@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8, 16])
 def test_gemm_split_k_is_deterministic(splits):
     import tffn
     rng = np.random.default_rng(99)
