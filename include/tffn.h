@@ -107,7 +107,9 @@ void tffn_session_free(tffn_session* s);
 int tffn_session_reset(tffn_session* s, int slot);
 int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */
 /* 0: plain stream launches. 1: programmatic dependent launch between the batch-1 kernels.
- * 2: 1 + the whole batch-1 step replayed from a CUDA graph. Default 1. */
+ * 2: 1 + every decode step (batch-1 and batched) replayed from a CUDA graph.
+ * 3: 2, and batch-1 steps run as ONE persistent cooperative kernel per token where the shape has an
+ *    instantiation (otherwise as in 2). Default 1. */
 int tffn_session_set_launch_mode(tffn_session* s, int mode);
 /* Which path single-token steps take: 1 (default) the fused batch-1 kernels when the shape
  * allows, 0 the batched tensor-core path. */
@@ -145,6 +147,11 @@ uint64_t tffn_session_launch_count(const tffn_session* s);
 int tffn_session_profile(tffn_session* s, int enable);
 int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int cap);
 const char* tffn_profile_class_name(int cls);
+/* Profiling aid (no counterpart in the reference): runs ONE batch-1 decode step of slot 0 on the
+ * persistent kernel, feeding the slot's previous pick, and returns per-CTA device timestamps
+ * (globaltimer, ns) of layer 1 in out[cta*16 + k]: k = 0 layer start, 1/2 before/after the barrier that
+ * ends QKV, 3/4 attention, 5/6 o_proj, 7/8 SwiGLU, 9/10 partial-sum fold. Returns the CTA count. */
+int tffn_session_mega_trace(tffn_session* s, uint64_t* out, int max_ctas);
 /* the stream the session launches on (a cudaStream_t) */
 void* tffn_session_stream(const tffn_session* s);
 

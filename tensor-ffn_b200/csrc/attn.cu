@@ -12,25 +12,21 @@
 #include "kernels.h"
 #include "ptx.cuh"
 #include "launch.h"
+#include "attn_core.cuh"
 
 namespace tffn {
 
 namespace {
 
-constexpr int kAttnThreads = 128;
-constexpr float kNegBig = -1e30f;  // the reference's mask value (qwen.cu:278)
-
-template <int HD, int G>
+template <int HD, int G, bool STAGED>
 __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
                                                               const int* __restrict__ tok_seq,
                                                               const int* __restrict__ tok_pos, bf16* __restrict__ ctx,
                                                               int nh, int splits, float* __restrict__ ws,
                                                               int* __restrict__ counters, int* status) {
-    constexpr int LPT = HD / 8;                  // lanes per cached token row (16 bytes each)
-    constexpr int NG = kAttnThreads / LPT;       // token rows in flight per CTA
-    __shared__ float s_m[NG][G], s_l[NG][G];
-    __shared__ float s_acc[NG][G][HD];
+    __shared__ AttnShared<HD, G> sh;
     __shared__ int s_last;
+    extern __shared__ __align__(128) uint8_t stage_raw[];  // STAGED: K pages | V pages | mbarrier
 
     pdl_launch_dependents();
     pdl_wait();
@@ -45,124 +41,37 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     chunk = (chunk + kPageTokens - 1) / kPageTokens * kPageTokens;
     const int c_begin = split * chunk;
     const int c_end = min(ctx_len, c_begin + chunk);
-
-    const int grp = threadIdx.x / LPT, sub = threadIdx.x % LPT;
-    const float scale = rsqrtf((float)HD);
-
-    float qr[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float4* qp = (const float4*)(q + ((size_t)t * nh + kvh * G + g) * HD + sub * 8);
-        float4 a = __ldcg(qp), b = __ldcg(qp + 1);
-        qr[g][0] = a.x; qr[g][1] = a.y; qr[g][2] = a.z; qr[g][3] = a.w;
-        qr[g][4] = b.x; qr[g][5] = b.y; qr[g][6] = b.z; qr[g][7] = b.w;
-    }
-    float m[G], l[G], acc[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = kNegBig;
-        l[g] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
-    }
-    const bf16* kpool = kv.k_pool + (size_t)layer * kv.layer_stride;
-    const bf16* vpool = kv.v_pool + (size_t)layer * kv.layer_stride;
-    const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
-    bool bad = false;
-
-    // U rows per thread group and iteration: their page lookups and 16-byte K/V loads are all in
-    // flight before the first dot product, which hides the HBM latency that a one-row loop pays
-    // per row. The trip count is uniform across the warp (the shuffles use the full mask); rows past
-    // the end of the range, or with a bad page id, are computed on zeros and then discarded.
-    constexpr int U = 4;
-    for (int base = c_begin; base < c_end; base += NG * U) {
-        int pg[U];
-        bool valid[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int tok = base + u * NG + grp;
-            valid[u] = tok < c_end;
-            pg[u] = valid[u] ? __ldcg(bt + tok / kPageTokens) : 0;
-        }
-        uint4 kk[U], vv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int tok = base + u * NG + grp;
-            if (valid[u] && (pg[u] < 0 || pg[u] >= kv.num_pages)) { bad = true; valid[u] = false; }
-            kk[u] = make_uint4(0, 0, 0, 0);
-            vv[u] = make_uint4(0, 0, 0, 0);
-            if (valid[u]) {
-                const size_t off = (((size_t)pg[u] * nkv + kvh) * kPageTokens + tok % kPageTokens) * HD + sub * 8;
-                kk[u] = __ldcg((const uint4*)(kpool + off));
-                vv[u] = __ldcg((const uint4*)(vpool + off));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t ku[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
-            float kf[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { kf[2 * j] = bf16_lo(ku[j]); kf[2 * j + 1] = bf16_hi(ku[j]); }
-            float s[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float d = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) d += qr[g][j] * kf[j];
-                s[g] = d;
-            }
-#pragma unroll
-            for (int o = LPT / 2; o > 0; o >>= 1)
-#pragma unroll
-                for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-            if (!valid[u]) continue;
-            const uint32_t vu[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
-            float vf[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { vf[2 * j] = bf16_lo(vu[j]); vf[2 * j + 1] = bf16_hi(vu[j]); }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float sc = s[g] * scale;
-                const float mn = fmaxf(m[g], sc);
-                const float corr = __expf(m[g] - mn);
-                const float p = __expf(sc - mn);
-                m[g] = mn;
-                l[g] = l[g] * corr + p;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + p * vf[j];
-            }
-        }
-    }
-    if (bad) dev_fail(status, DEV_ERR_BOUNDS);
-
-    // merge the NG row groups of this CTA
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (sub == 0) { s_m[grp][g] = m[g]; s_l[grp][g] = l[g]; }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s_acc[grp][g][sub * 8 + j] = acc[g][j];
-    }
-    __syncthreads();
     float* part = ws + ((size_t)unit * splits + split) * (size_t)(G * (HD + 2));
-    for (int idx = threadIdx.x; idx < G * HD; idx += kAttnThreads) {
-        const int g = idx / HD, d = idx % HD;
-        float M = kNegBig;
-#pragma unroll
-        for (int r = 0; r < NG; ++r) M = fmaxf(M, s_m[r][g]);
-        float L = 0.f, A = 0.f;
-#pragma unroll
-        for (int r = 0; r < NG; ++r) {
-            const float w = __expf(s_m[r][g] - M);
-            L += s_l[r][g] * w;
-            A += s_acc[r][g][d] * w;
+    bf16* ctx_tok = ctx + (size_t)t * nh * HD;
+    const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
+    bf16* ks = (bf16*)stage_raw;
+    bf16* vs = ks + AttnStageCfg<HD>::MAX_PAGES * AttnStageCfg<HD>::PAGE_ELEMS;
+    bool stage_bad = false;
+    if (STAGED) {
+        // all K/V rows of this CTA's range are requested up front (one bulk copy per page and pool)
+        uint64_t* bar = (uint64_t*)(stage_raw + AttnStageCfg<HD>::BYTES - 16);
+        if (threadIdx.x == 0) {
+            mbar_init(bar, 1);
+            fence_mbar_init();
         }
-        if (splits == 1) {
-            ctx[((size_t)t * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
-        } else {
-            part[g * (HD + 2) + 2 + d] = A;
-            if (d == 0) { part[g * (HD + 2)] = M; part[g * (HD + 2) + 1] = L; }
-        }
+        __syncthreads();
+        if (threadIdx.x < 32) stage_bad = !attn_stage_pages<HD>(kv, layer, bt, kvh, c_begin, c_end, ks, vs, bar, (int)threadIdx.x);
+        if (!mbar_wait(bar, 0, status, DEV_ERR_FULL_WAIT)) stage_bad = true;
+        stage_bad = __syncthreads_or(stage_bad);
     }
+    const bool bad = attn_range<HD, G, STAGED>(
+        q + (size_t)t * nh * HD, kv, layer, bt, kvh, c_begin, stage_bad ? c_begin : c_end,
+        (int)threadIdx.x, sh, [] { __syncthreads(); },
+        [&](int g, int d, float M, float L, float A) {
+            if (splits == 1) {
+                ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+            } else {
+                part[g * (HD + 2) + 2 + d] = A;
+                if (d == 0) { part[g * (HD + 2)] = M; part[g * (HD + 2) + 1] = L; }
+            }
+        },
+        ks, vs);
+    if (bad || stage_bad) dev_fail(status, DEV_ERR_BOUNDS);
     if (splits == 1) return;
 
     __threadfence();
@@ -178,44 +87,27 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     const float* parts = ws + (size_t)unit * splits * (size_t)(G * (HD + 2));
     for (int idx = threadIdx.x; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx % HD;
-        float M = kNegBig, L = 0.f, A = 0.f;
-        // 8 splits per round with all loads in flight; a running maximum keeps the merge exact
-        for (int z0 = 0; z0 < splits; z0 += 8) {
-            float mz[8], lz[8], az[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool live = z0 + j < splits;
-                const float* pz = parts + (size_t)(live ? z0 + j : 0) * G * (HD + 2) + g * (HD + 2);
-                mz[j] = live ? __ldcg(pz) : kNegBig;
-                lz[j] = live ? __ldcg(pz + 1) : 0.f;
-                az[j] = live ? __ldcg(pz + 2 + d) : 0.f;
-            }
-            float Mn = M;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, mz[j]);
-            const float corr = __expf(M - Mn);
-            L *= corr;
-            A *= corr;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float w = __expf(mz[j] - Mn);
-                L += lz[j] * w;
-                A += az[j] * w;
-            }
-            M = Mn;
-        }
-        ctx[((size_t)t * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+        ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits<HD, G>(parts, splits, g, d));
     }
 }
 
-template <int HD>
+template <int HD, bool STAGED>
 bool dispatch_g(int G, dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                 const int* tok_pos, bf16* ctx, int nh, int splits, float* ws, int* counters, int* status) {
 #define TFFN_ATTN_CASE(GG)                                                                                          \
-    case GG:                                                                                                       \
-        launch_k(k_attn_decode<HD, GG>, grid, dim3(kAttnThreads), 0, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, \
-                 splits, ws, counters, status);                                                                   \
-        return true;
+    case GG: {                                                                                                     \
+        if (STAGED) {                                                                                              \
+            static bool configured = false; /* benign race: the call is idempotent */                              \
+            if (!configured) {                                                                                     \
+                cudaFuncSetAttribute(k_attn_decode<HD, GG, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                     AttnStageCfg<HD>::BYTES);                                                     \
+                configured = true;                                                                                 \
+            }                                                                                                      \
+        }                                                                                                          \
+        launch_k(k_attn_decode<HD, GG, STAGED>, grid, dim3(kAttnThreads), STAGED ? AttnStageCfg<HD>::BYTES : 0, s, pdl, q, kv, \
+                 layer, tok_seq, tok_pos, ctx, nh, splits, ws, counters, status);                                  \
+        return true;                                                                                               \
+    }
     switch (G) {
         TFFN_ATTN_CASE(1)
         TFFN_ATTN_CASE(2)
@@ -232,31 +124,50 @@ bool dispatch_g(int G, dim3 grid, cudaStream_t s, bool pdl, const float* q, cons
 
 }  // namespace
 
-int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
+AttnPlan attention_plan(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
     const int G = nh / nkv;
     const int units = T * nkv;
-    int splits = 1;
+    auto fits = [&](int s) { return (size_t)units * s * G * (hd + 2) <= ws.partial_floats && units <= ws.num_counters; };
+    AttnPlan plan{1, false};
     if (units < 2 * num_sms) {
-        splits = (2 * num_sms + units - 1) / units;
+        int splits = (2 * num_sms + units - 1) / units;
         const int max_splits = (max_ctx + 2 * kPageTokens - 1) / (2 * kPageTokens);  // at least 64 rows per split
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
-        while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))
-            --splits;
+        while (splits > 1 && !fits(splits)) --splits;
+        plan.splits = splits;
     }
-    return splits;
+    // Staged variant: every CTA copies its whole range into shared memory first, so the range must
+    // fit the staging buffer; more splits are taken for that as long as the grid stays moderate.
+    const int max_pages = hd == 64 ? AttnStageCfg<64>::MAX_PAGES : AttnStageCfg<128>::MAX_PAGES;
+    const int ctx_pages = (max_ctx + kPageTokens - 1) / kPageTokens;
+    int need = plan.splits;
+    while (((ctx_pages + need - 1) / need) > max_pages) ++need;
+    // the kernel rounds a split's range up to whole pages: ceil(ceil(ctx / need) / page) pages
+    if ((need == 1 || fits(need)) && (long long)units * need <= 16LL * num_sms) {
+        plan.splits = need;
+        plan.staged = true;
+    }
+    return plan;
 }
 
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl) {
     const int G = nh / kv.nkv;
     const int units = T * kv.nkv;
-    const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
+    const AttnPlan plan = attention_plan(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
+    const int splits = plan.splits;
     dim3 grid(units, splits);
-    bool ok = false;
-    if (kv.hd == 64) ok = dispatch_g<64>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
-    else if (kv.hd == 128) ok = dispatch_g<128>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status);
-    (void)ok;
+#define TFFN_ATTN_GO(HDV, ST) \
+    dispatch_g<HDV, ST>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status)
+    if (kv.hd == 64) {
+        if (plan.staged) TFFN_ATTN_GO(64, true);
+        else TFFN_ATTN_GO(64, false);
+    } else if (kv.hd == 128) {
+        if (plan.staged) TFFN_ATTN_GO(128, true);
+        else TFFN_ATTN_GO(128, false);
+    }
+#undef TFFN_ATTN_GO
 }
 
 }  // namespace tffn

@@ -289,6 +289,14 @@ int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int
     return rc < 0 ? rc : n;
 }
 const char* tffn_profile_class_name(int cls) { return kclass_name(cls); }
+int tffn_session_mega_trace(tffn_session* s, uint64_t* out, int max_ctas) {
+    int n = 0;
+    int rc = guard([&] {
+        need(s, "NULL session");
+        n = s->s->mega_trace(out, max_ctas);
+    });
+    return rc < 0 ? rc : n;
+}
 int tffn_session_status(tffn_session* s) {
     int st = 0;
     int rc = guard([&] {

@@ -253,6 +253,28 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     bs1_tickets_.alloc(256 * 4);
     bs1_lm_val_.alloc((size_t)m->num_sms * 2 * 4);
     bs1_lm_idx_.alloc((size_t)m->num_sms * 2 * 4);
+    mega_ok_ = m->bs1_ok && bs1_mega_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
+    if (mega_ok_) {
+        int coop = 0;
+        TFFN_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+        mega_ok_ = coop != 0;
+    }
+    if (mega_ok_) {
+        std::vector<Bs1Layer> ls(L);
+        for (size_t l = 0; l < L; ++l) {
+            const LayerWeights& lw = m->layers[l];
+            ls[l].wqkv = lw.wqkv.as<bf16>();
+            ls[l].bqkv = lw.has_bias ? lw.bqkv.as<bf16>() : nullptr;
+            ls[l].wo = lw.wo.as<bf16>();
+            ls[l].attn_norm = lw.attn_norm.as<bf16>();
+            ls[l].ffn_norm = lw.ffn_norm.as<bf16>();
+            ls[l].ffn_base = lw.ffn.packed.as<bf16>();
+            ls[l].ffn_expert = e ? e->layers[l].packed.as<bf16>() : nullptr;
+        }
+        upload(bs1_layers_dev_, ls.data(), L * sizeof(Bs1Layer));
+        mega_attn_part_.alloc(bs1_mega_attn_part_floats((int)nkv, (int)hd, (int)(nh / nkv)) * 4);
+        mega_barrier_.alloc(64);
+    }
     (void)V;
 }
 
@@ -361,7 +383,7 @@ void Session::flush_tables() {
 }
 
 void Session::set_launch_mode(int mode) {
-    if (mode < 0 || mode > 2) throw Error(kErrInvalid, "launch mode must be 0, 1 or 2");
+    if (mode < 0 || mode > 3) throw Error(kErrInvalid, "launch mode must be 0, 1, 2 or 3");
     launch_mode_ = mode;
 }
 
@@ -661,6 +683,16 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
 }
 
 void Session::run_bs1(bool want_logits) {
+    if (launch_mode_ == 3 && mega_ok_ && !profile_) {
+        // one persistent cooperative kernel per token
+        const Bs1Ctx x = bs1_ctx(want_logits);
+        const int rc = launch_bs1_mega(x, (const Bs1Layer*)bs1_layers_dev_.p, m_->cfg.num_layers, m_->embed.as<bf16>(),
+                                       m_->final_norm.as<bf16>(), m_->lm_head, kv_, mega_attn_part_.as<float>(),
+                                       (unsigned*)mega_barrier_.p, stream_);
+        if (rc != 0) cuda_check((cudaError_t)rc, "persistent batch-1 kernel launch", __FILE__, __LINE__);
+        launches_ += 1;
+        return;
+    }
     if (launch_mode_ == 2 && !profile_) {
         if (!bs1_graph_ || bs1_graph_logits_ != want_logits) {
             if (bs1_graph_) {
@@ -686,6 +718,28 @@ void Session::run_bs1(bool want_logits) {
     TFFN_CUDA(cudaGetLastError());
 }
 
+int Session::mega_trace(uint64_t* out, int max_ctas) {
+    if (!mega_ok_) throw Error(kErrUnsupported, "no persistent batch-1 kernel for this shape");
+    if (!out || max_ctas < m_->num_sms) throw Error(kErrInvalid, "trace buffer too small");
+    ensure_pages(0, h_seq_len_[0] + 1);
+    flush_tables();
+    ensure_ring(1);
+    TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
+    DeviceBuffer tr;
+    tr.alloc((size_t)max_ctas * 16 * 8);
+    Bs1Ctx x = bs1_ctx(false);
+    x.trace = tr.as<unsigned long long>();
+    const int rc = launch_bs1_mega(x, (const Bs1Layer*)bs1_layers_dev_.p, m_->cfg.num_layers, m_->embed.as<bf16>(),
+                                   m_->final_norm.as<bf16>(), m_->lm_head, kv_, mega_attn_part_.as<float>(),
+                                   (unsigned*)mega_barrier_.p, stream_);
+    if (rc != 0) cuda_check((cudaError_t)rc, "persistent batch-1 kernel launch", __FILE__, __LINE__);
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    h_seq_len_[0] += 1;
+    TFFN_CUDA(cudaMemcpy(out, tr.p, (size_t)max_ctas * 16 * 8, cudaMemcpyDeviceToHost));
+    check_status();
+    return m_->num_sms;
+}
+
 void Session::drop_graphs() {
     if (bs1_graph_) cudaGraphExecDestroy(bs1_graph_);
     bs1_graph_ = nullptr;
@@ -703,13 +757,13 @@ void Session::run_decode_batched(int n_seqs, int max_ctx) {
         prof_end();
         launches_++;
     };
-    if (launch_mode_ != 2 || profile_ || hidden_rows_cap_ > 0) {
+    if (launch_mode_ < 2 || profile_ || hidden_rows_cap_ > 0) {
         body();
         return;
     }
     const Config& c = m_->cfg;
-    const int splits = attention_splits(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms);
-    const auto key = std::make_pair(n_seqs, splits);
+    const int plan = attention_plan(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms).key();
+    const auto key = std::make_pair(n_seqs, plan);
     auto it = dec_graphs_.find(key);
     if (it == dec_graphs_.end()) {
         cudaGraph_t graph = nullptr;

@@ -70,6 +70,9 @@ const char* kclass_name(int c);
 
 class Session {
 public:
+    // one persistent-kernel batch-1 step (feeds the previous pick) with phase timestamps of layer 1:
+    // out[cta*16 + k], k = 0 layer start, then before/after each of the five grid barriers
+    int mega_trace(uint64_t* out, int max_ctas);
     void set_profile(bool on);
     // accumulated device time (ms) and launches per class since set_profile(true); returns KC_COUNT
     int read_profile(float* ms, int* counts, int cap);
@@ -124,6 +127,8 @@ private:
 
     // batch-1 path
     DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
+    DeviceBuffer bs1_layers_dev_, mega_attn_part_, mega_barrier_;  // persistent batch-1 kernel (launch mode 3)
+    bool mega_ok_ = false;
     cudaGraphExec_t bs1_graph_ = nullptr;
     bool bs1_graph_logits_ = false;
     // batched decode steps captured per (sequences, attention splits)

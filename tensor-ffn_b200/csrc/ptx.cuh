@@ -17,6 +17,7 @@ enum DevStatus : int {
     DEV_ERR_ACC_WAIT = 3,     // epilogue gave up waiting for the accumulator
     DEV_ERR_BOUNDS = 4,       // an index check failed (token id, page id, position)
     DEV_ERR_TEST_WAIT = 5,    // the deliberate never-signalled wait of the self-test
+    DEV_ERR_GRID_WAIT = 6,    // a grid barrier of the persistent batch-1 kernel ran out of polls
 };
 
 constexpr uint32_t kSpinLimit = 1u << 22;

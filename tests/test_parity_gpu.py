@@ -60,7 +60,7 @@ def test_bs1_decode_path_teacher_forced(model_dirs, name, expert):
     m, e, s, o, cfg = _mk(model_dirs, name, expert)
     toks = synth.prompts(1, 40, 7, cfg["vocab_size"])[0]
     ref = o.forward(toks)["logits"]
-    for mode in (0, 1, 2):
+    for mode in (0, 1, 2, 3):  # 3 = one persistent kernel per token where the shape has an instantiation
         s.qwen_reset()
         s.set_launch_mode(mode)
         ours = []
@@ -153,7 +153,7 @@ def test_batched_decode_many_sequences(model_dirs, n_seqs):
 def test_decode_run_is_deterministic_and_matches_stepwise(model_dirs):
     """device-resident multi-step decode == step-by-step decode, bit-identical tokens, both paths"""
     import synth
-    for n_seqs, mode in ((1, 1), (4, 1), (1, 2), (4, 2)):
+    for n_seqs, mode in ((1, 1), (4, 1), (1, 2), (4, 2), (1, 3)):
         m, e, s, o, cfg = _mk(model_dirs, "tiny", True, max_batch=4, max_seq=128)
         s.set_launch_mode(mode)
         prompts = [synth.prompts(1, 11 + i, 200 + i, cfg["vocab_size"])[0] for i in range(n_seqs)]
