@@ -111,6 +111,11 @@ int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */
  * 3: 2, and batch-1 steps run as ONE persistent cooperative kernel per token where the shape has an
  *    instantiation (otherwise as in 2). Default 1. */
 int tffn_session_set_launch_mode(tffn_session* s, int mode);
+/* Timing aid: kernel classes (bit i = class i of tffn_profile_class_name) that the batched path
+ * skips from now on. The step then computes garbage; the drop in step time is what that class costs
+ * inside the overlapped (dependent-launch, graph) schedule, which per-kernel events cannot show.
+ * 0 restores normal operation. */
+int tffn_session_set_ablation(tffn_session* s, unsigned mask);
 /* Which path single-token steps take: 1 (default) the fused batch-1 kernels when the shape
  * allows, 0 the batched tensor-core path. */
 int tffn_session_set_bs1_path(tffn_session* s, int enable);

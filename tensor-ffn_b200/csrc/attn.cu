@@ -4,11 +4,18 @@
 // Reference arithmetic (inference/src/model/qwen.cu:349-412): scores = (q . k) / sqrt(hd) with
 // q in fp32 and k in bf16, softmax with max-subtraction and exp (cuda_ops.cu:106-126),
 // ctx = P V, ctx rounded to bf16; query head qh reads kv head qh * nkv / nh (qwen.cu:252).
-// The reference re-expands the whole cache to fp32 per layer and materialises the score
-// matrix; here one CTA per (token, kv head, context split) reads each K/V row once (16-byte
-// loads, hd/8 lanes per row) and shares it between the G = nh / nkv query heads of the group,
-// with an online softmax in fp32. Splits are merged by the last split to finish (a ticket,
-// no spinning), always in split order, so the result does not depend on scheduling.
+// The reference re-expands the whole cache to fp32 per layer and materialises the score matrix.
+//
+// Here one CTA per (token, kv head, context split) copies its K/V rows once into shared memory
+// (16-byte cp.async, two stages in flight, XOR-swizzled so that ldmatrix is conflict-free) and shares
+// them between the G = nh / nkv query heads of the group, which form the M dimension of warp-level
+// tensor-core tiles: S = Q K^T and O = P V as mma.sync m16n8k16 (bf16 operands, fp32 accumulate).
+// G is at most 8, so the 16-row tile is the natural fit: a tcgen05 tile (M >= 64) would be 89%
+// padding and put a TMEM round trip between the two contractions of a kernel that is bound by the
+// latency of its loads, not by tensor throughput. q and P are fp32 in the reference; each enters the
+// MMA as a bf16 pair (hi + lo, two MMAs), which keeps 16 mantissa bits of them. The softmax is the
+// online form in fp32, per 32- or 16-key block of a warp. Splits are merged by the last split to finish
+// (a ticket, no spinning), always in split order, so the result does not depend on scheduling.
 #include "kernels.h"
 #include "ptx.cuh"
 #include "launch.h"
@@ -18,19 +25,62 @@ namespace tffn {
 
 namespace {
 
-template <int HD, int G, bool STAGED>
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col); rows 8..15 of A are zero (a1 = a3 = 0)
+__device__ __forceinline__ void mma_16816_top(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// (x, y) as two bf16 pairs: hi = bf16(v), lo = bf16(v - hi); x in the low half (the lower k index)
+__device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+    hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+    lo = (uint32_t)bf16_bits(x - __bfloat162float(xh)) | ((uint32_t)bf16_bits(y - __bfloat162float(yh)) << 16);
+}
+
+template <int HD>
+struct AttnCfg {
+    static constexpr int ROW_BYTES = HD * 2;
+    static constexpr int GRAN = HD / 8;                // 16-byte granules per cached row
+    static constexpr int STAGE_ROWS = 8192 / HD;       // 16 KB of K and of V per stage: 128 rows at hd 64
+    static constexpr int WARP_ROWS = STAGE_ROWS / 4;   // rows of a stage per warp: 32 or 16
+    static constexpr int NT = WARP_ROWS / 8;           // 8-key tiles of S per warp and stage
+    static constexpr int KB = WARP_ROWS / 16;          // 16-key steps of P V
+    static constexpr int KS = HD / 16;                 // k-steps of Q K^T
+    static constexpr int DT = HD / 8;                  // 8-wide tiles of the output row
+    static constexpr int STAGE_BYTES = 2 * STAGE_ROWS * ROW_BYTES;  // K then V
+    static constexpr int MERGE_FLOATS = 4 * 8 * (HD + 2);           // per warp and head: max, sum, O[HD]
+    static constexpr int SMEM = 2 * STAGE_BYTES + MERGE_FLOATS * 4;
+};
+
+template <int HD>
 __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
                                                               const int* __restrict__ tok_seq,
                                                               const int* __restrict__ tok_pos, bf16* __restrict__ ctx,
-                                                              int nh, int splits, float* __restrict__ ws,
+                                                              int nh, int G, int splits, float* __restrict__ ws,
                                                               int* __restrict__ counters, int* status) {
-    __shared__ AttnShared<HD, G> sh;
+    using C = AttnCfg<HD>;
+    extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
-    extern __shared__ __align__(128) uint8_t stage_raw[];  // STAGED: K pages | V pages | mbarrier
+    float* merge = (float*)(smem + 2 * C::STAGE_BYTES);  // [warp][head][HD + 2]
 
     pdl_launch_dependents();
     pdl_wait();
 
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x;  // t * nkv + kvh
     const int nkv = kv.nkv;
     const int t = unit / nkv, kvh = unit % nkv;
@@ -41,42 +91,179 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     chunk = (chunk + kPageTokens - 1) / kPageTokens * kPageTokens;
     const int c_begin = split * chunk;
     const int c_end = min(ctx_len, c_begin + chunk);
+    const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
+    const bf16* kpool = kv.k_pool + (size_t)layer * kv.layer_stride;
+    const bf16* vpool = kv.v_pool + (size_t)layer * kv.layer_stride;
+    const uint32_t smem_base = smem_u32(smem);
+    bool bad = false;
+
+    // Copy of one stage: every thread moves GRAN * STAGE_ROWS / 128 granules of K and of V. Rows past
+    // the end of the range (or of a bad page) are zero-filled: their P is 0, and 0 * garbage could be NaN.
+    auto issue_stage = [&](int st) {
+        const int s_begin = c_begin + st * C::STAGE_ROWS;
+        const uint32_t kbuf = smem_base + (uint32_t)((st & 1) * C::STAGE_BYTES);
+        const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+        if (s_begin < c_end) {
+#pragma unroll
+            for (int i = 0; i < C::GRAN * C::STAGE_ROWS / kAttnThreads; ++i) {
+                const int idx = i * kAttnThreads + tid;
+                const int row = idx / C::GRAN, g = idx % C::GRAN;
+                const int tok = s_begin + row;
+                bool valid = tok < c_end;
+                int pg = 0;
+                if (valid) {
+                    pg = __ldcg(bt + tok / kPageTokens);
+                    if (pg < 0 || pg >= kv.num_pages) { bad = true; valid = false; pg = 0; }
+                }
+                const size_t off = (((size_t)pg * nkv + kvh) * kPageTokens + (valid ? tok % kPageTokens : 0)) * HD + g * 8;
+                const uint32_t dst = (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4));
+                cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
+                cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    const int n_stages = c_end > c_begin ? (c_end - c_begin + C::STAGE_ROWS - 1) / C::STAGE_ROWS : 0;
+    issue_stage(0);
+    issue_stage(1);
+
+    // Q fragments (A operand, rows = query heads of the group; rows >= G are zero): per k-step the
+    // pairs at k = (lane % 4) * 2 and k + 8 of head lane / 4, each as hi and lo bf16.
+    const int hrow = lane >> 2, quad = lane & 3;
+    uint32_t qh[C::KS][2], ql[C::KS][2];
+    {
+        const float* qp = q + (size_t)t * nh * HD + (size_t)(kvh * G + hrow) * HD + quad * 2;
+#pragma unroll
+        for (int ks = 0; ks < C::KS; ++ks) {
+            float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+            if (hrow < G) {
+                a = __ldcg((const float2*)(qp + ks * 16));
+                b = __ldcg((const float2*)(qp + ks * 16 + 8));
+            }
+            split_bf16x2(a.x, a.y, qh[ks][0], ql[ks][0]);
+            split_bf16x2(b.x, b.y, qh[ks][1], ql[ks][1]);
+        }
+    }
+    const float scale = rsqrtf((float)HD);
+    float m_run = kNegBig, l_run = 0.f;  // of head hrow; l_run is this thread's share (summed over the quad at the end)
+    float o[C::DT][4];
+#pragma unroll
+    for (int d = 0; d < C::DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    for (int st = 0; st < n_stages; ++st) {
+        if (st + 1 < n_stages) cp_async_wait<1>();
+        else cp_async_wait<0>();
+        __syncthreads();
+        const int w_begin = c_begin + st * C::STAGE_ROWS + warp * C::WARP_ROWS;  // first key of this warp
+        if (w_begin < c_end) {
+            const uint32_t kbuf = smem_base + (uint32_t)((st & 1) * C::STAGE_BYTES);
+            const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+            // ---- S = Q K^T for WARP_ROWS keys: NT tiles of 8 keys
+            float s[C::NT][4];
+#pragma unroll
+            for (int nt = 0; nt < C::NT; ++nt) {
+                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+                const int row = warp * C::WARP_ROWS + nt * 8 + (lane & 7);  // this lane's address row for ldmatrix
+#pragma unroll
+                for (int kp = 0; kp < C::KS / 2; ++kp) {
+                    uint32_t b[4];  // B fragments of k-steps 2kp and 2kp + 1 (matrix i = granule 4kp + i)
+                    const int g = kp * 4 + (lane >> 3);
+                    ldmatrix_x4(kbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
+                    mma_16816_top(s[nt], qh[2 * kp][0], qh[2 * kp][1], b[0], b[1]);
+                    mma_16816_top(s[nt], ql[2 * kp][0], ql[2 * kp][1], b[0], b[1]);
+                    mma_16816_top(s[nt], qh[2 * kp + 1][0], qh[2 * kp + 1][1], b[2], b[3]);
+                    mma_16816_top(s[nt], ql[2 * kp + 1][0], ql[2 * kp + 1][1], b[2], b[3]);
+                }
+            }
+            // ---- online softmax of head hrow over these keys (this thread: keys nt * 8 + quad * 2 + {0, 1})
+            float mx = kNegBig;
+#pragma unroll
+            for (int nt = 0; nt < C::NT; ++nt) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const bool live = w_begin + nt * 8 + quad * 2 + j < c_end;
+                    s[nt][j] = live ? s[nt][j] * scale : kNegBig;
+                    mx = fmaxf(mx, s[nt][j]);
+                }
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m_run, mx);  // finite: the first key of the warp's rows is in range
+            const float corr = __expf(m_run - mn);
+            m_run = mn;
+            l_run *= corr;
+#pragma unroll
+            for (int d = 0; d < C::DT; ++d) { o[d][0] *= corr; o[d][1] *= corr; }
+            uint32_t ph[C::NT], pl[C::NT];
+#pragma unroll
+            for (int nt = 0; nt < C::NT; ++nt) {
+                const float p0 = (w_begin + nt * 8 + quad * 2 < c_end) ? __expf(s[nt][0] - mn) : 0.f;
+                const float p1 = (w_begin + nt * 8 + quad * 2 + 1 < c_end) ? __expf(s[nt][1] - mn) : 0.f;
+                l_run += p0 + p1;
+                split_bf16x2(p0, p1, ph[nt], pl[nt]);
+            }
+            // ---- O += P V: per 16 keys, per pair of 8-wide output tiles one transposed ldmatrix of V
+#pragma unroll
+            for (int kb = 0; kb < C::KB; ++kb) {
+                const int row = warp * C::WARP_ROWS + kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+                for (int jp = 0; jp < C::DT / 2; ++jp) {
+                    uint32_t b[4];  // keys 0-7 / 8-15 of tile 2jp, then of tile 2jp + 1
+                    const int g = jp * 2 + (lane >> 4);
+                    ldmatrix_x4_trans(vbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
+                    mma_16816_top(o[2 * jp], ph[2 * kb], ph[2 * kb + 1], b[0], b[1]);
+                    mma_16816_top(o[2 * jp], pl[2 * kb], pl[2 * kb + 1], b[0], b[1]);
+                    mma_16816_top(o[2 * jp + 1], ph[2 * kb], ph[2 * kb + 1], b[2], b[3]);
+                    mma_16816_top(o[2 * jp + 1], pl[2 * kb], pl[2 * kb + 1], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();  // every warp is done with this buffer
+        if (st + 2 < n_stages) issue_stage(st + 2);
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps: (max, sum, O) of head hrow per warp
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    {
+        float* mw = merge + (size_t)(warp * 8 + hrow) * (HD + 2);
+        if (quad == 0) { mw[0] = m_run; mw[1] = l_run; }
+#pragma unroll
+        for (int d = 0; d < C::DT; ++d) {
+            mw[2 + d * 8 + quad * 2] = o[d][0];
+            mw[2 + d * 8 + quad * 2 + 1] = o[d][1];
+        }
+    }
+    __syncthreads();
     float* part = ws + ((size_t)unit * splits + split) * (size_t)(G * (HD + 2));
     bf16* ctx_tok = ctx + (size_t)t * nh * HD;
-    const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
-    bf16* ks = (bf16*)stage_raw;
-    bf16* vs = ks + AttnStageCfg<HD>::MAX_PAGES * AttnStageCfg<HD>::PAGE_ELEMS;
-    bool stage_bad = false;
-    if (STAGED) {
-        // all K/V rows of this CTA's range are requested up front (one bulk copy per page and pool)
-        uint64_t* bar = (uint64_t*)(stage_raw + AttnStageCfg<HD>::BYTES - 16);
-        if (threadIdx.x == 0) {
-            mbar_init(bar, 1);
-            fence_mbar_init();
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx % HD;
+        float M = kNegBig;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, merge[(size_t)(w * 8 + g) * (HD + 2)]);
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* mw = merge + (size_t)(w * 8 + g) * (HD + 2);
+            const float wgt = __expf(mw[0] - M);
+            L += mw[1] * wgt;
+            A += mw[2 + d] * wgt;
         }
-        __syncthreads();
-        if (threadIdx.x < 32) stage_bad = !attn_stage_pages<HD>(kv, layer, bt, kvh, c_begin, c_end, ks, vs, bar, (int)threadIdx.x);
-        if (!mbar_wait(bar, 0, status, DEV_ERR_FULL_WAIT)) stage_bad = true;
-        stage_bad = __syncthreads_or(stage_bad);
+        if (splits == 1) {
+            ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+        } else {
+            part[g * (HD + 2) + 2 + d] = A;
+            if (d == 0) { part[g * (HD + 2)] = M; part[g * (HD + 2) + 1] = L; }
+        }
     }
-    const bool bad = attn_range<HD, G, STAGED>(
-        q + (size_t)t * nh * HD, kv, layer, bt, kvh, c_begin, stage_bad ? c_begin : c_end,
-        (int)threadIdx.x, sh, [] { __syncthreads(); },
-        [&](int g, int d, float M, float L, float A) {
-            if (splits == 1) {
-                ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
-            } else {
-                part[g * (HD + 2) + 2 + d] = A;
-                if (d == 0) { part[g * (HD + 2)] = M; part[g * (HD + 2) + 1] = L; }
-            }
-        },
-        ks, vs);
-    if (bad || stage_bad) dev_fail(status, DEV_ERR_BOUNDS);
+    if (bad) dev_fail(status, DEV_ERR_BOUNDS);
     if (splits == 1) return;
 
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         const int old = atomicAdd(&counters[unit], 1);
         s_last = (old == splits - 1);
         if (old == splits - 1) counters[unit] = 0;
@@ -85,89 +272,49 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     if (!s_last) return;
     __threadfence();
     const float* parts = ws + (size_t)unit * splits * (size_t)(G * (HD + 2));
-    for (int idx = threadIdx.x; idx < G * HD; idx += kAttnThreads) {
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx % HD;
-        ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits<HD, G>(parts, splits, g, d));
+        ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits(parts, splits, G, HD, g, d));
     }
 }
 
-template <int HD, bool STAGED>
-bool dispatch_g(int G, dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
-                const int* tok_pos, bf16* ctx, int nh, int splits, float* ws, int* counters, int* status) {
-#define TFFN_ATTN_CASE(GG)                                                                                          \
-    case GG: {                                                                                                     \
-        if (STAGED) {                                                                                              \
-            static bool configured = false; /* benign race: the call is idempotent */                              \
-            if (!configured) {                                                                                     \
-                cudaFuncSetAttribute(k_attn_decode<HD, GG, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                     AttnStageCfg<HD>::BYTES);                                                     \
-                configured = true;                                                                                 \
-            }                                                                                                      \
-        }                                                                                                          \
-        launch_k(k_attn_decode<HD, GG, STAGED>, grid, dim3(kAttnThreads), STAGED ? AttnStageCfg<HD>::BYTES : 0, s, pdl, q, kv, \
-                 layer, tok_seq, tok_pos, ctx, nh, splits, ws, counters, status);                                  \
-        return true;                                                                                               \
+template <int HD>
+void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
+               const int* tok_pos, bf16* ctx, int nh, int G, int splits, float* ws, int* counters, int* status) {
+    static bool configured = false;  // benign race: the call is idempotent
+    if (!configured) {
+        cudaFuncSetAttribute(k_attn_decode<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
+        configured = true;
     }
-    switch (G) {
-        TFFN_ATTN_CASE(1)
-        TFFN_ATTN_CASE(2)
-        TFFN_ATTN_CASE(3)
-        TFFN_ATTN_CASE(4)
-        TFFN_ATTN_CASE(5)
-        TFFN_ATTN_CASE(6)
-        TFFN_ATTN_CASE(7)
-        TFFN_ATTN_CASE(8)
-    }
-#undef TFFN_ATTN_CASE
-    return false;
+    launch_k(k_attn_decode<HD>, grid, dim3(kAttnThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
+             nh, G, splits, ws, counters, status);
 }
 
 }  // namespace
 
-AttnPlan attention_plan(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
+int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
     const int G = nh / nkv;
     const int units = T * nkv;
-    auto fits = [&](int s) { return (size_t)units * s * G * (hd + 2) <= ws.partial_floats && units <= ws.num_counters; };
-    AttnPlan plan{1, false};
+    int splits = 1;
     if (units < 2 * num_sms) {
-        int splits = (2 * num_sms + units - 1) / units;
+        splits = (2 * num_sms + units - 1) / units;
         const int max_splits = (max_ctx + 2 * kPageTokens - 1) / (2 * kPageTokens);  // at least 64 rows per split
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
-        while (splits > 1 && !fits(splits)) --splits;
-        plan.splits = splits;
+        while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))
+            --splits;
     }
-    // Staged variant: every CTA copies its whole range into shared memory first, so the range must
-    // fit the staging buffer; more splits are taken for that as long as the grid stays moderate.
-    const int max_pages = hd == 64 ? AttnStageCfg<64>::MAX_PAGES : AttnStageCfg<128>::MAX_PAGES;
-    const int ctx_pages = (max_ctx + kPageTokens - 1) / kPageTokens;
-    int need = plan.splits;
-    while (((ctx_pages + need - 1) / need) > max_pages) ++need;
-    // the kernel rounds a split's range up to whole pages: ceil(ceil(ctx / need) / page) pages
-    if ((need == 1 || fits(need)) && (long long)units * need <= 16LL * num_sms) {
-        plan.splits = need;
-        plan.staged = true;
-    }
-    return plan;
+    return splits;
 }
 
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl) {
-    const int G = nh / kv.nkv;
+    const int G = nh / kv.nkv;  // at most 8 (checked when the model is loaded)
     const int units = T * kv.nkv;
-    const AttnPlan plan = attention_plan(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
-    const int splits = plan.splits;
+    const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
     dim3 grid(units, splits);
-#define TFFN_ATTN_GO(HDV, ST) \
-    dispatch_g<HDV, ST>(G, grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, splits, ws.partials, ws.counters, status)
-    if (kv.hd == 64) {
-        if (plan.staged) TFFN_ATTN_GO(64, true);
-        else TFFN_ATTN_GO(64, false);
-    } else if (kv.hd == 128) {
-        if (plan.staged) TFFN_ATTN_GO(128, true);
-        else TFFN_ATTN_GO(128, false);
-    }
-#undef TFFN_ATTN_GO
+    if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, ws.partials, ws.counters, status);
+    else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, ws.partials, ws.counters, status);
 }
 
 }  // namespace tffn

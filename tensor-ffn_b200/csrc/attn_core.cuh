@@ -1,5 +1,6 @@
-// Core of the paged GQA decode attention, shared by k_attn_decode (attn.cu) and the persistent
-// batch-1 kernel: 128 threads process the cached rows [c_begin, c_end) of one (token, kv head) and
+// Paged GQA decode attention on the CUDA cores, used by the persistent batch-1 kernel (whose
+// 128-thread groups process one context split each), and the merge of context splits that
+// k_attn_decode (attn.cu) shares with it: 128 threads process the cached rows [c_begin, c_end) of one (token, kv head) and
 // hand the merged (max, sum, weighted V) of every (query head of the group, dim) to `out`.
 // Arithmetic follows inference/src/model/qwen.cu:349-412 (see attn.cu).
 #pragma once
@@ -21,13 +22,10 @@ struct AttnShared {
 
 // tid in [0, 128); sync() must be a barrier over exactly those 128 threads; q_tok = fp32 q of this
 // token [nh * HD]; bt = the sequence's block-table row. Returns true if a page id was out of range.
-// With STAGED the rows of [c_begin, c_end) were copied page by page into shared memory beforehand
-// (ks / vs: row r of the range at r * HD, see attn_stage_pages) and are read from there.
-template <int HD, int G, bool STAGED = false, typename SyncFn, typename OutFn>
+template <int HD, int G, typename SyncFn, typename OutFn>
 __device__ __forceinline__ bool attn_range(const float* __restrict__ q_tok, const KvView& kv, int layer,
                                            const int* __restrict__ bt, int kvh, int c_begin, int c_end, int tid,
-                                           AttnShared<HD, G>& sh, SyncFn sync, OutFn out, const bf16* ks = nullptr,
-                                           const bf16* vs = nullptr) {
+                                           AttnShared<HD, G>& sh, SyncFn sync, OutFn out) {
     constexpr int LPT = AttnShared<HD, G>::LPT;
     constexpr int NG = AttnShared<HD, G>::NG;
     const int grp = tid / LPT, sub = tid % LPT;
@@ -66,7 +64,7 @@ __device__ __forceinline__ bool attn_range(const float* __restrict__ q_tok, cons
         for (int u = 0; u < U; ++u) {
             const int tok = base + u * NG + grp;
             valid[u] = tok < c_end;
-            pg[u] = (valid[u] && !STAGED) ? __ldcg(bt + tok / kPageTokens) : 0;
+            pg[u] = valid[u] ? __ldcg(bt + tok / kPageTokens) : 0;
         }
         uint4 kk[U], vv[U];
 #pragma unroll
@@ -76,15 +74,9 @@ __device__ __forceinline__ bool attn_range(const float* __restrict__ q_tok, cons
             kk[u] = make_uint4(0, 0, 0, 0);
             vv[u] = make_uint4(0, 0, 0, 0);
             if (valid[u]) {
-                if (STAGED) {
-                    const size_t off = (size_t)(tok - c_begin) * HD + sub * 8;
-                    kk[u] = *(const uint4*)(ks + off);
-                    vv[u] = *(const uint4*)(vs + off);
-                } else {
-                    const size_t off = (((size_t)pg[u] * nkv + kvh) * kPageTokens + tok % kPageTokens) * HD + sub * 8;
-                    kk[u] = __ldcg((const uint4*)(kpool + off));
-                    vv[u] = __ldcg((const uint4*)(vpool + off));
-                }
+                const size_t off = (((size_t)pg[u] * nkv + kvh) * kPageTokens + tok % kPageTokens) * HD + sub * 8;
+                kk[u] = __ldcg((const uint4*)(kpool + off));
+                vv[u] = __ldcg((const uint4*)(vpool + off));
             }
         }
 #pragma unroll
@@ -149,52 +141,18 @@ __device__ __forceinline__ bool attn_range(const float* __restrict__ q_tok, cons
     return bad;
 }
 
-// Pages a CTA may stage (K and V each): 64 KB of dynamic shared memory in total, so that two CTAs
-// still share an SM next to the merge buffers.
-template <int HD>
-struct AttnStageCfg {
-    static constexpr int PAGE_ELEMS = kPageTokens * HD;
-    static constexpr int MAX_PAGES = 32 * 1024 / (PAGE_ELEMS * 2);  // 8 at head_dim 64, 4 at 128
-    static constexpr int BYTES = 2 * MAX_PAGES * PAGE_ELEMS * 2 + 16;
-};
-
-// Called by warp 0 (all 32 lanes) after `bar` was initialised with count 1 and made visible:
-// requests every page of [c_begin, c_end) for one kv head as one contiguous bulk copy per page and
-// pool. c_begin is a multiple of the page size. Returns false on a bad page id / too many pages.
-template <int HD>
-__device__ __forceinline__ bool attn_stage_pages(const KvView& kv, int layer, const int* __restrict__ bt, int kvh, int c_begin,
-                                                 int c_end, bf16* ks, bf16* vs, uint64_t* bar, int lane) {
-    using C = AttnStageCfg<HD>;
-    const int p0 = c_begin / kPageTokens;
-    const int np = c_end > c_begin ? (c_end - c_begin + kPageTokens - 1) / kPageTokens : 0;
-    int pg = 0;
-    bool ok = np <= C::MAX_PAGES;
-    if (lane < np && ok) {
-        pg = __ldcg(bt + p0 + lane);
-        if (pg < 0 || pg >= kv.num_pages) ok = false;
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (lane == 0) mbar_arrive_expect_tx(bar, ok ? (uint32_t)(np * 2 * C::PAGE_ELEMS * 2) : 0u);
-    __syncwarp();
-    if (ok && lane < np) {
-        const size_t src = (size_t)layer * kv.layer_stride + ((size_t)pg * kv.nkv + kvh) * (size_t)C::PAGE_ELEMS;
-        bulk_g2s(ks + (size_t)lane * C::PAGE_ELEMS, kv.k_pool + src, (uint32_t)(C::PAGE_ELEMS * 2), bar);
-        bulk_g2s(vs + (size_t)lane * C::PAGE_ELEMS, kv.v_pool + src, (uint32_t)(C::PAGE_ELEMS * 2), bar);
-    }
-    return ok;
-}
-
 // merge of `splits` partial results laid out [split][G][HD + 2] = (max, sum, weighted V[HD]) for one
 // (query head g, dim d); all loads of a round of R splits are in flight together
-template <int HD, int G, int R = 8>
-__device__ __forceinline__ float attn_merge_splits(const float* __restrict__ parts, int splits, int g, int d) {
+template <int R = 8>
+__device__ __forceinline__ float attn_merge_splits(const float* __restrict__ parts, int splits, int G, int HD, int g, int d) {
     float M = kNegBig, L = 0.f, A = 0.f;
+    const size_t stride = (size_t)G * (HD + 2);
     for (int z0 = 0; z0 < splits; z0 += R) {
         float mz[R], lz[R], az[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
             const bool live = z0 + j < splits;
-            const float* pz = parts + (size_t)(live ? z0 + j : 0) * G * (HD + 2) + g * (HD + 2);
+            const float* pz = parts + (size_t)(live ? z0 + j : 0) * stride + g * (HD + 2);
             mz[j] = live ? __ldcg(pz) : kNegBig;
             lz[j] = live ? __ldcg(pz + 1) : 0.f;
             az[j] = live ? __ldcg(pz + 2 + d) : 0.f;
@@ -214,6 +172,10 @@ __device__ __forceinline__ float attn_merge_splits(const float* __restrict__ par
         M = Mn;
     }
     return A / L;
+}
+template <int HD, int G, int R = 8>
+__device__ __forceinline__ float attn_merge_splits(const float* __restrict__ parts, int splits, int g, int d) {
+    return attn_merge_splits<R>(parts, splits, G, HD, g, d);
 }
 
 }  // namespace tffn

@@ -229,6 +229,12 @@ int tffn_session_set_launch_mode(tffn_session* s, int mode) {
         s->s->set_launch_mode(mode);
     });
 }
+int tffn_session_set_ablation(tffn_session* s, unsigned mask) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_ablation(mask);
+    });
+}
 int tffn_session_set_bs1_path(tffn_session* s, int enable) {
     return guard([&] {
         need(s, "NULL session");

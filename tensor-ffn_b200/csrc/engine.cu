@@ -387,6 +387,13 @@ void Session::set_launch_mode(int mode) {
     launch_mode_ = mode;
 }
 
+void Session::set_ablation(unsigned mask) {
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    for (auto& kv : dec_graphs_) cudaGraphExecDestroy(kv.second.exec);
+    dec_graphs_.clear();
+    ablate_mask_ = mask;
+}
+
 void Session::capture_hidden(int max_rows) {
     if (max_rows < 0) throw Error(kErrInvalid, "max_rows must be >= 0");
     TFFN_CUDA(cudaStreamSynchronize(stream_));
@@ -493,7 +500,10 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     int* status = status_.as<int>();
     const GemmWorkspace gws = gemm_ws();
     const bool pdl = launch_mode_ >= 1 && !profile_;
+    // timing-only ablation: a class in the mask is not launched (results are then meaningless)
+    auto live = [&](int cls) { return ((ablate_mask_ >> cls) & 1u) == 0; };
     auto gemm = [&](GemmCall& call, int cls) {
+        if (!live(cls)) return;
         call.pdl = pdl;
         prof_begin(cls);
         int rc = launch_gemm(call, gws, stream_);
@@ -509,7 +519,8 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     for (int l = 0; l < c.num_layers; ++l) {
         const LayerWeights& ly = m_->layers[l];
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
+        if (live(KC_RMSNORM))
+            launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
         prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
@@ -539,8 +550,9 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         gemm(g, KC_GEMM_QKV);
         g.qkv = nullptr;
         prof_begin(KC_ATTENTION);
-        launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
-                         status, stream_, pdl);
+        if (live(KC_ATTENTION))
+            launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
+                             status, stream_, pdl);
         prof_end();
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
@@ -550,7 +562,8 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.ldo = H;
         gemm(g, KC_GEMM_OPROJ);
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
+        if (live(KC_RMSNORM))
+            launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
         prof_end();
         launches_ += 3;
         // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records; the expert's
@@ -612,7 +625,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.ldo = V;
         gemm(g, KC_GEMM_LMHEAD);
         prof_begin(KC_ARGMAX);
-        launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_, pdl);
+        if (live(KC_ARGMAX)) launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_, pdl);
         prof_end();
         launches_ += 2;
     }
@@ -762,8 +775,8 @@ void Session::run_decode_batched(int n_seqs, int max_ctx) {
         return;
     }
     const Config& c = m_->cfg;
-    const int plan = attention_plan(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms).key();
-    const auto key = std::make_pair(n_seqs, plan);
+    const int splits = attention_splits(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms);
+    const auto key = std::make_pair(n_seqs, splits);
     auto it = dec_graphs_.find(key);
     if (it == dec_graphs_.end()) {
         cudaGraph_t graph = nullptr;

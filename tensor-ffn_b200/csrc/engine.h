@@ -85,6 +85,8 @@ public:
     void decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_tokens, float* logits);
     void decode_run(int n_seqs, int steps, int32_t* tokens_out);
     void set_launch_mode(int mode);
+    // timing-only: kernel classes (bit = KClass) that the batched path does not launch
+    void set_ablation(unsigned mask);
     void set_bs1_path(bool on) { use_bs1_ = on; }
     void capture_hidden(int max_rows);
     int get_hidden(int layer, uint16_t* dst, int max_rows);
@@ -101,6 +103,7 @@ private:
     cudaStream_t stream_;
     bool own_stream_ = false;
     int launch_mode_ = 1;
+    unsigned ablate_mask_ = 0;
     bool use_bs1_ = true;
     uint64_t launches_ = 0;
 

@@ -98,14 +98,8 @@ struct AttnWorkspace {
     int* counters;    // [T*nkv]
     int num_counters;
 };
-// What launch_attention will launch for these sizes (a CUDA-graph key: grid and kernel depend on it):
-// context splits, and whether each CTA stages its K/V range in shared memory with bulk copies.
-struct AttnPlan {
-    int splits;
-    bool staged;
-    int key() const { return splits * 2 + (staged ? 1 : 0); }
-};
-AttnPlan attention_plan(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
+// context splits launch_attention will use (a CUDA-graph key: the grid depends on it)
+int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
 // one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t]
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl = false);

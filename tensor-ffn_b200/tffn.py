@@ -73,6 +73,7 @@ _SIGS = {
     "tffn_session_reset": (_i, [_vp, _i]),
     "tffn_session_seq_len": (_i, [_vp, _i]),
     "tffn_session_set_launch_mode": (_i, [_vp, _i]),
+    "tffn_session_set_ablation": (_i, [_vp, ctypes.c_uint]),
     "tffn_session_set_bs1_path": (_i, [_vp, _i]),
     "tffn_session_capture_hidden": (_i, [_vp, _i]),
     "tffn_session_get_hidden": (_i, [_vp, _i, _vp, _i]),
@@ -200,7 +201,8 @@ class ExpertModel:
             self._h = None
 
     def __del__(self):
-        self.free()
+        if _L is not None:  # module globals are gone at interpreter shutdown
+            self.free()
 
 
 class QwenModel:
@@ -221,7 +223,8 @@ class QwenModel:
             self._h = None
 
     def __del__(self):
-        self.free()
+        if _L is not None:  # module globals are gone at interpreter shutdown
+            self.free()
 
 
 def qwen_load(model_dir: str, device: int = 0) -> QwenModel:
@@ -256,7 +259,8 @@ class Session:
             self._h = None
 
     def __del__(self):
-        self.free()
+        if _L is not None:  # module globals are gone at interpreter shutdown
+            self.free()
 
     def qwen_reset(self, slot: int = -1):
         """qwen_reset (inference/src/model/qwen.cu:174)"""
@@ -267,6 +271,10 @@ class Session:
 
     def set_launch_mode(self, mode: int):
         _check(_L.tffn_session_set_launch_mode(self._h, mode))
+
+    def set_ablation(self, mask: int):
+        """timing aid: skip the kernel classes whose bit is set (results become meaningless)"""
+        _check(_L.tffn_session_set_ablation(self._h, mask))
 
     def set_bs1_path(self, on: bool):
         _check(_L.tffn_session_set_bs1_path(self._h, int(on)))
