@@ -152,6 +152,16 @@ uint64_t tffn_session_launch_count(const tffn_session* s);
 int tffn_session_profile(tffn_session* s, int enable);
 int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int cap);
 const char* tffn_profile_class_name(int cls);
+/* Profiling aid (no counterpart in the reference): runs three batched decode steps of slots
+ * 0..n_seqs-1 in the session's launch mode (the sequences advance by three tokens) and reports the
+ * timeline of the last one. out[i*7] = kernel class of launch i (tffn_profile_class_name), then the
+ * minimum and maximum over the launch's CTAs of: kernel entry, return from the grid-dependency wait,
+ * exit (globaltimer, ns). Unlike per-kernel events this shows the overlapped schedule as it runs.
+ * If trace_out is not NULL and launch number trace_launch is a tensor-core GEMM of at most trace_ctas
+ * CTAs, trace_out[cta*64 + k] receives that launch's per-CTA phase timestamps (k as documented for
+ * tffn_op_gemm_trace). Returns the number of launches (at most max_launches are recorded). */
+int tffn_session_timeline(tffn_session* s, int n_seqs, uint64_t* out, int max_launches, int trace_launch,
+                          uint64_t* trace_out, int trace_ctas);
 /* Profiling aid (no counterpart in the reference): runs ONE batch-1 decode step of slot 0 on the
  * persistent kernel, feeding the slot's previous pick, and returns per-CTA device timestamps
  * (globaltimer, ns) of layer 1 in out[cta*16 + k]: k = 0 layer start, 1/2 before/after the barrier that

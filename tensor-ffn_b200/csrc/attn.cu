@@ -13,7 +13,8 @@
 // G is at most 8, so the 16-row tile is the natural fit: a tcgen05 tile (M >= 64) would be 89%
 // padding and put a TMEM round trip between the two contractions of a kernel that is bound by the
 // latency of its loads, not by tensor throughput. q and P are fp32 in the reference; each enters the
-// MMA as a bf16 pair (hi + lo, two MMAs), which keeps 16 mantissa bits of them. The softmax is the
+// MMA as a bf16 pair (hi + lo, 16 mantissa bits): hi in tile rows 0-7, lo in rows 8-15, so one MMA
+// yields both partial products in the same thread, which adds them. The softmax is the
 // online form in fp32, per 32- or 16-key block of a warp. Splits are merged by the last split to finish
 // (a ticket, no spinning), always in split order, so the result does not depend on scheduling.
 #include "kernels.h"
@@ -39,10 +40,13 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col); rows 8..15 of A are zero (a1 = a3 = 0)
-__device__ __forceinline__ void mma_16816_top(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col). Fragment of lane (g = lane / 4, t = lane % 4):
+// a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9];
+// b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g]; c0, c1 = D[g][2t, 2t+1], c2, c3 = D[g+8][2t, 2t+1].
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // (x, y) as two bf16 pairs: hi = bf16(v), lo = bf16(v - hi); x in the low half (the lower k index)
 __device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uint32_t& lo) {
@@ -70,15 +74,20 @@ template <int HD>
 __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
                                                               const int* __restrict__ tok_seq,
                                                               const int* __restrict__ tok_pos, bf16* __restrict__ ctx,
-                                                              int nh, int G, int splits, float* __restrict__ ws,
-                                                              int* __restrict__ counters, int* status) {
+                                                              int nh, int G, int splits, int early,
+                                                              float* __restrict__ ws, int* __restrict__ counters,
+                                                              int* status, unsigned long long* tl) {
     using C = AttnCfg<HD>;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
     float* merge = (float*)(smem + 2 * C::STAGE_BYTES);  // [warp][head][HD + 2]
 
+    // With `early` (decode) everything but q and the newest cached row (the one the previous kernel
+    // wrote, at position tok_pos[t]) is older than the previous kernel, so token data, block table and
+    // the first two stages of K/V are requested before waiting for it; the newest row follows after.
+    if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
-    pdl_wait();
+    if (!early) pdl_wait();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x;  // t * nkv + kvh
@@ -100,25 +109,36 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     // Copy of one stage: every thread moves GRAN * STAGE_ROWS / 128 granules of K and of V. Rows past
     // the end of the range (or of a bad page) are zero-filled: their P is 0, and 0 * garbage could be NaN.
     auto issue_stage = [&](int st) {
-        const int s_begin = c_begin + st * C::STAGE_ROWS;
+        const int s_begin = c_begin + st * C::STAGE_ROWS;  // a multiple of the page size
         const uint32_t kbuf = smem_base + (uint32_t)((st & 1) * C::STAGE_BYTES);
         const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
         if (s_begin < c_end) {
+            // the page ids of the stage first (independent loads, the same for every thread), so that no
+            // copy waits behind another copy's table lookup
+            constexpr int PPS = C::STAGE_ROWS / kPageTokens;
+            int pgs[PPS];
 #pragma unroll
-            for (int i = 0; i < C::GRAN * C::STAGE_ROWS / kAttnThreads; ++i) {
-                const int idx = i * kAttnThreads + tid;
-                const int row = idx / C::GRAN, g = idx % C::GRAN;
+            for (int j = 0; j < PPS; ++j) {
+                const int tok0 = s_begin + j * kPageTokens;
+                const bool pv = tok0 < c_end;
+                const int pg = pv ? __ldg(bt + tok0 / kPageTokens) : -1;
+                if (pv && (pg < 0 || pg >= kv.num_pages)) bad = true;
+                pgs[j] = (pg >= 0 && pg < kv.num_pages) ? pg : -1;
+            }
+            constexpr int ROWS_PER_IT = kAttnThreads / C::GRAN;
+            const int row0 = tid / C::GRAN, g = tid % C::GRAN;
+#pragma unroll
+            for (int i = 0; i < C::STAGE_ROWS / ROWS_PER_IT; ++i) {
+                const int row = i * ROWS_PER_IT + row0;
+                const int pg = pgs[(i * ROWS_PER_IT) / kPageTokens];
                 const int tok = s_begin + row;
-                bool valid = tok < c_end;
-                int pg = 0;
-                if (valid) {
-                    pg = __ldcg(bt + tok / kPageTokens);
-                    if (pg < 0 || pg >= kv.num_pages) { bad = true; valid = false; pg = 0; }
-                }
-                const size_t off = (((size_t)pg * nkv + kvh) * kPageTokens + (valid ? tok % kPageTokens : 0)) * HD + g * 8;
+                const bool valid = tok < c_end && pg >= 0;
+                const size_t off = (((size_t)(valid ? pg : 0) * nkv + kvh) * kPageTokens + row % kPageTokens) * HD + g * 8;
                 const uint32_t dst = (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4));
-                cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
-                cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
+                if (!(early && st < 2 && tok == ctx_len - 1)) {  // the newest row is copied after the wait
+                    cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
+                    cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
+                }
             }
         }
         cp_async_commit();
@@ -126,9 +146,28 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     const int n_stages = c_end > c_begin ? (c_end - c_begin + C::STAGE_ROWS - 1) / C::STAGE_ROWS : 0;
     issue_stage(0);
     issue_stage(1);
+    if (tid == 0 && !early) tl_mark(tl, 1);
+    if (early) {
+        pdl_wait();
+        if (tid == 0) tl_mark(tl, 1);
+        const int rel = ctx_len - 1 - c_begin;  // newest row, relative to this split
+        if (rel >= 0 && rel < 2 * C::STAGE_ROWS && ctx_len - 1 < c_end && tid < C::GRAN) {
+            const int row = rel % C::STAGE_ROWS, g = tid;
+            const uint32_t kbuf = smem_base + (uint32_t)((rel / C::STAGE_ROWS) * C::STAGE_BYTES);
+            const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+            int pg = __ldcg(bt + (ctx_len - 1) / kPageTokens);
+            const bool valid = pg >= 0 && pg < kv.num_pages;
+            if (!valid) { bad = true; pg = 0; }
+            const size_t off = (((size_t)pg * nkv + kvh) * kPageTokens + (ctx_len - 1) % kPageTokens) * HD + g * 8;
+            const uint32_t dst = (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4));
+            cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
+            cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
+        }
+        cp_async_commit();
+    }
 
-    // Q fragments (A operand, rows = query heads of the group; rows >= G are zero): per k-step the
-    // pairs at k = (lane % 4) * 2 and k + 8 of head lane / 4, each as hi and lo bf16.
+    // Q fragments (A operand; tile row g = hi part of query head g of the group, row g + 8 = its lo
+    // part, heads >= G are zero): per k-step the pairs at k = (lane % 4) * 2 and k + 8 of head lane / 4.
     const int hrow = lane >> 2, quad = lane & 3;
     uint32_t qh[C::KS][2], ql[C::KS][2];
     {
@@ -151,7 +190,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     for (int d = 0; d < C::DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
     for (int st = 0; st < n_stages; ++st) {
-        if (st + 1 < n_stages) cp_async_wait<1>();
+        if (st + 1 < n_stages && !(early && st == 0)) cp_async_wait<1>();  // the newest row is the last group
         else cp_async_wait<0>();
         __syncthreads();
         const int w_begin = c_begin + st * C::STAGE_ROWS + warp * C::WARP_ROWS;  // first key of this warp
@@ -169,10 +208,8 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
                     uint32_t b[4];  // B fragments of k-steps 2kp and 2kp + 1 (matrix i = granule 4kp + i)
                     const int g = kp * 4 + (lane >> 3);
                     ldmatrix_x4(kbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
-                    mma_16816_top(s[nt], qh[2 * kp][0], qh[2 * kp][1], b[0], b[1]);
-                    mma_16816_top(s[nt], ql[2 * kp][0], ql[2 * kp][1], b[0], b[1]);
-                    mma_16816_top(s[nt], qh[2 * kp + 1][0], qh[2 * kp + 1][1], b[2], b[3]);
-                    mma_16816_top(s[nt], ql[2 * kp + 1][0], ql[2 * kp + 1][1], b[2], b[3]);
+                    mma_16816(s[nt], qh[2 * kp][0], ql[2 * kp][0], qh[2 * kp][1], ql[2 * kp][1], b[0], b[1]);
+                    mma_16816(s[nt], qh[2 * kp + 1][0], ql[2 * kp + 1][0], qh[2 * kp + 1][1], ql[2 * kp + 1][1], b[2], b[3]);
                 }
             }
             // ---- online softmax of head hrow over these keys (this thread: keys nt * 8 + quad * 2 + {0, 1})
@@ -182,7 +219,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const bool live = w_begin + nt * 8 + quad * 2 + j < c_end;
-                    s[nt][j] = live ? s[nt][j] * scale : kNegBig;
+                    s[nt][j] = live ? (s[nt][j] + s[nt][j + 2]) * scale : kNegBig;  // q_hi . k + q_lo . k
                     mx = fmaxf(mx, s[nt][j]);
                 }
             }
@@ -193,7 +230,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
             m_run = mn;
             l_run *= corr;
 #pragma unroll
-            for (int d = 0; d < C::DT; ++d) { o[d][0] *= corr; o[d][1] *= corr; }
+            for (int d = 0; d < C::DT; ++d) { o[d][0] *= corr; o[d][1] *= corr; o[d][2] *= corr; o[d][3] *= corr; }
             uint32_t ph[C::NT], pl[C::NT];
 #pragma unroll
             for (int nt = 0; nt < C::NT; ++nt) {
@@ -211,10 +248,8 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
                     uint32_t b[4];  // keys 0-7 / 8-15 of tile 2jp, then of tile 2jp + 1
                     const int g = jp * 2 + (lane >> 4);
                     ldmatrix_x4_trans(vbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
-                    mma_16816_top(o[2 * jp], ph[2 * kb], ph[2 * kb + 1], b[0], b[1]);
-                    mma_16816_top(o[2 * jp], pl[2 * kb], pl[2 * kb + 1], b[0], b[1]);
-                    mma_16816_top(o[2 * jp + 1], ph[2 * kb], ph[2 * kb + 1], b[2], b[3]);
-                    mma_16816_top(o[2 * jp + 1], pl[2 * kb], pl[2 * kb + 1], b[2], b[3]);
+                    mma_16816(o[2 * jp], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[0], b[1]);
+                    mma_16816(o[2 * jp + 1], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[2], b[3]);
                 }
             }
         }
@@ -231,8 +266,8 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         if (quad == 0) { mw[0] = m_run; mw[1] = l_run; }
 #pragma unroll
         for (int d = 0; d < C::DT; ++d) {
-            mw[2 + d * 8 + quad * 2] = o[d][0];
-            mw[2 + d * 8 + quad * 2 + 1] = o[d][1];
+            mw[2 + d * 8 + quad * 2] = o[d][0] + o[d][2];  // P_hi V + P_lo V
+            mw[2 + d * 8 + quad * 2 + 1] = o[d][1] + o[d][3];
         }
     }
     __syncthreads();
@@ -259,7 +294,10 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         }
     }
     if (bad) dev_fail(status, DEV_ERR_BOUNDS);
-    if (splits == 1) return;
+    if (splits == 1) {
+        if (tid == 0) tl_mark(tl, 2);
+        return;
+    }
 
     __threadfence();
     __syncthreads();
@@ -269,25 +307,30 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         if (old == splits - 1) counters[unit] = 0;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        if (tid == 0) tl_mark(tl, 2);
+        return;
+    }
     __threadfence();
     const float* parts = ws + (size_t)unit * splits * (size_t)(G * (HD + 2));
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx % HD;
         ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits(parts, splits, G, HD, g, d));
     }
+    if (tid == 0) tl_mark(tl, 2);
 }
 
 template <int HD>
 void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
-               const int* tok_pos, bf16* ctx, int nh, int G, int splits, float* ws, int* counters, int* status) {
+               const int* tok_pos, bf16* ctx, int nh, int G, int splits, int early, float* ws, int* counters, int* status,
+               unsigned long long* tl) {
     static bool configured = false;  // benign race: the call is idempotent
     if (!configured) {
         cudaFuncSetAttribute(k_attn_decode<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
         configured = true;
     }
     launch_k(k_attn_decode<HD>, grid, dim3(kAttnThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
-             nh, G, splits, ws, counters, status);
+             nh, G, splits, early, ws, counters, status, tl);
 }
 
 }  // namespace
@@ -308,13 +351,15 @@ int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWork
 }
 
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
-                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl) {
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl,
+                      bool only_newest_row_fresh, unsigned long long* tl) {
+    const int early = (pdl && only_newest_row_fresh) ? 1 : 0;
     const int G = nh / kv.nkv;  // at most 8 (checked when the model is loaded)
     const int units = T * kv.nkv;
     const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
     dim3 grid(units, splits);
-    if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, ws.partials, ws.counters, status);
-    else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, ws.partials, ws.counters, status);
+    if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl);
+    else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl);
 }
 
 }  // namespace tffn

@@ -295,6 +295,15 @@ int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int
     return rc < 0 ? rc : n;
 }
 const char* tffn_profile_class_name(int cls) { return kclass_name(cls); }
+int tffn_session_timeline(tffn_session* s, int n_seqs, uint64_t* out, int max_launches, int trace_launch,
+                          uint64_t* trace_out, int trace_ctas) {
+    int n = 0;
+    int rc = guard([&] {
+        need(s, "NULL session");
+        n = s->s->timeline(n_seqs, out, max_launches, trace_launch, trace_out, trace_ctas);
+    });
+    return rc < 0 ? rc : n;
+}
 int tffn_session_mega_trace(tffn_session* s, uint64_t* out, int max_ctas) {
     int n = 0;
     int rc = guard([&] {
@@ -347,6 +356,7 @@ int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* 
             const long long ctas = (long long)((N + 127) / 128) * ((T + bn - 1) / bn) * (splits > 0 ? splits : 8);
             if (ctas > trace_ctas) throw Error(kErrInvalid, "trace buffer too small for this grid");
             g.trace = dtrace.as<unsigned long long>();
+            g.trace_ctas = trace_ctas;
         }
         cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
         GemmWorkspace ws{part.as<float>(), part.bytes / 4, cnt.as<int>(), 8192, status.as<int>(), prop.multiProcessorCount};

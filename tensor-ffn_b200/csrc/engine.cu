@@ -505,6 +505,9 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     auto gemm = [&](GemmCall& call, int cls) {
         if (!live(cls)) return;
         call.pdl = pdl;
+        call.tl = tl_next(cls);
+        call.trace = (tl_on_ && (int)tl_cls_.size() - 1 == tl_trace_launch_) ? tl_trace_buf_.as<unsigned long long>() : nullptr;
+        call.trace_ctas = (int)(tl_trace_buf_.bytes / (64 * 8));
         prof_begin(cls);
         int rc = launch_gemm(call, gws, stream_);
         prof_end();
@@ -513,14 +516,15 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         launches_++;
     };
     prof_begin(KC_EMBED);
-    launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_, false);
+    launch_embed(tokens, m_->embed.as<bf16>(), h_.as<bf16>(), T, H, V, status, stream_, false, tl_next(KC_EMBED));
     prof_end();
     launches_++;
     for (int l = 0; l < c.num_layers; ++l) {
         const LayerWeights& ly = m_->layers[l];
         prof_begin(KC_RMSNORM);
         if (live(KC_RMSNORM))
-            launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
+            launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl,
+                           tl_next(KC_RMSNORM));
         prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
@@ -552,7 +556,8 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         prof_begin(KC_ATTENTION);
         if (live(KC_ATTENTION))
             launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
-                             status, stream_, pdl);
+                             status, stream_, pdl, decode /* the step's first kernel (embed) is a full dependency */,
+                             tl_next(KC_ATTENTION));
         prof_end();
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
@@ -563,7 +568,8 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         gemm(g, KC_GEMM_OPROJ);
         prof_begin(KC_RMSNORM);
         if (live(KC_RMSNORM))
-            launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl);
+            launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl,
+                           tl_next(KC_RMSNORM));
         prof_end();
         launches_ += 3;
         // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records; the expert's
@@ -611,7 +617,8 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     if (n_logit_rows > 0) {
         const int* rows = logit_rows_are_all ? nullptr : row_idx_.as<int>();
         prof_begin(KC_RMSNORM);
-        launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_, pdl);
+        launch_rmsnorm(h_.as<bf16>(), m_->final_norm.as<bf16>(), xn_last_.as<bf16>(), n_logit_rows, H, c.rms_norm_eps, rows, stream_, pdl,
+                       tl_next(KC_RMSNORM));
         prof_end();
         GemmCall g;
         memset(&g, 0, sizeof g);
@@ -625,7 +632,11 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.ldo = V;
         gemm(g, KC_GEMM_LMHEAD);
         prof_begin(KC_ARGMAX);
-        if (live(KC_ARGMAX)) launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), stream_, pdl);
+        if (live(KC_ARGMAX)) {
+            const AttnWorkspace aw = attn_ws();  // idle by now: its partials and (zero) counters serve as scratch
+            launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), aw.partials, aw.partial_floats, aw.counters,
+                          aw.num_counters, m_->num_sms, stream_, pdl, tl_next(KC_ARGMAX));
+        }
         prof_end();
         launches_ += 2;
     }
@@ -676,11 +687,13 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
         ly.ffn_base = lw.ffn.packed.as<bf16>();
         ly.ffn_expert = e_ ? e_->layers[l].packed.as<bf16>() : nullptr;
         prof_begin(KC_BS1_QKV);
-        launch_bs1_qkv(x, ly, m_->embed.as<bf16>(), kv_, l, l == 0, stream_, pdl);
+        // the first kernel of a step is a full dependency: what earlier steps wrote (sequence length,
+        // older cache rows) is then stable for every kernel of this step, also ahead of its grid wait
+        launch_bs1_qkv(x, ly, m_->embed.as<bf16>(), kv_, l, l == 0, stream_, pdl && l > 0);
         prof_end();
         prof_begin(KC_ATTENTION);
         launch_attention(x.q, kv_, l, identity_.as<int>(), seq_len_dev_.as<int>(), x.ctx, 1, c.num_heads, max_seq_, attn_ws(),
-                         m_->num_sms, status_.as<int>(), stream_, pdl);
+                         m_->num_sms, status_.as<int>(), stream_, pdl, true);
         prof_end();
         prof_begin(KC_BS1_OPROJ);
         launch_bs1_oproj(x, ly, stream_, pdl);
@@ -751,6 +764,57 @@ int Session::mega_trace(uint64_t* out, int max_ctas) {
     TFFN_CUDA(cudaMemcpy(out, tr.p, (size_t)max_ctas * 16 * 8, cudaMemcpyDeviceToHost));
     check_status();
     return m_->num_sms;
+}
+
+unsigned long long* Session::tl_next(int cls) {
+    if (!tl_on_ || (size_t)(tl_cls_.size() + 1) * 48 > tl_buf_.bytes) return nullptr;
+    tl_cls_.push_back(cls);
+    return tl_buf_.as<unsigned long long>() + (tl_cls_.size() - 1) * 6;
+}
+
+int Session::timeline(int n_seqs, uint64_t* out, int max_launches, int trace_launch, uint64_t* trace_out, int trace_ctas) {
+    if (!out || max_launches < 1) throw Error(kErrInvalid, "bad timeline arguments");
+    const bool want_trace = trace_out && trace_ctas > 0 && trace_launch >= 0;
+    if (want_trace) {
+        tl_trace_buf_.alloc((size_t)trace_ctas * 64 * 8);
+        TFFN_CUDA(cudaMemset(tl_trace_buf_.p, 0, tl_trace_buf_.bytes));
+    }
+    tl_trace_launch_ = want_trace ? trace_launch : -1;
+    if (n_seqs == 1 && use_bs1_ && m_->bs1_ok) throw Error(kErrUnsupported, "the timeline covers the batched path only");
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    drop_graphs();
+    tl_buf_.alloc((size_t)max_launches * 48);
+    std::vector<uint64_t> init((size_t)max_launches * 6);
+    for (size_t i = 0; i < init.size(); ++i) init[i] = (i & 1) ? 0ull : ~0ull;
+    tl_on_ = true;
+    try {
+        for (int rep = 0; rep < 3; ++rep) {  // with graphs the first step captures, the last one is reported
+            if (launch_mode_ < 2 || rep == 0) tl_cls_.clear();
+            TFFN_CUDA(cudaMemcpy(tl_buf_.p, init.data(), init.size() * 8, cudaMemcpyHostToDevice));
+            decode_run(n_seqs, 1, nullptr);
+        }
+    } catch (...) {
+        tl_on_ = false;
+        tl_trace_launch_ = -1;
+        drop_graphs();
+        throw;
+    }
+    tl_on_ = false;
+    tl_trace_launch_ = -1;
+    drop_graphs();
+    if (want_trace) {
+        TFFN_CUDA(cudaMemcpy(trace_out, tl_trace_buf_.p, tl_trace_buf_.bytes, cudaMemcpyDeviceToHost));
+        tl_trace_buf_.release();
+    }
+    const int n = (int)tl_cls_.size();
+    std::vector<uint64_t> raw((size_t)n * 6);
+    TFFN_CUDA(cudaMemcpy(raw.data(), tl_buf_.p, raw.size() * 8, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; ++i) {
+        out[(size_t)i * 7] = (uint64_t)tl_cls_[i];
+        for (int j = 0; j < 6; ++j) out[(size_t)i * 7 + 1 + j] = raw[(size_t)i * 6 + j];
+    }
+    tl_buf_.release();
+    return n;
 }
 
 void Session::drop_graphs() {

@@ -73,6 +73,13 @@ public:
     // one persistent-kernel batch-1 step (feeds the previous pick) with phase timestamps of layer 1:
     // out[cta*16 + k], k = 0 layer start, then before/after each of the five grid barriers
     int mega_trace(uint64_t* out, int max_ctas);
+    // Runs three batched decode steps of n_seqs slots (the sequences advance) and reports the last one:
+    // per kernel launch 7 u64 = class, then min / max over its CTAs of entry, grid-wait return and exit
+    // (globaltimer ns). Returns the number of launches. If launch number trace_launch is a tensor-core
+    // GEMM, its per-CTA phase timestamps (64 u64 per CTA, see GemmCall::trace; the grid must not exceed
+    // trace_ctas CTAs) are returned in trace_out.
+    int timeline(int n_seqs, uint64_t* out, int max_launches, int trace_launch = -1, uint64_t* trace_out = nullptr,
+                 int trace_ctas = 0);
     void set_profile(bool on);
     // accumulated device time (ms) and launches per class since set_profile(true); returns KC_COUNT
     int read_profile(float* ms, int* counts, int cap);
@@ -104,6 +111,12 @@ private:
     bool own_stream_ = false;
     int launch_mode_ = 1;
     unsigned ablate_mask_ = 0;
+    bool tl_on_ = false;
+    DeviceBuffer tl_buf_;
+    std::vector<int> tl_cls_;
+    int tl_trace_launch_ = -1;
+    DeviceBuffer tl_trace_buf_;
+    unsigned long long* tl_next(int cls);
     bool use_bs1_ = true;
     uint64_t launches_ = 0;
 

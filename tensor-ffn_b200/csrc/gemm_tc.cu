@@ -18,6 +18,7 @@
 // and the element-wise kernels around them (silu_mul :58-69, add :152-157,
 // k_add_fp32_to_bf16 inference/src/model/qwen.cu:282-285).
 #include "kernels.h"
+#include <cstdlib>
 #include "ptx.cuh"
 #include <cstdio>
 #include <cstring>
@@ -37,7 +38,7 @@ struct GemmDev {
     CUtensorMap tmW[4];  // [problem * 2 + operand pair]
     CUtensorMap tmX[4];
     int kblocks[2];
-    int N, T, splits, mode, t_tiles, stages;
+    int N, T, splits, mode, t_tiles, stages, rotate;
     int tile_n;          // output indices per tile: 128, or 64 for GEMM_SWIGLU (64 gate rows + 64 up rows per tile)
     float alpha;
     void* out[2];        // per problem
@@ -45,6 +46,7 @@ struct GemmDev {
     int* status;
     GemmQkvEpilogue qkv;  // GEMM_QKV only
     unsigned long long* trace;  // optional: 64 timestamps (ns) per CTA, see GemmCall::trace
+    unsigned long long* tl;     // optional: step timeline of this launch
 };
 
 __device__ __forceinline__ unsigned long long gtime_ns() {
@@ -202,12 +204,18 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
     const int kb_begin = (int)(((long long)blockIdx.z * total_kb) / p.splits);
     const int kb_end = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
     const int n_iters = kb_end - kb_begin;
+    // Every CTA of a launch multiplies by the same activation rows. Walking K in the same order they
+    // would all ask L2 for the same activation box at the same moment (the boxes then arrive one after
+    // another, about 0.5 us apart, measured with 152 CTAs); each CTA therefore starts at its own
+    // k-block and wraps around. The order is fixed per CTA, so results stay reproducible.
+    const int rot = (p.rotate && n_iters > 1) ? (int)((blockIdx.x * 5u + blockIdx.y * 3u) % (unsigned)n_iters) : 0;
     const bool has0 = kb_begin < p.kblocks[0] && n_iters > 0;
     const bool has1 = kb_end > p.kblocks[0] && p.kblocks[1] > 0 && n_iters > 0;
     constexpr uint32_t tmem_cols = Cfg::TMEM_COLS;
 
     if (threadIdx.x == 0) {
         TFFN_TRACE(0);
+        tl_mark(p.tl, 0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -233,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             // requested before griddepcontrol.wait, the activation boxes after it.
             const int pre = n_iters < STAGES ? n_iters : STAGES;
             for (int it = 0; it < pre; ++it) {
-                const int i = kb_begin + it;
+                const int i = kb_begin + (it + rot) % n_iters;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 mbar_arrive_expect_tx(&full[it], Cfg::STAGE_BYTES);
@@ -247,8 +255,9 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             TFFN_TRACE(1);
             pdl_wait();
             TFFN_TRACE(2);
+            tl_mark(p.tl, 1);
             for (int it = 0; it < pre; ++it) {
-                const int i = kb_begin + it;
+                const int i = kb_begin + (it + rot) % n_iters;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 tma_load_2d(smem + it * Cfg::STAGE_BYTES + Cfg::A_BYTES, &p.tmX[prob * 2 + seg], kb * BK, t0, &full[it]);
@@ -257,7 +266,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, p.status, DEV_ERR_EMPTY_WAIT)) break;
-                const int i = kb_begin + it;
+                const int i = kb_begin + (it + rot) % n_iters;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 uint8_t* a = smem + s * Cfg::STAGE_BYTES;
@@ -284,7 +293,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                 if (!ok) break;
                 if (it < 12) TFFN_TRACE(16 + it);
                 tc_fence_after();
-                const int seg = (kb_begin + it) >= p.kblocks[0] ? 1 : 0;
+                const int seg = (kb_begin + (it + rot) % n_iters) >= p.kblocks[0] ? 1 : 0;
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                 const uint32_t b_addr = a_addr + Cfg::A_BYTES;
                 const uint32_t d = tmem_base + (uint32_t)(seg * BN);
@@ -343,7 +352,39 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
         cluster_sync_all();
         if (threadIdx.x == 64) TFFN_TRACE(6);
     }
-    if (warp >= 2 && n_iters > 0) {
+    if (warp >= 2 && n_iters > 0 && p.splits == 1 && p.mode != GEMM_QKV) {
+        // Unsplit tile: every column comes from this CTA's own plane, nothing to wait for, so four
+        // columns per warp are in flight at a time.
+        const int w = warp - 2;
+        const int ncols = min(BN, p.T - t0);
+        const float* plane = (const float*)smem;
+        if (threadIdx.x == 64) TFFN_TRACE(9);
+        if (halves) {
+            // rows 0..63 of the tile hold gate, rows 64..127 up, for the same 64 output indices;
+            // lane l finishes indices n0 + 2l and n0 + 2l + 1
+            bf16* o = (bf16*)out;
+            const int nn = n0 + 2 * lane;
+            const bool pair = nn + 1 < p.N && (p.ldo & 1) == 0;
+#pragma unroll 4
+            for (int c = w; c < ncols; c += 4) {
+                const float2 g = *(const float2*)(plane + (size_t)c * BM + 2 * lane);
+                const float2 u = *(const float2*)(plane + (size_t)c * BM + 64 + 2 * lane);
+                const float a0 = silu_mul_bf16(g.x, u.x), a1 = silu_mul_bf16(g.y, u.y);
+                bf16* dst = o + (size_t)(t0 + c) * (size_t)p.ldo + nn;
+                if (pair) {
+                    *(uint32_t*)dst = (uint32_t)bf16_bits(a0) | ((uint32_t)bf16_bits(a1) << 16);
+                } else {
+                    if (nn < p.N) dst[0] = __float2bfloat16_rn(a0);
+                    if (nn + 1 < p.N) dst[1] = __float2bfloat16_rn(a1);
+                }
+            }
+        } else {
+            const int n = n0 + lane * 4;
+#pragma unroll 4
+            for (int c = w; c < ncols; c += 4)
+                finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4));
+        }
+    } else if (warp >= 2 && n_iters > 0) {
         const int w = warp - 2;
         const int r4 = lane * 4;
         const int n = n0 + r4;
@@ -353,7 +394,9 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
 #pragma unroll
         for (int z = 0; z < kMaxSplits; ++z) peer[z] = (p.splits > 1 && z < p.splits) ? map_shared_rank(plane_local, (uint32_t)z) : plane_local;
         const int ncols = (BN - (int)rank + p.splits - 1) / p.splits;  // columns rank, rank + S, ...
+        if (threadIdx.x == 64) TFFN_TRACE(9);
         for (int k = w; k < ncols; k += 4) {
+            if (threadIdx.x == 64 && k == 4) TFFN_TRACE(10);
             const int c = (int)rank + k * p.splits;
             const int t = t0 + c;
             if (t >= p.T) break;  // warp-uniform
@@ -404,7 +447,10 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
         if (threadIdx.x == 64) TFFN_TRACE(7);
         cluster_sync_all();  // keep this CTA's plane alive until its peers have read it
     }
-    if (threadIdx.x == 64) TFFN_TRACE(8);
+    if (threadIdx.x == 64) {
+        TFFN_TRACE(8);
+        tl_mark(p.tl, 2);
+    }
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
@@ -507,6 +553,7 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     p.ldo = c.ldo;
     p.status = ws.status;
     p.trace = c.trace;
+    p.tl = c.tl;
     if (c.mode == GEMM_QKV) {
         if (!c.qkv || c.op[1].K > 0 || c.out2 || (c.qkv->kv.hd != 64 && c.qkv->kv.hd != 128)) return (int)cudaErrorInvalidValue;
         p.qkv = *c.qkv;
@@ -529,9 +576,33 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     if (splits > total_kb) return (int)cudaErrorInvalidValue;
     const bool shared_sm = tiles * splits > ws.num_sms;  // more than one CTA per SM
     p.stages = shared_sm ? Cfg::SHARED_STAGES : Cfg::MAX_STAGES;
+    {
+        // No deeper than the k-blocks a CTA streams (but deep enough to park the epilogue plane): the
+        // shared memory a CTA does not claim lets CTAs of the next kernel of the stream become resident
+        // early under programmatic dependent launch and fetch their weights ahead of their grid wait.
+        const int iters = (total_kb + splits - 1) / splits;
+        const int plane_stages = (BN * BM * 4 + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
+        int want = iters > plane_stages ? iters : plane_stages;
+        static int cap = -1;
+        if (cap < 0) {
+            const char* e = getenv("TFFN_GEMM_RING_CAP");
+            cap = e ? atoi(e) : 0;
+        }
+        if (cap > 0 && want > cap && cap >= plane_stages) want = cap;
+        if (p.stages > want) p.stages = want;
+    }
     p.splits = splits;
+    {
+        static int rotate = -1;
+        if (rotate < 0) {
+            const char* e = getenv("TFFN_GEMM_ROTATE");
+            rotate = e ? atoi(e) : 1;
+        }
+        p.rotate = rotate;
+    }
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3(n_tiles, t_tiles * nprob, splits);
+    if ((long long)n_tiles * t_tiles * nprob * splits > c.trace_ctas) p.trace = nullptr;
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = Cfg::smem_bytes(p.stages);
     cfg.stream = stream;

@@ -63,6 +63,8 @@ struct GemmCall {
     // 2 dependency wait over, 3 last MMA issued, 4 accumulator complete, 5 epilogue/park done,
     // 6 cluster barrier passed, 7 reduction done, 8 end, 16+i stage i arrived (i < 40)
     unsigned long long* trace;
+    int trace_ctas;          // CTAs the trace buffer holds; a larger grid is not traced
+    unsigned long long* tl;  // optional 6 u64 of the step timeline (see tl_mark)
     bool pdl;          // launch with programmatic dependent launch (the kernel waits before touching X / out)
 };
 struct GemmWorkspace {
@@ -80,16 +82,19 @@ int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream,
 
 // ------------------------------------------------------------------ row kernels of the batched path
 // (pdl: launch with programmatic dependent launch; every kernel here waits before reading its inputs)
+// tl: optional 6 u64 of the step timeline (see tl_mark): min / max over the CTAs of entry, grid-wait return, exit
 void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s,
-                  bool pdl = false);
+                  bool pdl = false, unsigned long long* tl = nullptr);
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
-                    bool pdl = false);
+                    bool pdl = false, unsigned long long* tl = nullptr);
 // qkv fp32 [T, (nh+2nkv)*hd] -> bf16 round, bias (bf16 add), RoPE, q fp32 [T, nh*hd], K/V into pages
 void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
                      const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
                      int T, int nh, int max_pos, int* status, cudaStream_t s, bool pdl = false);
-// logits fp32 [R, V] -> argmax (lowest index among maxima)
-void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s, bool pdl = false);
+// logits fp32 [R, V] -> argmax (lowest index among maxima). scratch (>= 2 * R * 64 floats) and
+// counters (>= R ints, zero, left zero) let several blocks share a row; without them one block per row.
+void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,
+                   int num_counters, int num_sms, cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
 
 // ------------------------------------------------------------------ attention over the paged cache
 struct AttnWorkspace {
@@ -100,9 +105,13 @@ struct AttnWorkspace {
 };
 // context splits launch_attention will use (a CUDA-graph key: the grid depends on it)
 int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
-// one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t]
+// one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t].
+// only_newest_row_fresh (decode): of everything the kernel reads, only q and the cached row at
+// tok_pos[t] were written since the last kernel of the stream that was launched WITHOUT programmatic
+// dependent launch; the rest may then be fetched before the previous kernel has finished.
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
-                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl = false);
+                      int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl = false,
+                      bool only_newest_row_fresh = false, unsigned long long* tl = nullptr);
 
 // ------------------------------------------------------------------ batch-1 fused decode kernels
 struct Bs1Layer {

@@ -109,6 +109,17 @@ __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch
+// Step timeline (a diagnostic): six timestamps per launch — minimum and maximum over the CTAs of
+// kernel entry (which = 0), return from the grid-dependency wait (1) and exit (2). tl = nullptr: off.
+__device__ __forceinline__ void tl_mark(unsigned long long* tl, int which) {
+    if (tl) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMin(tl + 2 * which, t);
+        atomicMax(tl + 2 * which + 1, t);
+    }
+}
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -170,10 +181,12 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-// SiLU(g) * u on bf16-rounded inputs, rounded to bf16 (inference/src/backend/cuda_ops.cu:58-69)
+// SiLU(g) * u on bf16-rounded inputs, rounded to bf16 (inference/src/backend/cuda_ops.cu:58-69). The
+// reference is built with fast math, so its division and exponential are the approximate ones as well;
+// the IEEE division would also be a subroutine call per value, which serialises an epilogue.
 __device__ __forceinline__ float silu_mul_bf16(float g_acc, float u_acc) {
     float g = bf16_round(g_acc), u = bf16_round(u_acc);
-    return bf16_round((g / (1.f + __expf(-g))) * u);
+    return bf16_round(__fdividef(g, 1.f + __expf(-g)) * u);
 }
 
 }  // namespace tffn

@@ -10,9 +10,11 @@ namespace {
 
 // h[t,:] = table[tokens[t],:]  (k_embed, inference/src/model/qwen.cu:216-220); ids are bounds-checked.
 __global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ h, int T,
-                             int H, int V, int* status) {
+                             int H, int V, int* status, unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
+    if (threadIdx.x == 0) tl_mark(tl, 1);
     int t = blockIdx.x;
     int tok = __ldcg(tokens + t);
     if (tok < 0 || tok >= V) {
@@ -22,14 +24,17 @@ __global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restr
     const uint4* src = (const uint4*)(table + (size_t)tok * H);
     uint4* dst = (uint4*)(h + (size_t)t * H);
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+    if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
 // out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w))  (k_rmsnorm, inference/src/backend/cuda_ops.cu:75-96)
 __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                       bf16* __restrict__ out, int H, float eps,
-                                                      const int* __restrict__ row_idx) {
+                                                      const int* __restrict__ row_idx, unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
+    if (threadIdx.x == 0) tl_mark(tl, 1);
     const int r = blockIdx.x;
     const int src_row = row_idx ? row_idx[r] : r;
     const uint4* xr = (const uint4*)(x + (size_t)src_row * H);
@@ -62,6 +67,7 @@ __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x
         }
         orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
+    if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
 // After the fused q|k|v GEMM (fp32 accumulators): round to bf16, add the bias in bf16
@@ -119,39 +125,75 @@ __global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict
     dst[i + half] = __float2bfloat16_rn(x1);
 }
 
-// greedy pick: first index of the strict maximum (sample(), inference/src/main.cpp:45-51)
-__global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int V, int* __restrict__ out) {
+// greedy pick: first index of the strict maximum (sample(), inference/src/main.cpp:45-51).
+// grid (rows, S): block (r, s) scans slice s of row r; the last block of a row to finish (a ticket, no
+// spinning) combines the S partial results, so the pick does not depend on scheduling.
+__device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+__global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ logits, int V, int S, int* __restrict__ out,
+                                                      float* __restrict__ scratch, int* __restrict__ counters,
+                                                      unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
-    const float* row = logits + (size_t)blockIdx.x * V;
+    if (threadIdx.x == 0) tl_mark(tl, 1);
+    const int r = blockIdx.x, s = blockIdx.y;
+    const float* row = logits + (size_t)r * V;
+    const int chunk = (((V + S - 1) / S) + 3) & ~3;
+    const int v0 = s * chunk, v1 = min(V, v0 + chunk);
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += 1024) {
-        float v = __ldcg(row + i);
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    if ((V & 3) == 0) {
+        for (int i = v0 + threadIdx.x * 4; i < v1; i += 256 * 4) {  // v1 - v0 is a multiple of 4 here
+            const float4 v = __ldcg((const float4*)(row + i));
+            argmax_take(best, bi, v.x, i);
+            argmax_take(best, bi, v.y, i + 1);
+            argmax_take(best, bi, v.z, i + 2);
+            argmax_take(best, bi, v.w, i + 3);
+        }
+    } else {
+        for (int i = v0 + threadIdx.x; i < v1; i += 256) argmax_take(best, bi, __ldcg(row + i), i);
     }
     // NaN-free inputs assumed; if every value is -inf the lowest index 0 wins below
-    __shared__ float sv[32];
-    __shared__ int si[32];
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ int s_last;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
     if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
     if (threadIdx.x < 32) {
-        best = sv[threadIdx.x];
-        bi = si[threadIdx.x];
+        best = threadIdx.x < 8 ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < 8 ? si[threadIdx.x] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        for (int o = 4; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (threadIdx.x == 0) {
+            if (S == 1) {
+                out[r] = (bi == 0x7fffffff) ? 0 : bi;
+                s_last = 0;
+            } else {
+                scratch[((size_t)r * S + s) * 2] = best;
+                scratch[((size_t)r * S + s) * 2 + 1] = __int_as_float(bi);
+                __threadfence();
+                const int old = atomicAdd(&counters[r], 1);
+                s_last = (old == S - 1);
+                if (s_last) counters[r] = 0;
+            }
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
     }
+    __syncthreads();
+    if (s_last && threadIdx.x < 32) {
+        __threadfence();
+        best = -INFINITY;
+        bi = 0x7fffffff;
+        for (int z = threadIdx.x; z < S; z += 32)
+            argmax_take(best, bi, __ldcg(scratch + ((size_t)r * S + z) * 2), __float_as_int(__ldcg(scratch + ((size_t)r * S + z) * 2 + 1)));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (threadIdx.x == 0) out[r] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+    if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
 __global__ void k_cast_f32_bf16(const float* __restrict__ src, bf16* __restrict__ dst, size_t n) {
@@ -186,12 +228,13 @@ __global__ void k_wait_selftest(int* status) {
 
 }  // namespace
 
-void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s, bool pdl) {
-    launch_k(k_embed_rows, dim3(T), dim3(128), 0, s, pdl, tokens, table, h, T, H, V, status);
+void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s, bool pdl,
+                  unsigned long long* tl) {
+    launch_k(k_embed_rows, dim3(T), dim3(128), 0, s, pdl, tokens, table, h, T, H, V, status, tl);
 }
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
-                    bool pdl) {
-    launch_k(k_rmsnorm_rows, dim3(T), dim3(128), 0, s, pdl, x, w, out, H, eps, row_idx);
+                    bool pdl, unsigned long long* tl) {
+    launch_k(k_rmsnorm_rows, dim3(T), dim3(128), 0, s, pdl, x, w, out, H, eps, row_idx, tl);
 }
 void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
                      const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
@@ -200,8 +243,13 @@ void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf1
     launch_k(k_qkv_post, grid, dim3(kv.hd / 2), 0, s, pdl, qkv, bq, bk, bv, rope_cos, rope_sin, tok_seq, tok_pos, q_out, kv,
              layer, nh, max_pos, status);
 }
-void launch_argmax(const float* logits, int R, int V, int* out, cudaStream_t s, bool pdl) {
-    launch_k(k_argmax_rows, dim3(R), dim3(1024), 0, s, pdl, logits, V, out);
+void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,
+                   int num_counters, int num_sms, cudaStream_t s, bool pdl, unsigned long long* tl) {
+    int S = (4 * num_sms + R - 1) / R;  // about four blocks of 256 threads per SM
+    if (S > 64) S = 64;
+    if (S > V / 1024) S = V / 1024;
+    if (S < 1 || !scratch || !counters || R > num_counters || (size_t)R * S * 2 > scratch_floats) S = 1;
+    launch_k(k_argmax_rows, dim3(R, S), dim3(256), 0, s, pdl, logits, V, S, out, scratch, counters, tl);
 }
 void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s) {
     int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);

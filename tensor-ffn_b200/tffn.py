@@ -85,6 +85,7 @@ _SIGS = {
     "tffn_session_profile_read": (_i, [_vp, _vp, _vp, _i]),
     "tffn_profile_class_name": (_cp, [_i]),
     "tffn_session_mega_trace": (_i, [_vp, _vp, _i]),
+    "tffn_session_timeline": (_i, [_vp, _i, _vp, _i, _i, _vp, _i]),
     "tffn_session_status": (_i, [_vp]),
     "tffn_session_launch_count": (ctypes.c_uint64, [_vp]),
     "tffn_session_stream": (_vp, [_vp]),
@@ -328,6 +329,19 @@ class Session:
         n = np.zeros(64, dtype=np.int32)
         k = _check(_L.tffn_session_profile_read(self._h, ms.ctypes.data, n.ctypes.data, 64))
         return {_L.tffn_profile_class_name(i).decode(): (float(ms[i]), int(n[i])) for i in range(k) if n[i] > 0}
+
+    def timeline(self, n_seqs: int, max_launches: int = 1024, trace_launch: int = -1, trace_ctas: int = 0):
+        """three batched decode steps; timeline of the last: (class names, uint64 [launches, 6] =
+        min/max over CTAs of entry, grid-wait return, exit in globaltimer ns[, uint64 [trace_ctas, 64]
+        per-CTA phase timestamps of GEMM launch number trace_launch])"""
+        out = np.zeros((max_launches, 7), dtype=np.uint64)
+        tr = np.zeros((max(trace_ctas, 1), 64), dtype=np.uint64)
+        n = _check(_L.tffn_session_timeline(self._h, n_seqs, out.ctypes.data, max_launches, trace_launch,
+                                            tr.ctypes.data if trace_ctas > 0 else None, trace_ctas))
+        names = [_L.tffn_profile_class_name(int(c)).decode() for c in out[:n, 0]]
+        if trace_ctas > 0:
+            return names, out[:n, 1:], tr
+        return names, out[:n, 1:]
 
     def mega_trace(self, max_ctas: int = 256) -> np.ndarray:
         """one persistent-kernel batch-1 step with phase timestamps of layer 1: uint64 [ctas, 16]"""
