@@ -18,7 +18,6 @@
 // and the element-wise kernels around them (silu_mul :58-69, add :152-157,
 // k_add_fp32_to_bf16 inference/src/model/qwen.cu:282-285).
 #include "kernels.h"
-#include <cstdlib>
 #include "ptx.cuh"
 #include <cstdio>
 #include <cstring>
@@ -32,13 +31,14 @@ namespace {
 constexpr int BM = 128;  // weight rows per tile
 constexpr int BK = 64;   // K elements per stage (128 bytes of bf16)
 constexpr int kGemmThreads = 192;
+constexpr int kMaxSmem = 227 * 1024;  // dynamic shared memory a CTA may claim on sm_100
 constexpr int kMaxSplits = 16;  // cluster size; above 8 needs the non-portable opt-in (gemm_prepare)
 
 struct GemmDev {
     CUtensorMap tmW[4];  // [problem * 2 + operand pair]
     CUtensorMap tmX[4];
     int kblocks[2];
-    int N, T, splits, mode, t_tiles, stages, rotate;
+    int N, T, splits, mode, t_tiles, stages;
     int tile_n;          // output indices per tile: 128, or 64 for GEMM_SWIGLU (64 gate rows + 64 up rows per tile)
     float alpha;
     void* out[2];        // per problem
@@ -84,12 +84,42 @@ __device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d)
                       (uint32_t)bf16_bits(c) | ((uint32_t)bf16_bits(d) << 16));
 }
 
+// What a finalisation reads from global memory besides the accumulators. None of it depends on this
+// kernel's own arithmetic, so with split-K (where a warp finishes at most two columns) the epilogue warps
+// fetch it while the MMAs still run, instead of paying two or three dependent L2 round trips per column
+// after the reduction.
+struct FinalizePre {
+    bool valid;      // the fields below were fetched
+    uint2 residual;  // GEMM_RESIDUAL: the four old bf16 values
+    int pos, pg;     // GEMM_QKV: position and page of the token (pg = -1: bad page or position)
+    float4 cs, sn;   // GEMM_QKV: the RoPE table entries of this lane's rows
+};
+
+// GEMM_QKV: position of token t, its page, and the RoPE entries for rows n .. n+3
+__device__ __forceinline__ void prefetch_qkv(const GemmDev& p, int n, int t, FinalizePre& f) {
+    const GemmQkvEpilogue& e = p.qkv;
+    const int hd = e.kv.hd, half = hd >> 1;
+    f.valid = true;
+    f.pos = __ldcg(e.tok_pos + t);
+    f.pg = -1;
+    f.cs = f.sn = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (f.pos < 0 || f.pos >= e.max_pos || n >= p.N) return;
+    const int seq = __ldcg(e.tok_seq + t);
+    const int pg = __ldcg(e.kv.block_table + (size_t)seq * e.kv.max_pages_per_seq + f.pos / kPageTokens);
+    f.pg = (pg >= 0 && pg < e.kv.num_pages) ? pg : -1;
+    if (n < (e.nh + e.kv.nkv) * hd) {  // q and k rows are rotated
+        const int i = (n % hd) % half;
+        f.cs = *(const float4*)(e.rope_cos + (size_t)f.pos * half + i);
+        f.sn = *(const float4*)(e.rope_sin + (size_t)f.pos * half + i);
+    }
+}
+
 // GEMM_QKV: round to bf16, add the bias in bf16 (k_add_bias, inference/src/model/qwen.cu:223-226),
 // rotate q and k in fp32 at the token's position (k_rope, qwen.cu:232-244) — the RoPE partner rows
 // (i <-> i + hd/2) sit hd/8 lanes away in the same warp, because a warp holds all 128 rows of a
 // column — keep q in fp32, write k (rounded after the rotation) and v as bf16 into the
 // sequence's page (qwen.cu:339-346). Every lane of the warp must call it (shuffles).
-__device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, float4 v, int lane) {
+__device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, float4 v, FinalizePre f) {
     const GemmQkvEpilogue& e = p.qkv;
     const int hd = e.kv.hd, half = hd >> 1;
     const int d = n % hd;  // tiles start at multiples of 128 and hd divides 128
@@ -105,10 +135,9 @@ __device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, flo
     float xp[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) xp[j] = __shfl_xor_sync(0xffffffffu, x[j], hd >> 3);
-    (void)lane;
     if (!in_range) return;
-    const int pos = __ldcg(e.tok_pos + t);
-    if (pos < 0 || pos >= e.max_pos) {
+    if (!f.valid) prefetch_qkv(p, n, t, f);
+    if (f.pos < 0 || f.pos >= e.max_pos) {
         dev_fail(p.status, DEV_ERR_BOUNDS);
         return;
     }
@@ -116,10 +145,7 @@ __device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, flo
     const int kind = n < nq ? 0 : (n < nq + nk ? 1 : 2);
     float o[4] = {x[0], x[1], x[2], x[3]};
     if (kind != 2) {
-        const int i = d % half;
-        const float4 c = *(const float4*)(e.rope_cos + (size_t)pos * half + i);
-        const float4 s = *(const float4*)(e.rope_sin + (size_t)pos * half + i);
-        const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+        const float cs[4] = {f.cs.x, f.cs.y, f.cs.z, f.cs.w}, sn[4] = {f.sn.x, f.sn.y, f.sn.z, f.sn.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = d < half ? x[j] * cs[j] - xp[j] * sn[j] : xp[j] * sn[j] + x[j] * cs[j];
     }
@@ -127,23 +153,29 @@ __device__ __forceinline__ void finalize_qkv(const GemmDev& p, int n, int t, flo
         *(float4*)(e.q_out + (size_t)t * nq + n) = make_float4(o[0], o[1], o[2], o[3]);
         return;
     }
-    const int head = kind == 1 ? (n - nq) / hd : (n - nq - nk) / hd;
-    const int seq = __ldcg(e.tok_seq + t);
-    const int pg = __ldcg(e.kv.block_table + (size_t)seq * e.kv.max_pages_per_seq + pos / kPageTokens);
-    if (pg < 0 || pg >= e.kv.num_pages) {
+    if (f.pg < 0) {
         dev_fail(p.status, DEV_ERR_BOUNDS);
         return;
     }
+    const int head = kind == 1 ? (n - nq) / hd : (n - nq - nk) / hd;
     bf16* pool = (kind == 1 ? e.kv.k_pool : e.kv.v_pool) + (size_t)e.layer * e.kv.layer_stride;
-    bf16* dst = pool + (((size_t)pg * e.kv.nkv + head) * kPageTokens + pos % kPageTokens) * hd + d;
+    bf16* dst = pool + (((size_t)f.pg * e.kv.nkv + head) * kPageTokens + f.pos % kPageTokens) * hd + d;
     *(uint2*)dst = pack_bf16x4(o[0], o[1], o[2], o[3]);
 }
 
-// STORE / RESIDUAL / SWIGLU (the SwiGLU value was formed before parking)
-__device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int n, int t, float4 v) {
+__device__ __forceinline__ bool plain_is_vector(const GemmDev& p, int n) { return (n + 3 < p.N) && ((p.ldo & 3) == 0); }
+
+// GEMM_RESIDUAL: the old values of rows n .. n+3 of token t (read through L2)
+__device__ __forceinline__ void prefetch_residual(const GemmDev& p, const void* out, int n, int t, FinalizePre& f) {
+    f.valid = n < p.N && plain_is_vector(p, n);
+    if (f.valid) f.residual = __ldcg((const uint2*)((const bf16*)out + (size_t)t * (size_t)p.ldo + n));
+}
+
+// STORE / RESIDUAL / SWIGLU (the SwiGLU value was formed before the call)
+__device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int n, int t, float4 v, FinalizePre pre) {
     if (n >= p.N) return;
     const size_t o = (size_t)t * (size_t)p.ldo + n;
-    const bool vec = (n + 3 < p.N) && ((p.ldo & 3) == 0);
+    const bool vec = plain_is_vector(p, n);
     const float f[4] = {v.x, v.y, v.z, v.w};
     switch (p.mode) {
         case GEMM_STORE_F32:
@@ -157,7 +189,7 @@ __device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int 
             // h = bf16(float(h) + sum) (k_add_fp32_to_bf16, qwen.cu:282-285); h is read through L2
             bf16* h = (bf16*)out;
             if (vec) {
-                const uint2 old = __ldcg((const uint2*)(h + o));
+                const uint2 old = pre.valid ? pre.residual : __ldcg((const uint2*)(h + o));
                 *(uint2*)(h + o) = pack_bf16x4(bf16_lo(old.x) + f[0], bf16_hi(old.x) + f[1], bf16_lo(old.y) + f[2],
                                                bf16_hi(old.y) + f[3]);
             } else {
@@ -183,6 +215,12 @@ __device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t addr) {
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ void add4(float4& a, const float4& b) {
+    a.x += b.x;
+    a.y += b.y;
+    a.z += b.z;
+    a.w += b.w;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(const __grid_constant__ GemmDev p) {
@@ -204,11 +242,6 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
     const int kb_begin = (int)(((long long)blockIdx.z * total_kb) / p.splits);
     const int kb_end = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
     const int n_iters = kb_end - kb_begin;
-    // Every CTA of a launch multiplies by the same activation rows. Walking K in the same order they
-    // would all ask L2 for the same activation box at the same moment (the boxes then arrive one after
-    // another, about 0.5 us apart, measured with 152 CTAs); each CTA therefore starts at its own
-    // k-block and wraps around. The order is fixed per CTA, so results stay reproducible.
-    const int rot = (p.rotate && n_iters > 1) ? (int)((blockIdx.x * 5u + blockIdx.y * 3u) % (unsigned)n_iters) : 0;
     const bool has0 = kb_begin < p.kblocks[0] && n_iters > 0;
     const bool has1 = kb_end > p.kblocks[0] && p.kblocks[1] > 0 && n_iters > 0;
     constexpr uint32_t tmem_cols = Cfg::TMEM_COLS;
@@ -232,6 +265,8 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    FinalizePre pre[2];  // epilogue warps, split-K: operands of the columns they will finish
+    pre[0].valid = pre[1].valid = false;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -241,7 +276,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             // requested before griddepcontrol.wait, the activation boxes after it.
             const int pre = n_iters < STAGES ? n_iters : STAGES;
             for (int it = 0; it < pre; ++it) {
-                const int i = kb_begin + (it + rot) % n_iters;
+                const int i = kb_begin + it;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 mbar_arrive_expect_tx(&full[it], Cfg::STAGE_BYTES);
@@ -257,7 +292,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             TFFN_TRACE(2);
             tl_mark(p.tl, 1);
             for (int it = 0; it < pre; ++it) {
-                const int i = kb_begin + (it + rot) % n_iters;
+                const int i = kb_begin + it;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 tma_load_2d(smem + it * Cfg::STAGE_BYTES + Cfg::A_BYTES, &p.tmX[prob * 2 + seg], kb * BK, t0, &full[it]);
@@ -266,7 +301,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, p.status, DEV_ERR_EMPTY_WAIT)) break;
-                const int i = kb_begin + (it + rot) % n_iters;
+                const int i = kb_begin + it;
                 const int seg = i >= p.kblocks[0] ? 1 : 0;
                 const int kb = seg ? i - p.kblocks[0] : i;
                 uint8_t* a = smem + s * Cfg::STAGE_BYTES;
@@ -293,7 +328,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                 if (!ok) break;
                 if (it < 12) TFFN_TRACE(16 + it);
                 tc_fence_after();
-                const int seg = (kb_begin + (it + rot) % n_iters) >= p.kblocks[0] ? 1 : 0;
+                const int seg = (kb_begin + it) >= p.kblocks[0] ? 1 : 0;
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                 const uint32_t b_addr = a_addr + Cfg::A_BYTES;
                 const uint32_t d = tmem_base + (uint32_t)(seg * BN);
@@ -309,12 +344,24 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             umma_commit(acc_full);  // arrives when every MMA above has finished (also on the error path)
         }
     } else {
-        // Epilogue warps 2..5 own TMEM lane quarter (warp % 4): thread = one weight row. They add up
-        // the accumulation chains, combine the two operand pairs (SwiGLU, or base + alpha * expert)
-        // and park ONE fp32 plane [column][row] in the idle stage memory.
+        // Epilogue warps 2..5 own TMEM lane quarter (warp % 4): thread = one weight row. They combine
+        // the two operand pairs (base + alpha * expert) and park ONE fp32 plane [column][row] in the
+        // idle stage memory.
         const int q = warp & 3;
         const int row = q * 32 + lane;
         pdl_wait();  // later phases read and write buffers of earlier kernels
+        if (p.splits > 1) {
+            // split-K: the (at most two) columns this warp will finish are known; fetch their operands now
+            const int S = p.splits, cps = BN / S, rank = (int)cluster_ctarank();
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int jj = (warp - 2) + 4 * u, t = t0 + jj * S + rank;
+                if (cps <= 8 && jj < cps && t < p.T) {
+                    if (p.mode == GEMM_QKV) prefetch_qkv(p, n0 + lane * 4, t, pre[u]);
+                    else if (p.mode == GEMM_RESIDUAL) prefetch_residual(p, out, n0 + lane * 4, t, pre[u]);
+                }
+            }
+        }
         // every lane waits (acquire); the outcome is made warp-uniform because tcgen05.ld is .aligned
         bool ok = mbar_wait(acc_full, 0, p.status, DEV_ERR_ACC_WAIT);
         ok = __all_sync(0xffffffffu, ok);
@@ -342,15 +389,21 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 64) TFFN_TRACE(5);
-    // With split-K the splits of one output tile form a thread-block cluster (1,1,splits): after the
-    // cluster barrier each CTA finalises the columns it owns (column % splits == rank) by summing the
-    // parked planes of all ranks, in rank order, over distributed shared memory. Without a split
-    // the CTA finalises all columns from its own plane. Finalisation is vectorised the other way
-    // round from the TMEM layout: a warp takes one column, a lane 4 consecutive rows, so every global
-    // access is 8 or 16 bytes per lane and the RoPE partner of a row sits in the same warp.
+    // Finalisation is vectorised the other way round from the TMEM layout: a warp takes one column, a
+    // lane 4 consecutive rows, so every global access is 8 or 16 bytes per lane and the RoPE partner of
+    // a row sits in the same warp. With split-K the splits of one output tile form a thread-block
+    // cluster (1,1,splits): after a cluster barrier each rank finalises the columns it owns
+    // (column % splits == rank), adding up the parked planes of all ranks in rank order over
+    // distributed shared memory (the result does not depend on scheduling). A second cluster barrier
+    // keeps every plane alive until its peers have read it; a thread arrives at it as soon as its own
+    // remote reads are done and waits only before it leaves, so the barrier's latency hides behind the
+    // global stores. (Measured alternatives, both slower per launch: pushing the partial columns into the
+    // owners' shared memory with 4-byte remote stores, +3 us; exchanging the planes through an L2
+    // workspace, +1 us.)
     if (p.splits > 1) {
         cluster_sync_all();
         if (threadIdx.x == 64) TFFN_TRACE(6);
+        if (warp < 2) cluster_arrive();
     }
     if (warp >= 2 && n_iters > 0 && p.splits == 1 && p.mode != GEMM_QKV) {
         // Unsplit tile: every column comes from this CTA's own plane, nothing to wait for, so four
@@ -380,73 +433,74 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             }
         } else {
             const int n = n0 + lane * 4;
+            FinalizePre none;
+            none.valid = false;
 #pragma unroll 4
             for (int c = w; c < ncols; c += 4)
-                finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4));
+                finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4), none);
         }
-    } else if (warp >= 2 && n_iters > 0) {
+    } else if (warp >= 2) {
         const int w = warp - 2;
         const int r4 = lane * 4;
         const int n = n0 + r4;
-        const uint32_t rank = p.splits > 1 ? cluster_ctarank() : 0u;
+        const int S = p.splits, cps = BN / S;
+        const uint32_t rank = S > 1 ? cluster_ctarank() : 0u;
         const uint32_t plane_local = smem_u32(smem);
-        uint32_t peer[kMaxSplits];
-#pragma unroll
-        for (int z = 0; z < kMaxSplits; ++z) peer[z] = (p.splits > 1 && z < p.splits) ? map_shared_rank(plane_local, (uint32_t)z) : plane_local;
-        const int ncols = (BN - (int)rank + p.splits - 1) / p.splits;  // columns rank, rank + S, ...
         if (threadIdx.x == 64) TFFN_TRACE(9);
-        for (int k = w; k < ncols; k += 4) {
-            if (threadIdx.x == 64 && k == 4) TFFN_TRACE(10);
-            const int c = (int)rank + k * p.splits;
-            const int t = t0 + c;
-            if (t >= p.T) break;  // warp-uniform
-            const uint32_t off = (uint32_t)(((size_t)c * BM + r4) * 4);
-            float4 acc;
-            if (p.splits == 1) {
-                acc = *(const float4*)(smem + off);
-            } else {
-                float4 v[kMaxSplits];
-#pragma unroll
-                for (int z = 0; z < kMaxSplits; ++z) v[z] = (z < p.splits) ? ld_shared_cluster_v4(peer[z] + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-                acc = v[0];
-#pragma unroll
-                for (int z = 1; z < kMaxSplits; ++z) {  // rank order: the sum does not depend on scheduling
-                    acc.x += v[z].x;
-                    acc.y += v[z].y;
-                    acc.z += v[z].z;
-                    acc.w += v[z].w;
-                }
-            }
+        // sum over the ranks' planes of rows row_off .. row_off+3 of tile column c
+        auto column_sum = [&](int c, int row_off) {
+            const uint32_t off = (uint32_t)(((size_t)c * BM + row_off) * 4);
+            if (S == 1) return *(const float4*)(smem + off);
+            float4 acc = ld_shared_cluster_v4(map_shared_rank(plane_local + off, 0u));
+#pragma unroll 4
+            for (int z = 1; z < S; ++z) add4(acc, ld_shared_cluster_v4(map_shared_rank(plane_local + off, (uint32_t)z)));
+            return acc;
+        };
+        auto finish = [&](int t, float4 acc, float4 up, const FinalizePre& f) {
             if (p.mode == GEMM_QKV) {
-                finalize_qkv(p, n, t, acc, lane);
+                finalize_qkv(p, n, t, acc, f);
             } else if (halves) {
                 // rows 0..63 of the tile hold gate, rows 64..127 up, for the same 64 output indices
-                if (lane < 16) {
-                    float4 up;
-                    if (p.splits == 1) {
-                        up = *(const float4*)(smem + off + 64 * 4);
-                    } else {
-                        up = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                        for (int z = 0; z < kMaxSplits; ++z)
-                            if (z < p.splits) {
-                                const float4 u = ld_shared_cluster_v4(peer[z] + off + 64 * 4);
-                                up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
-                            }
-                    }
+                if (lane < 16)
                     finalize_plain(p, out, n, t,
                                    make_float4(silu_mul_bf16(acc.x, up.x), silu_mul_bf16(acc.y, up.y), silu_mul_bf16(acc.z, up.z),
-                                               silu_mul_bf16(acc.w, up.w)));
-                }
+                                               silu_mul_bf16(acc.w, up.w)), f);
             } else {
-                finalize_plain(p, out, n, t, acc);
+                finalize_plain(p, out, n, t, acc, f);
             }
+        };
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (S > 1 && cps <= 8) {
+            // at most two columns per warp: all remote reads first, then the arrival, then the stores
+            float4 acc[2], up[2];
+            bool have[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int jj = w + 4 * u, c = jj * S + (int)rank;
+                have[u] = n_iters > 0 && jj < cps && t0 + c < p.T;  // warp-uniform
+                acc[u] = have[u] ? column_sum(c, r4) : zero4;
+                up[u] = (have[u] && halves && lane < 16) ? column_sum(c, r4 + 64) : zero4;
+            }
+            cluster_arrive();
+            if (threadIdx.x == 64) TFFN_TRACE(10);
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (have[u]) finish(t0 + (w + 4 * u) * S + (int)rank, acc[u], up[u], pre[u]);
+        } else {
+            FinalizePre none;
+            none.valid = false;
+            for (int jj = w; jj < cps && n_iters > 0; jj += 4) {
+                const int c = jj * S + (int)rank;
+                if (t0 + c >= p.T) break;  // warp-uniform
+                const float4 acc = column_sum(c, r4);
+                const float4 up = (halves && lane < 16) ? column_sum(c, r4 + 64) : zero4;
+                finish(t0 + c, acc, up, none);
+            }
+            if (S > 1) cluster_arrive();
         }
-    }
-    if (p.splits > 1) {
         if (threadIdx.x == 64) TFFN_TRACE(7);
-        cluster_sync_all();  // keep this CTA's plane alive until its peers have read it
     }
+    if (p.splits > 1) cluster_wait();  // every peer has finished reading this CTA's plane
     if (threadIdx.x == 64) {
         TFFN_TRACE(8);
         tl_mark(p.tl, 2);
@@ -582,24 +636,10 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
         // early under programmatic dependent launch and fetch their weights ahead of their grid wait.
         const int iters = (total_kb + splits - 1) / splits;
         const int plane_stages = (BN * BM * 4 + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
-        int want = iters > plane_stages ? iters : plane_stages;
-        static int cap = -1;
-        if (cap < 0) {
-            const char* e = getenv("TFFN_GEMM_RING_CAP");
-            cap = e ? atoi(e) : 0;
-        }
-        if (cap > 0 && want > cap && cap >= plane_stages) want = cap;
+        const int want = iters > plane_stages ? iters : plane_stages;
         if (p.stages > want) p.stages = want;
     }
     p.splits = splits;
-    {
-        static int rotate = -1;
-        if (rotate < 0) {
-            const char* e = getenv("TFFN_GEMM_ROTATE");
-            rotate = e ? atoi(e) : 1;
-        }
-        p.rotate = rotate;
-    }
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3(n_tiles, t_tiles * nprob, splits);
     if ((long long)n_tiles * t_tiles * nprob * splits > c.trace_ctas) p.trace = nullptr;
@@ -630,7 +670,7 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
 int gemm_prepare() {
     cudaError_t e;
 #define TFFN_PREP(BN)                                                                                                 \
-    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::smem_bytes(GemmCfg<BN>::MAX_STAGES)); \
+    e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem); \
     if (e != cudaSuccess) return (int)e;                                                                             \
     e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);                     \
     if (e != cudaSuccess) return (int)e;

@@ -96,6 +96,11 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves separately, for a barrier whose arrival and wait are apart (every thread of every
+// CTA of the cluster executes each of them once per phase). Release: the thread's earlier loads and
+// stores, remote ones included, are performed first.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 // shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
 __device__ __forceinline__ uint32_t map_shared_rank(uint32_t local_smem_addr, uint32_t rank) {
     uint32_t r;
