@@ -45,6 +45,14 @@ def peaks():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+# DRAM traffic of k_gemm_tc from the ncu capture summarised in profiles/ncu_gemm_tc_decode_shapes.md
+# (one launch each of the two largest decode shapes, 64 tokens): dram read+write bytes per byte of
+# weights for a layer-sized launch whose output stays in L2, and the part of the LM head's fp32 logits
+# that reaches DRAM before the launch ends.
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 17643264 / 17432576
+NCU_LMHEAD_LOGIT_WRITE_FRACTION = 26198016 / 38895616
+
+
 def model_dir(shape: str) -> str:
     base = "/dev/shm" if os.path.isdir("/dev/shm") and shutil.disk_usage("/dev/shm").free > (8 << 30) else "/tmp"
     return os.path.join(base, f"tffn_bench_{shape}")
@@ -184,7 +192,7 @@ def run_ours(a):
     barrier()
     d, ep, cfg = ensure_model(a.shape)
     K, W, n = a.steps, a.warmup, a.seqs
-    max_seq = a.prompt + W + K + 8
+    max_seq = a.prompt + W + K + 8 + 16  # + the per-kernel profile pass and the timeline steps
     stream = torch.cuda.Stream(device=local)
     model = tffn.qwen_load(d, device=local)
     expert = tffn.checkpoint_load(ep, model, 0.1)
@@ -241,7 +249,30 @@ def run_ours(a):
     roofline = {"bound": "hbm", "kernel": "k_gemm_tc (all launches of a decode step)", "achieved": achieved,
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "launches_per_step": gemm_n, "avg_launch_us": 1e3 * gemm_ms / max(gemm_n, 1),
-                "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1), "traffic": a.traffic}
+                "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1)}
+    # traffic per launch: the captured ratio applied to this step's weight bytes, plus the logits written
+    traffic = gemm_bytes * NCU_DRAM_BYTES_PER_WEIGHT_BYTE + NCU_LMHEAD_LOGIT_WRITE_FRACTION * n * cfg["vocab_size"] * 4
+    roofline["traffic"] = a.traffic if a.traffic is not None else traffic / max(gemm_n, 1)
+    roofline["traffic_source"] = ("--traffic" if a.traffic is not None else
+                                  "ncu capture of two launches (profiles/ncu_gemm_tc_decode_shapes.md), scaled by weight bytes")
+    # the same step as it runs (graph + dependent launches): per kernel class the time from the previous
+    # kernel's last CTA leaving to this kernel's last CTA leaving, from in-kernel globaltimer stamps
+    in_situ = None
+    try:
+        names, tl = sess.timeline(n)
+        tl = tl.astype(np.int64)
+        agg: dict = {}
+        prev = int(tl[:, 0].min())
+        for nm, r in zip(names, tl):
+            e = agg.setdefault(nm, [0, 0.0])
+            e[0] += 1
+            e[1] += (int(r[5]) - prev) / 1e3
+            prev = int(r[5])
+        in_situ = {"step_us": (int(tl[:, 5].max()) - int(tl[:, 0].min())) / 1e3,
+                   "kernels": [{"kernel": nm, "launches": v[0], "us_per_launch": v[1] / v[0]}
+                               for nm, v in sorted(agg.items(), key=lambda kv: -kv[1][1])]}
+    except Exception as ex:  # a diagnostic: never fail the bench line for it
+        in_situ = {"error": str(ex)}
     step_bytes = sum(v for k, v in kb.items() if k.startswith("gemm_tc:")) + kb["attn_decode"]
     step_roofline = {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / 1e9 / (ms / K / 1e3),
                      "peak": peak, "unit": "GB/s", "frac": step_bytes / 1e9 / (ms / K / 1e3) / peak}
@@ -317,7 +348,7 @@ def run_ours(a):
                        "prompt_len": a.prompt, "decode_steps": K, "parallelism": f"dp{world} (no collective)",
                        "l2": "no flush: each step streams 1.6 GB of weights + KV, far more than the 126 MB L2"},
             "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "step_roofline": step_roofline,
-            "kernels": kernels, "clocks": clocks, "cpu_baseline": cpu, "prefill_s": prefill_s,
+            "kernels": kernels, "kernels_in_situ": in_situ, "clocks": clocks, "cpu_baseline": cpu, "prefill_s": prefill_s,
             "checksum_tokens": int(np.asarray(toks_dev, dtype=np.int64).sum()),
         }
         if bs1:
@@ -389,6 +420,32 @@ def run_reference(a):
     print(json.dumps(line), flush=True)
 
 
+def run_kernel_case(a):
+    """k_gemm_tc alone, one launch per shape, inputs seeded: [64 tokens] x [gate|up rows of one layer]
+    (17 MB of weights, cold: what every layer's launch sees in a step that cycles 1 GB through L2) and
+    x [vocabulary rows] (272 MB, larger than L2). Prints one JSON line with the wall time of each call
+    (host copies included, so not a kernel time)."""
+    import synth
+    import tffn
+    cfg = synth.SHAPES[a.shape] if hasattr(synth, "SHAPES") else None
+    H = cfg["hidden_size"] if isinstance(cfg, dict) else 896
+    I = cfg["intermediate_size"] if isinstance(cfg, dict) else 4864
+    V = cfg["vocab_size"] if isinstance(cfg, dict) else 151936
+    rng = np.random.default_rng(7)
+    X = synth.f32_to_bf16(rng.standard_normal((a.seqs, H), dtype=np.float32))
+    out = {"kernel_case": "gemm", "tokens": a.seqs, "K": H, "cases": []}
+    for name, N in (("gate_up_rows", 2 * I), ("lm_head", V)):
+        W = synth.f32_to_bf16((rng.standard_normal((N, H), dtype=np.float32) * 0.02))
+        t0 = time.perf_counter()
+        y = tffn.op_gemm(X, W)
+        dt = time.perf_counter() - t0
+        ref = synth.bf16_to_f32(X[:2]) @ synth.bf16_to_f32(W[:256]).T
+        err = float(np.abs(y[:2, :256] - ref).max())
+        out["cases"].append({"name": name, "N": N, "weight_bytes": int(N) * H * 2, "out_bytes": a.seqs * int(N) * 4,
+                             "call_s": dt, "max_abs_err_vs_numpy_sample": err})
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,10 +462,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-prompt", type=int, default=64)
     ap.add_argument("--cpu-tokens", type=int, default=128)
+    ap.add_argument("--kernel-case", default="", choices=["", "gemm"],
+                    help="run only the tensor-core GEMM on the decode step's two largest shapes (gate|up rows, LM head) "
+                         "through the op-level entry point and exit: the small program that ncu captures are taken from")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), if known")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    if a.kernel_case:
+        run_kernel_case(a)
+        return
     if a.impl == "reference":
         run_reference(a)
     else:

@@ -337,13 +337,11 @@ int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* 
         cudaDeviceProp prop;
         TFFN_CUDA(cudaGetDeviceProperties(&prop, device));
         const int rows = T < 256 ? 256 : T;
-        DeviceBuffer dx, dw, dout, part, cnt, status, dtrace;
+        DeviceBuffer dx, dw, dout, status, dtrace;
         if (trace && trace_ctas > 0) dtrace.alloc((size_t)trace_ctas * 64 * 8);
         dx.alloc((size_t)rows * K * 2);
         dw.alloc((size_t)N * K * 2);
         dout.alloc((size_t)T * N * 4);
-        part.alloc((size_t)64 << 20);
-        cnt.alloc(8192 * 4);
         status.alloc(4);
         TFFN_CUDA(cudaMemcpy(dx.p, X, (size_t)T * K * 2, cudaMemcpyHostToDevice));
         TFFN_CUDA(cudaMemcpy(dw.p, W, (size_t)N * K * 2, cudaMemcpyHostToDevice));
@@ -359,7 +357,7 @@ int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* 
             g.trace_ctas = trace_ctas;
         }
         cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
-        GemmWorkspace ws{part.as<float>(), part.bytes / 4, cnt.as<int>(), 8192, status.as<int>(), prop.multiProcessorCount};
+        GemmWorkspace ws{status.as<int>(), prop.multiProcessorCount};
         int rc = launch_gemm(g, ws, 0, splits);
         if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");
         if (rc != 0) cuda_check((cudaError_t)rc, "tensor-core GEMM launch", __FILE__, __LINE__);

@@ -175,7 +175,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     const Config& c = m->cfg;
     const size_t H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
     const size_t nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim, L = c.num_layers;
-    const size_t nqkv = (nh + 2 * nkv) * hd;
+
     max_pages_per_seq_ = (max_seq + kPageTokens - 1) / kPageTokens;
     num_pages_ = max_batch * max_pages_per_seq_;
     const size_t layer_stride = (size_t)num_pages_ * nkv * kPageTokens * hd;
@@ -228,15 +228,12 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     }
     h_.alloc(T * H * 2);
     xn_.alloc(T * H * 2);
-    qkv_.alloc(T * nqkv * 4);
     q_.alloc(T * nh * hd * 4);
     ctx_.alloc(T * nh * hd * 2);
     act_b_.alloc(T * I * 2);
     if (e_) act_e_.alloc(T * I * 2);
     xn_last_.alloc(T * H * 2);
     ensure_logits(std::max<size_t>(256, max_batch));
-    gemm_partials_.alloc((size_t)64 << 20);
-    gemm_counters_.alloc(8192 * 4);
     attn_partials_.alloc((size_t)32 << 20);
     attn_counters_.alloc(16384 * 4);
     status_.alloc(4);
@@ -302,10 +299,6 @@ int32_t* Session::pinned_i32(size_t n) {
 
 GemmWorkspace Session::gemm_ws() const {
     GemmWorkspace w;
-    w.partials = gemm_partials_.as<float>();
-    w.partial_floats = gemm_partials_.bytes / 4;
-    w.counters = gemm_counters_.as<int>();
-    w.num_counters = (int)(gemm_counters_.bytes / 4);
     w.status = status_.as<int>();
     w.num_sms = m_->num_sms;
     return w;
@@ -429,7 +422,7 @@ void Session::check_status() {
 
 // ---------------------------------------------------------------- per-launch profile
 const char* kclass_name(int c) {
-    static const char* names[KC_COUNT] = {"embed_rows", "rmsnorm_rows", "gemm_tc:qkv", "qkv_post", "attn_decode",
+    static const char* names[KC_COUNT] = {"embed_rows", "rmsnorm_rows", "gemm_tc:qkv", "attn_decode",
                                           "gemm_tc:o_proj", "gemm_tc:gate_up_swiglu", "gemm_tc:down", "gemm_tc:lm_head",
                                           "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead"};
     return (c >= 0 && c < KC_COUNT) ? names[c] : "?";

@@ -63,7 +63,7 @@ struct Expert {
 
 // kernel classes of the per-launch profile (tffn_session_profile_*)
 enum KClass : int {
-    KC_EMBED = 0, KC_RMSNORM, KC_GEMM_QKV, KC_QKV_POST, KC_ATTENTION, KC_GEMM_OPROJ, KC_GEMM_GATEUP, KC_GEMM_DOWN,
+    KC_EMBED = 0, KC_RMSNORM, KC_GEMM_QKV, KC_ATTENTION, KC_GEMM_OPROJ, KC_GEMM_GATEUP, KC_GEMM_DOWN,
     KC_GEMM_LMHEAD, KC_ARGMAX, KC_ADVANCE, KC_BS1_QKV, KC_BS1_OPROJ, KC_BS1_FFN, KC_BS1_LMHEAD, KC_COUNT
 };
 const char* kclass_name(int c);
@@ -132,9 +132,9 @@ private:
 
     // token metadata and activations of the batched path
     DeviceBuffer tokens_, tok_seq_, tok_pos_, row_idx_, picks_, identity_, dec_tokens_;
-    DeviceBuffer h_, xn_, qkv_, q_, ctx_, act_b_, act_e_, xn_last_, logits_;
+    DeviceBuffer h_, xn_, q_, ctx_, act_b_, act_e_, xn_last_, logits_;
     size_t logits_rows_ = 0;
-    DeviceBuffer gemm_partials_, gemm_counters_, attn_partials_, attn_counters_;
+    DeviceBuffer attn_partials_, attn_counters_;
     DeviceBuffer status_, out_ring_, step_counter_;
     int out_ring_cap_ = 0;
     int* h_status_ = nullptr;  // pinned

@@ -68,11 +68,7 @@ struct GemmCall {
     bool pdl;          // launch with programmatic dependent launch (the kernel waits before touching X / out)
 };
 struct GemmWorkspace {
-    float* partials;        // split-K partial tiles
-    size_t partial_floats;  // capacity
-    int* counters;          // one ticket per output tile, zero on entry and on exit
-    int num_counters;
-    int* status;            // device status word
+    int* status;  // device status word
     int num_sms;
 };
 // opt the kernels into their dynamic shared memory sizes (once per device, outside stream capture)
@@ -87,10 +83,6 @@ void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, i
                   bool pdl = false, unsigned long long* tl = nullptr);
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
                     bool pdl = false, unsigned long long* tl = nullptr);
-// qkv fp32 [T, (nh+2nkv)*hd] -> bf16 round, bias (bf16 add), RoPE, q fp32 [T, nh*hd], K/V into pages
-void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
-                     const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
-                     int T, int nh, int max_pos, int* status, cudaStream_t s, bool pdl = false);
 // logits fp32 [R, V] -> argmax (lowest index among maxima). scratch (>= 2 * R * 64 floats) and
 // counters (>= R ints, zero, left zero) let several blocks share a row; without them one block per row.
 void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,

@@ -94,61 +94,6 @@ __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x
     if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
-// After the fused q|k|v GEMM (fp32 accumulators): round to bf16, add the bias in bf16
-// (k_add_bias, qwen.cu:223-226), rotate q and k in fp32 at the token's position
-// (k_rope, qwen.cu:232-244), keep q in fp32, round k to bf16 into its page, store v as bf16
-// (qwen.cu:339-346). grid (T, nh + 2*nkv), block hd/2: thread i owns the pair (i, i + hd/2).
-__global__ void k_qkv_post(const float* __restrict__ qkv, const bf16* __restrict__ bq, const bf16* __restrict__ bk,
-                           const bf16* __restrict__ bv, const float* __restrict__ rope_cos,
-                           const float* __restrict__ rope_sin, const int* __restrict__ tok_seq,
-                           const int* __restrict__ tok_pos, float* __restrict__ q_out, KvView kv, int layer, int nh,
-                           int max_pos, int* status) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = blockIdx.x, head = blockIdx.y, i = threadIdx.x;
-    const int hd = kv.hd, half = hd >> 1, nkv = kv.nkv;
-    const int nq = nh * hd, nk = nkv * hd, ntot = nq + 2 * nk;
-    const int pos = __ldcg(tok_pos + t), seq = __ldcg(tok_seq + t);
-    const float* row = qkv + (size_t)t * ntot;
-    int col0;
-    const bf16* bias;
-    int kind;  // 0 q, 1 k, 2 v
-    int hh;
-    if (head < nh) { kind = 0; hh = head; col0 = head * hd; bias = bq ? bq + head * hd : nullptr; }
-    else if (head < nh + nkv) { kind = 1; hh = head - nh; col0 = nq + hh * hd; bias = bk ? bk + hh * hd : nullptr; }
-    else { kind = 2; hh = head - nh - nkv; col0 = nq + nk + hh * hd; bias = bv ? bv + hh * hd : nullptr; }
-    float x0 = bf16_round(__ldcg(row + col0 + i)), x1 = bf16_round(__ldcg(row + col0 + i + half));
-    if (bias) {
-        x0 = bf16_round(x0 + __bfloat162float(bias[i]));
-        x1 = bf16_round(x1 + __bfloat162float(bias[i + half]));
-    }
-    if (pos < 0 || pos >= max_pos) {
-        if (i == 0) dev_fail(status, DEV_ERR_BOUNDS);
-        return;
-    }
-    if (kind != 2) {
-        const float c = rope_cos[(size_t)pos * half + i], s = rope_sin[(size_t)pos * half + i];
-        const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
-        x0 = r0;
-        x1 = r1;
-    }
-    if (kind == 0) {
-        float* qo = q_out + (size_t)t * nq + hh * hd;
-        qo[i] = x0;
-        qo[i + half] = x1;
-        return;
-    }
-    const int pg = __ldcg(kv.block_table + (size_t)seq * kv.max_pages_per_seq + pos / kPageTokens);
-    if (pg < 0 || pg >= kv.num_pages) {
-        if (i == 0) dev_fail(status, DEV_ERR_BOUNDS);
-        return;
-    }
-    bf16* pool = (kind == 1 ? kv.k_pool : kv.v_pool) + (size_t)layer * kv.layer_stride;
-    bf16* dst = pool + (((size_t)pg * nkv + hh) * kPageTokens + pos % kPageTokens) * hd;
-    dst[i] = __float2bfloat16_rn(x0);
-    dst[i + half] = __float2bfloat16_rn(x1);
-}
-
 // greedy pick: first index of the strict maximum (sample(), inference/src/main.cpp:45-51).
 // grid (rows, S): block (r, s) scans slice s of row r; the last block of a row to finish (a ticket, no
 // spinning) combines the S partial results, so the pick does not depend on scheduling.
@@ -259,13 +204,6 @@ void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, i
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
                     bool pdl, unsigned long long* tl) {
     launch_k(k_rmsnorm_rows, dim3(T), dim3(128), 0, s, pdl, x, w, out, H, eps, row_idx, tl);
-}
-void launch_qkv_post(const float* qkv, const bf16* bq, const bf16* bk, const bf16* bv, const float* rope_cos,
-                     const float* rope_sin, const int* tok_seq, const int* tok_pos, float* q_out, KvView kv, int layer,
-                     int T, int nh, int max_pos, int* status, cudaStream_t s, bool pdl) {
-    dim3 grid(T, nh + 2 * kv.nkv);
-    launch_k(k_qkv_post, grid, dim3(kv.hd / 2), 0, s, pdl, qkv, bq, bk, bv, rope_cos, rope_sin, tok_seq, tok_pos, q_out, kv,
-             layer, nh, max_pos, status);
 }
 void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,
                    int num_counters, int num_sms, cudaStream_t s, bool pdl, unsigned long long* tl) {
