@@ -55,36 +55,56 @@ __device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uin
     lo = (uint32_t)bf16_bits(x - __bfloat162float(xh)) | ((uint32_t)bf16_bits(y - __bfloat162float(yh)) << 16);
 }
 
+constexpr int kAttnCtaThreads = 256;  // 8 warps: each takes 16 keys of a 128-key stage
+constexpr int kAttnWarps = kAttnCtaThreads / 32;
+
 template <int HD>
 struct AttnCfg {
     static constexpr int ROW_BYTES = HD * 2;
     static constexpr int GRAN = HD / 8;                // 16-byte granules per cached row
-    static constexpr int STAGE_ROWS = 8192 / HD;       // 16 KB of K and of V per stage: 128 rows at hd 64
-    static constexpr int WARP_ROWS = STAGE_ROWS / 4;   // rows of a stage per warp: 32 or 16
+    static constexpr int STAGE_ROWS = 128;             // keys per stage
+    static constexpr int NST = 256 / HD;               // stage buffers: 4 at head_dim 64, 2 at 128 (128 KB either way)
+    static constexpr int WARP_ROWS = STAGE_ROWS / kAttnWarps;  // 16 keys of a stage per warp
     static constexpr int NT = WARP_ROWS / 8;           // 8-key tiles of S per warp and stage
     static constexpr int KB = WARP_ROWS / 16;          // 16-key steps of P V
     static constexpr int KS = HD / 16;                 // k-steps of Q K^T
     static constexpr int DT = HD / 8;                  // 8-wide tiles of the output row
     static constexpr int STAGE_BYTES = 2 * STAGE_ROWS * ROW_BYTES;  // K then V
-    static constexpr int MERGE_FLOATS = 4 * 8 * (HD + 2);           // per warp and head: max, sum, O[HD]
-    static constexpr int SMEM = 2 * STAGE_BYTES + MERGE_FLOATS * 4;
+    static constexpr int MERGE_FLOATS = kAttnWarps * 8 * (HD + 2);  // per warp and head: max, sum, O[HD]
+    static constexpr int SMEM = NST * STAGE_BYTES;                  // the merge buffer reuses the first stage
+    static_assert(MERGE_FLOATS * 4 <= STAGE_BYTES, "merge buffer must fit a stage");
+    static_assert(NST >= 2 && KB >= 1, "");
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
+__global__ void __launch_bounds__(kAttnCtaThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
                                                               const int* __restrict__ tok_seq,
                                                               const int* __restrict__ tok_pos, bf16* __restrict__ ctx,
                                                               int nh, int G, int splits, int early,
                                                               float* __restrict__ ws, int* __restrict__ counters,
-                                                              int* status, unsigned long long* tl) {
+                                                              int* status, unsigned long long* tl,
+                                                              unsigned long long* trace) {
     using C = AttnCfg<HD>;
+    // optional per-CTA phase stamps (globaltimer ns), 16 per CTA: 0 entry, 1 token data read, 2 first
+    // stages requested, 3 grid wait over, 4 first stage landed, 5 all keys processed, 6 partial result
+    // written, 7 ticket taken, 8 exit
+#define ATTN_TRACE(slot)                                                                              \
+    do {                                                                                              \
+        if (trace && threadIdx.x == 0) {                                                              \
+            unsigned long long t_;                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
+            trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (slot)] = t_;                  \
+        }                                                                                             \
+    } while (0)
+    ATTN_TRACE(0);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
-    float* merge = (float*)(smem + 2 * C::STAGE_BYTES);  // [warp][head][HD + 2]
+    // [warp][head][HD + 2]; in the first stage buffer, which is idle once every warp has left the key loop
+    float* merge = (float*)smem;
 
     // With `early` (decode) everything but q and the newest cached row (the one the previous kernel
     // wrote, at position tok_pos[t]) is older than the previous kernel, so token data, block table and
-    // the first two stages of K/V are requested before waiting for it; the newest row follows after.
+    // the first NST stages of K/V are requested before waiting for it; the newest row follows after.
     if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     if (!early) pdl_wait();
@@ -100,42 +120,50 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     chunk = (chunk + kPageTokens - 1) / kPageTokens * kPageTokens;
     const int c_begin = split * chunk;
     const int c_end = min(ctx_len, c_begin + chunk);
+    ATTN_TRACE(1);
     const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
     const bf16* kpool = kv.k_pool + (size_t)layer * kv.layer_stride;
     const bf16* vpool = kv.v_pool + (size_t)layer * kv.layer_stride;
     const uint32_t smem_base = smem_u32(smem);
     bool bad = false;
 
-    // Copy of one stage: every thread moves GRAN * STAGE_ROWS / 128 granules of K and of V. Rows past
-    // the end of the range (or of a bad page) are zero-filled: their P is 0, and 0 * garbage could be NaN.
-    auto issue_stage = [&](int st) {
-        const int s_begin = c_begin + st * C::STAGE_ROWS;  // a multiple of the page size
-        const uint32_t kbuf = smem_base + (uint32_t)((st & 1) * C::STAGE_BYTES);
-        const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+    // Every warp owns rows [warp * 16, warp * 16 + 16) of every stage: it copies them itself and is the
+    // only one to read them, so the key loop needs no CTA-wide barrier and the warps run independently.
+    // The 16 rows lie in one page; the page ids of the warp's rows in stages 0..31 are fetched up front
+    // (lane = stage), so that no copy waits behind a table lookup. Rows past the end of the range (or of
+    // a bad page) are zero-filled: their P is 0, and 0 * garbage could be NaN.
+    const int wrow0 = warp * C::WARP_ROWS;
+    int pg_lane = -1;
+    {
+        const int tok0 = c_begin + lane * C::STAGE_ROWS + wrow0;
+        if (tok0 < c_end) {
+            const int pg = __ldg(bt + tok0 / kPageTokens);
+            if (pg < 0 || pg >= kv.num_pages) bad = true;
+            else pg_lane = pg;
+        }
+    }
+    auto issue_stage = [&](int st) {  // the whole warp calls it
+        const int s_begin = c_begin + st * C::STAGE_ROWS + wrow0;  // first key of this warp in the stage
         if (s_begin < c_end) {
-            // the page ids of the stage first (independent loads, the same for every thread), so that no
-            // copy waits behind another copy's table lookup
-            constexpr int PPS = C::STAGE_ROWS / kPageTokens;
-            int pgs[PPS];
-#pragma unroll
-            for (int j = 0; j < PPS; ++j) {
-                const int tok0 = s_begin + j * kPageTokens;
-                const bool pv = tok0 < c_end;
-                const int pg = pv ? __ldg(bt + tok0 / kPageTokens) : -1;
-                if (pv && (pg < 0 || pg >= kv.num_pages)) bad = true;
-                pgs[j] = (pg >= 0 && pg < kv.num_pages) ? pg : -1;
+            int pg;
+            if (st < 32) {
+                pg = __shfl_sync(0xffffffffu, pg_lane, st);
+            } else {
+                pg = __ldg(bt + s_begin / kPageTokens);
+                if (pg < 0 || pg >= kv.num_pages) { bad = true; pg = -1; }
             }
-            constexpr int ROWS_PER_IT = kAttnThreads / C::GRAN;
-            const int row0 = tid / C::GRAN, g = tid % C::GRAN;
+            const uint32_t kbuf = smem_base + (uint32_t)((st % C::NST) * C::STAGE_BYTES);
+            const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+            const size_t page_off = ((size_t)(pg >= 0 ? pg : 0) * nkv + kvh) * kPageTokens * HD;
 #pragma unroll
-            for (int i = 0; i < C::STAGE_ROWS / ROWS_PER_IT; ++i) {
-                const int row = i * ROWS_PER_IT + row0;
-                const int pg = pgs[(i * ROWS_PER_IT) / kPageTokens];
-                const int tok = s_begin + row;
+            for (int i = 0; i < C::WARP_ROWS * C::GRAN / 32; ++i) {
+                const int idx = i * 32 + lane;
+                const int r = idx / C::GRAN, g = idx % C::GRAN;
+                const int row = wrow0 + r, tok = s_begin + r;
                 const bool valid = tok < c_end && pg >= 0;
-                const size_t off = (((size_t)(valid ? pg : 0) * nkv + kvh) * kPageTokens + row % kPageTokens) * HD + g * 8;
+                const size_t off = page_off + (size_t)(tok % kPageTokens) * HD + g * 8;
                 const uint32_t dst = (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4));
-                if (!(early && st < 2 && tok == ctx_len - 1)) {  // the newest row is copied after the wait
+                if (!(early && st < C::NST && tok == ctx_len - 1)) {  // the newest row is copied after the wait
                     cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
                     cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
                 }
@@ -144,18 +172,23 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         cp_async_commit();
     };
     const int n_stages = c_end > c_begin ? (c_end - c_begin + C::STAGE_ROWS - 1) / C::STAGE_ROWS : 0;
-    issue_stage(0);
-    issue_stage(1);
+#pragma unroll
+    for (int st = 0; st < C::NST; ++st) issue_stage(st);
+    ATTN_TRACE(2);
     if (tid == 0 && !early) tl_mark(tl, 1);
     if (early) {
+        // page of the newest row (the table entry is in L1 by now: the up-front lookups read it)
+        const int newest_pg = ctx_len > 0 ? __ldg(bt + (ctx_len - 1) / kPageTokens) : -1;
         pdl_wait();
+        ATTN_TRACE(3);
         if (tid == 0) tl_mark(tl, 1);
         const int rel = ctx_len - 1 - c_begin;  // newest row, relative to this split
-        if (rel >= 0 && rel < 2 * C::STAGE_ROWS && ctx_len - 1 < c_end && tid < C::GRAN) {
-            const int row = rel % C::STAGE_ROWS, g = tid;
+        if (rel >= 0 && rel < C::NST * C::STAGE_ROWS && ctx_len - 1 < c_end && (rel % C::STAGE_ROWS) / C::WARP_ROWS == warp &&
+            lane < C::GRAN) {
+            const int row = rel % C::STAGE_ROWS, g = lane;
             const uint32_t kbuf = smem_base + (uint32_t)((rel / C::STAGE_ROWS) * C::STAGE_BYTES);
             const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
-            int pg = __ldcg(bt + (ctx_len - 1) / kPageTokens);
+            int pg = newest_pg;
             const bool valid = pg >= 0 && pg < kv.num_pages;
             if (!valid) { bad = true; pg = 0; }
             const size_t off = (((size_t)pg * nkv + kvh) * kPageTokens + (ctx_len - 1) % kPageTokens) * HD + g * 8;
@@ -189,13 +222,17 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
 #pragma unroll
     for (int d = 0; d < C::DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
+    // One copy group per stage, committed in stage order (empty past the end of the range), and with
+    // `early` one more for the newest row after the first NST: stage st has landed once at most NST - 1
+    // younger groups are pending. The first iteration of an early launch also needs the newest row.
     for (int st = 0; st < n_stages; ++st) {
-        if (st + 1 < n_stages && !(early && st == 0)) cp_async_wait<1>();  // the newest row is the last group
-        else cp_async_wait<0>();
-        __syncthreads();
+        if (early && st == 0) cp_async_wait<0>();
+        else cp_async_wait<C::NST - 1>();
+        __syncwarp();  // the lanes' copies of this warp's rows are complete and visible to the warp
+        if (st == 0) ATTN_TRACE(4);
         const int w_begin = c_begin + st * C::STAGE_ROWS + warp * C::WARP_ROWS;  // first key of this warp
         if (w_begin < c_end) {
-            const uint32_t kbuf = smem_base + (uint32_t)((st & 1) * C::STAGE_BYTES);
+            const uint32_t kbuf = smem_base + (uint32_t)((st % C::NST) * C::STAGE_BYTES);
             const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
             // ---- S = Q K^T for WARP_ROWS keys: NT tiles of 8 keys
             float s[C::NT][4];
@@ -253,12 +290,14 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
                 }
             }
         }
-        __syncthreads();  // every warp is done with this buffer
-        if (st + 2 < n_stages) issue_stage(st + 2);
+        __syncwarp();  // every lane is done with the warp's rows of this buffer
+        issue_stage(st + C::NST);  // commits a group even when there is nothing left to copy
     }
     cp_async_wait<0>();
+    __syncthreads();  // every warp has left the key loop: the first stage buffer becomes the merge buffer
+    ATTN_TRACE(5);
 
-    // ---- merge the four warps: (max, sum, O) of head hrow per warp
+    // ---- merge the eight warps: (max, sum, O) of head hrow per warp
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     {
@@ -273,14 +312,14 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
     __syncthreads();
     float* part = ws + ((size_t)unit * splits + split) * (size_t)(G * (HD + 2));
     bf16* ctx_tok = ctx + (size_t)t * nh * HD;
-    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+    for (int idx = tid; idx < G * HD; idx += kAttnCtaThreads) {
         const int g = idx / HD, d = idx % HD;
         float M = kNegBig;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, merge[(size_t)(w * 8 + g) * (HD + 2)]);
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, merge[(size_t)(w * 8 + g) * (HD + 2)]);
         float L = 0.f, A = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < kAttnWarps; ++w) {
             const float* mw = merge + (size_t)(w * 8 + g) * (HD + 2);
             const float wgt = __expf(mw[0] - M);
             L += mw[1] * wgt;
@@ -294,6 +333,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         }
     }
     if (bad) dev_fail(status, DEV_ERR_BOUNDS);
+    ATTN_TRACE(6);
     if (splits == 1) {
         if (tid == 0) tl_mark(tl, 2);
         return;
@@ -307,41 +347,99 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const float* __res
         if (old == splits - 1) counters[unit] = 0;
     }
     __syncthreads();
+    ATTN_TRACE(7);
     if (!s_last) {
         if (tid == 0) tl_mark(tl, 2);
         return;
     }
     __threadfence();
     const float* parts = ws + (size_t)unit * splits * (size_t)(G * (HD + 2));
-    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
-        const int g = idx / HD, d = idx % HD;
-        ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits(parts, splits, G, HD, g, d));
+    constexpr int kMergeSplits = 16;  // up to here: one pass with every load in flight
+    if (splits <= kMergeSplits) {
+        // weight of split z for head g: exp(m_z - M) / sum_z l_z exp(m_z - M), kept in the (idle) merge buffer
+        float* wgt = merge;  // [g][kMergeSplits]
+        if (tid < G) {
+            float mz[kMergeSplits], lz[kMergeSplits];
+#pragma unroll
+            for (int z = 0; z < kMergeSplits; ++z) {
+                const bool live = z < splits;
+                const float* pz = parts + (size_t)(live ? z : 0) * G * (HD + 2) + tid * (HD + 2);
+                mz[z] = live ? __ldcg(pz) : kNegBig;
+                lz[z] = live ? __ldcg(pz + 1) : 0.f;
+            }
+            float M = kNegBig, L = 0.f;
+#pragma unroll
+            for (int z = 0; z < kMergeSplits; ++z) M = fmaxf(M, mz[z]);
+#pragma unroll
+            for (int z = 0; z < kMergeSplits; ++z) {  // split order
+                mz[z] = z < splits ? __expf(mz[z] - M) : 0.f;
+                L += lz[z] * mz[z];
+            }
+#pragma unroll
+            for (int z = 0; z < kMergeSplits; ++z) wgt[tid * kMergeSplits + z] = mz[z] / L;
+        }
+        __syncthreads();
+        constexpr int ITERS = (8 * HD + kAttnCtaThreads - 1) / kAttnCtaThreads;  // G <= 8
+        float res[ITERS];
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int idx = tid + it * kAttnCtaThreads;
+            const bool on = idx < G * HD;
+            const int g = on ? idx / HD : 0, d = on ? idx % HD : 0;
+            float A = 0.f;
+            for (int z0 = 0; z0 < splits; z0 += 4) {
+                float az[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    az[j] = (on && z0 + j < splits) ? __ldcg(parts + (size_t)(z0 + j) * G * (HD + 2) + g * (HD + 2) + 2 + d) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (z0 + j < splits) A += az[j] * wgt[g * kMergeSplits + z0 + j];
+            }
+            res[it] = A;
+        }
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int idx = tid + it * kAttnCtaThreads;
+            if (idx < G * HD) ctx_tok[(size_t)(kvh * G + idx / HD) * HD + idx % HD] = __float2bfloat16_rn(res[it]);
+        }
+    } else {
+        for (int idx = tid; idx < G * HD; idx += kAttnCtaThreads) {
+            const int g = idx / HD, d = idx % HD;
+            ctx_tok[(size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(attn_merge_splits(parts, splits, G, HD, g, d));
+        }
     }
+    ATTN_TRACE(8);
     if (tid == 0) tl_mark(tl, 2);
+#undef ATTN_TRACE
 }
 
 template <int HD>
 void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                const int* tok_pos, bf16* ctx, int nh, int G, int splits, int early, float* ws, int* counters, int* status,
-               unsigned long long* tl) {
+               unsigned long long* tl, unsigned long long* trace) {
     static bool configured = false;  // benign race: the call is idempotent
     if (!configured) {
         cudaFuncSetAttribute(k_attn_decode<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
         configured = true;
     }
-    launch_k(k_attn_decode<HD>, grid, dim3(kAttnThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
-             nh, G, splits, early, ws, counters, status, tl);
+    launch_k(k_attn_decode<HD>, grid, dim3(kAttnCtaThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
+             nh, G, splits, early, ws, counters, status, tl, trace);
 }
 
 }  // namespace
 
 int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
+    // One CTA per SM is the target: a CTA holds 128 KB of K/V in flight and its eight warps keep up with
+    // what one SM can take in, and a launch without splits needs no merge (a partial write, a ticket and a
+    // second read-back cost about 6 us per launch when measured with three splits). Splits are used only
+    // when there are fewer (token, kv head) units than half the SMs, with at least one stage per split.
     const int G = nh / nkv;
     const int units = T * nkv;
     int splits = 1;
-    if (units < 2 * num_sms) {
-        splits = (2 * num_sms + units - 1) / units;
-        const int max_splits = (max_ctx + 2 * kPageTokens - 1) / (2 * kPageTokens);  // at least 64 rows per split
+    if (units * 2 <= num_sms) {
+        splits = num_sms / units;
+        const int max_splits = (max_ctx + 127) / 128;
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
         while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))
@@ -352,14 +450,15 @@ int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWork
 
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl,
-                      bool only_newest_row_fresh, unsigned long long* tl) {
+                      bool only_newest_row_fresh, unsigned long long* tl, unsigned long long* trace, int trace_ctas) {
     const int early = (pdl && only_newest_row_fresh) ? 1 : 0;
     const int G = nh / kv.nkv;  // at most 8 (checked when the model is loaded)
     const int units = T * kv.nkv;
     const int splits = attention_splits(T, nh, kv.nkv, kv.hd, max_ctx, ws, num_sms);
     dim3 grid(units, splits);
-    if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl);
-    else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl);
+    if ((long long)units * splits > trace_ctas) trace = nullptr;
+    if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl, trace);
+    else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl, trace);
 }
 
 }  // namespace tffn

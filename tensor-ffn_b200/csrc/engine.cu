@@ -547,10 +547,13 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         gemm(g, KC_GEMM_QKV);
         g.qkv = nullptr;
         prof_begin(KC_ATTENTION);
-        if (live(KC_ATTENTION))
+        if (live(KC_ATTENTION)) {
+            unsigned long long* tl = tl_next(KC_ATTENTION);
+            const bool traced = tl_on_ && (int)tl_cls_.size() - 1 == tl_trace_launch_;
             launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
-                             status, stream_, pdl, decode /* the step's first kernel (embed) is a full dependency */,
-                             tl_next(KC_ATTENTION));
+                             status, stream_, pdl, decode /* the step's first kernel (embed) is a full dependency */, tl,
+                             traced ? tl_trace_buf_.as<unsigned long long>() : nullptr, (int)(tl_trace_buf_.bytes / (16 * 8)));
+        }
         prof_end();
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};

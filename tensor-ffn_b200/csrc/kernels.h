@@ -103,7 +103,8 @@ int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWork
 // dependent launch; the rest may then be fetched before the previous kernel has finished.
 void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, bf16* ctx, int T,
                       int nh, int max_ctx, AttnWorkspace ws, int num_sms, int* status, cudaStream_t s, bool pdl = false,
-                      bool only_newest_row_fresh = false, unsigned long long* tl = nullptr);
+                      bool only_newest_row_fresh = false, unsigned long long* tl = nullptr,
+                      unsigned long long* trace = nullptr, int trace_ctas = 0);  // trace: 16 u64 per CTA, see attn.cu
 
 // ------------------------------------------------------------------ batch-1 fused decode kernels
 struct Bs1Layer {

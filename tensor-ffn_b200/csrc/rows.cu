@@ -28,69 +28,45 @@ __global__ void k_embed_rows(const int* __restrict__ tokens, const bf16* __restr
 }
 
 // out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w))  (k_rmsnorm, inference/src/backend/cuda_ops.cu:75-96)
-// The row stays in registers between the two passes (up to 8 x 16 bytes per thread, i.e. H <= 8192;
-// anything beyond that is read a second time).
 __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                       bf16* __restrict__ out, int H, float eps,
                                                       const int* __restrict__ row_idx, unsigned long long* tl) {
     if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
-    const int r = blockIdx.x;
-    const int n16 = H / 8;
-    const uint4* wr = (const uint4*)w;
-    constexpr int KEEP = 8;
-    uint4 g[KEEP];  // the norm weights do not depend on the previous kernel
-#pragma unroll
-    for (int u = 0; u < KEEP; ++u) {
-        const int i = threadIdx.x + u * 128;
-        g[u] = i < n16 ? __ldg(wr + i) : make_uint4(0, 0, 0, 0);
-    }
     pdl_wait();
     if (threadIdx.x == 0) tl_mark(tl, 1);
+    const int r = blockIdx.x;
     const int src_row = row_idx ? row_idx[r] : r;
     const uint4* xr = (const uint4*)(x + (size_t)src_row * H);
-    uint4 v[KEEP];
     float ss = 0.f;
-#pragma unroll
-    for (int u = 0; u < KEEP; ++u) {
-        const int i = threadIdx.x + u * 128;
-        v[u] = i < n16 ? __ldcg(xr + i) : make_uint4(0, 0, 0, 0);
-    }
-    auto sq = [&](const uint4& q) {
-        const uint32_t u4[4] = {q.x, q.y, q.z, q.w};
+    for (int i = threadIdx.x; i < H / 8; i += 128) {
+        uint4 v = __ldcg(xr + i);
+        uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float a = bf16_lo(u4[j]), b = bf16_hi(u4[j]);
+            float a = bf16_lo(u[j]), b = bf16_hi(u[j]);
             ss += a * a + b * b;
         }
-    };
-#pragma unroll
-    for (int u = 0; u < KEEP; ++u) sq(v[u]);
-    for (int i = threadIdx.x + KEEP * 128; i < n16; i += 128) sq(__ldcg(xr + i));
+    }
     __shared__ float red[4];
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     ss = red[0] + red[1] + red[2] + red[3];
     const float rinv = rsqrtf(ss / (float)H + eps);
+    const uint4* wr = (const uint4*)w;
     uint4* orow = (uint4*)(out + (size_t)r * H);
-    auto scale = [&](const uint4& q, const uint4& gq) {
-        const uint32_t u4[4] = {q.x, q.y, q.z, q.w}, gw[4] = {gq.x, gq.y, gq.z, gq.w};
-        uint32_t o[4];
+    for (int i = threadIdx.x; i < H / 8; i += 128) {
+        uint4 v = __ldcg(xr + i), g = __ldg(wr + i);
+        uint32_t u[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w}, o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float a = bf16_lo(u4[j]) * rinv * bf16_lo(gw[j]);
-            const float b = bf16_hi(u4[j]) * rinv * bf16_hi(gw[j]);
+            float a = bf16_lo(u[j]) * rinv * bf16_lo(gw[j]);
+            float b = bf16_hi(u[j]) * rinv * bf16_hi(gw[j]);
             o[j] = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
         }
-        return make_uint4(o[0], o[1], o[2], o[3]);
-    };
-#pragma unroll
-    for (int u = 0; u < KEEP; ++u) {
-        const int i = threadIdx.x + u * 128;
-        if (i < n16) orow[i] = scale(v[u], g[u]);
+        orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    for (int i = threadIdx.x + KEEP * 128; i < n16; i += 128) orow[i] = scale(__ldcg(xr + i), __ldg(wr + i));
     if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
