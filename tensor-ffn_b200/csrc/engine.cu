@@ -624,14 +624,26 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.op[0] = {m_->lm_head, H, xn_last_.as<bf16>(), H, H};
         g.N = V;
         g.mode = GEMM_STORE_F32;
-        g.out = logits_.p;
         g.ldo = V;
+        // The greedy pick rides in the LM head's epilogue (per-tile maxima, combined by a tiny kernel); the
+        // fp32 logits themselves are written only when the caller asked for them. The attention workspace is
+        // idle by now and serves as scratch.
+        const AttnWorkspace aw = attn_ws();
+        const int v_tiles = (V + 127) / 128;
+        const bool fused_pick = (size_t)n_logit_rows * v_tiles * 2 <= aw.partial_floats;
+        if (fused_pick) {
+            g.amax_val = aw.partials;
+            g.amax_idx = (int*)(aw.partials + (size_t)n_logit_rows * v_tiles);
+        }
+        g.out = (store_logits_ || !fused_pick) ? logits_.p : nullptr;
         gemm(g, KC_GEMM_LMHEAD);
         prof_begin(KC_ARGMAX);
         if (live(KC_ARGMAX)) {
-            const AttnWorkspace aw = attn_ws();  // idle by now: its partials and (zero) counters serve as scratch
-            launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), aw.partials, aw.partial_floats, aw.counters,
-                          aw.num_counters, m_->num_sms, stream_, pdl, tl_next(KC_ARGMAX));
+            if (fused_pick)
+                launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX));
+            else
+                launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), aw.partials, aw.partial_floats, aw.counters,
+                              aw.num_counters, m_->num_sms, stream_, pdl, tl_next(KC_ARGMAX));
         }
         prof_end();
         launches_ += 2;
@@ -836,7 +848,7 @@ void Session::run_decode_batched(int n_seqs, int max_ctx) {
     }
     const Config& c = m_->cfg;
     const int splits = attention_splits(n_seqs, c.num_heads, c.num_kv_heads, c.head_dim, max_ctx, attn_ws(), m_->num_sms);
-    const auto key = std::make_pair(n_seqs, splits);
+    const auto key = std::make_pair(n_seqs, splits * 2 + (store_logits_ ? 1 : 0));
     auto it = dec_graphs_.find(key);
     if (it == dec_graphs_.end()) {
         cudaGraph_t graph = nullptr;
@@ -910,6 +922,7 @@ void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs
         TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * T, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
         if (!last_rows.empty())
             TFFN_CUDA(cudaMemcpyAsync(row_idx_.p, pin + 3 * T, last_rows.size() * 4, cudaMemcpyHostToDevice, stream_));
+        store_logits_ = logits_last != nullptr;
         run_batched(T, (int)last_rows.size(), false, false, max_ctx);
         if (!last_rows.empty()) {
             std::vector<int> picks(last_rows.size());
@@ -957,6 +970,7 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
         TFFN_CUDA(cudaMemcpyAsync(tokens_.p, pin, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
         TFFN_CUDA(cudaMemcpyAsync(tok_seq_.p, pin + n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
         TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+        store_logits_ = logits != nullptr;
         if (logits) {
             run_batched(n, n, true, false, h_seq_len_[slot] + c0 + n);
             TFFN_CUDA(cudaMemcpyAsync(logits + (size_t)c0 * V, logits_.p, (size_t)n * V * 4, cudaMemcpyDeviceToHost, stream_));
@@ -1000,6 +1014,7 @@ void Session::decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_to
     } else {
         int max_ctx = 1;
         for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + 1);
+        store_logits_ = logits != nullptr;
         run_decode_batched(n_seqs, max_ctx);
     }
     TFFN_CUDA(cudaMemcpyAsync(pin, dec_tokens_.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, stream_));
@@ -1025,6 +1040,7 @@ void Session::decode_run(int n_seqs, int steps, int32_t* tokens_out) {
         if (bs1) {
             run_bs1(false);
         } else {
+            store_logits_ = false;  // a device-resident loop hands out tokens only
             run_decode_batched(n_seqs, max_ctx);
         }
     }

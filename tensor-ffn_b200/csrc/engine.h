@@ -111,6 +111,7 @@ private:
     bool own_stream_ = false;
     int launch_mode_ = 1;
     unsigned ablate_mask_ = 0;
+    bool store_logits_ = true;  // whether the LM head writes its fp32 logits (the greedy pick does not need them)
     bool tl_on_ = false;
     DeviceBuffer tl_buf_;
     std::vector<int> tl_cls_;

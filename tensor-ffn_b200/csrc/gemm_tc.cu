@@ -47,6 +47,8 @@ struct GemmDev {
     GemmQkvEpilogue qkv;  // GEMM_QKV only
     unsigned long long* trace;  // optional: 64 timestamps (ns) per CTA, see GemmCall::trace
     unsigned long long* tl;     // optional: step timeline of this launch
+    float* amax_val;            // GEMM_STORE_F32: per (token, tile) maximum and its index, or nullptr
+    int* amax_idx;
 };
 
 __device__ __forceinline__ unsigned long long gtime_ns() {
@@ -71,7 +73,7 @@ struct GemmCfg {
     static constexpr int MAX_STAGES = (196 * 1024 / STAGE_BYTES) > 10 ? 10 : (196 * 1024 / STAGE_BYTES);
     static constexpr int SHARED_STAGES = (BN <= 64) ? 4 : MAX_STAGES;
     // the epilogue parks one fp32 plane [BN][128] in the (by then idle) stage memory
-    static_assert(BN * BM * 4 <= SHARED_STAGES * STAGE_BYTES, "plane must fit the smallest ring");
+    static_assert(BN * BM * 4 + BN * 8 <= SHARED_STAGES * STAGE_BYTES, "plane (+ per-token maxima) must fit the smallest ring");
     static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/; }
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulators, power of two
 };
@@ -179,6 +181,7 @@ __device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int 
     const float f[4] = {v.x, v.y, v.z, v.w};
     switch (p.mode) {
         case GEMM_STORE_F32:
+            if (!out) break;  // only the fused arg-max was asked for
             if (vec) {
                 *(float4*)((float*)out + o) = v;
             } else {
@@ -210,6 +213,33 @@ __device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int 
     }
 }
 
+// Fused greedy pick (GEMM_STORE_F32): all 32 lanes of the warp that finished tile column t hold rows
+// n .. n+3 of it; the tile's maximum and its index (lowest index among equal maxima: sample(),
+// inference/src/main.cpp:45-51) go to amax_val / amax_idx [t][tile].
+__device__ __forceinline__ void warp_amax(const GemmDev& p, int n, float4 v, float& best, int& bi) {
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    best = -INFINITY;
+    bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (n + j < p.N && (f[j] > best || (f[j] == best && n + j < bi))) { best = f[j]; bi = n + j; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+}
+__device__ __forceinline__ void publish_amax(const GemmDev& p, int n, int t, float4 v, int lane) {
+    if (!p.amax_val) return;
+    float best;
+    int bi;
+    warp_amax(p, n, v, best, bi);
+    if (lane == 0) {
+        p.amax_val[(size_t)t * gridDim.x + blockIdx.x] = best;
+        p.amax_idx[(size_t)t * gridDim.x + blockIdx.x] = bi;
+    }
+}
 __device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t addr) {
     float4 v;
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
@@ -405,10 +435,11 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
         if (threadIdx.x == 64) TFFN_TRACE(6);
         if (warp < 2) cluster_arrive();
     }
-    if (warp >= 2 && n_iters > 0 && p.splits == 1 && p.mode != GEMM_QKV) {
-        // Unsplit tile: every column comes from this CTA's own plane, nothing to wait for, so four
-        // columns per warp are in flight at a time.
-        const int w = warp - 2;
+    constexpr int kWarps = kGemmThreads / 32;
+    if (n_iters > 0 && p.splits == 1 && p.mode != GEMM_QKV) {
+        // Unsplit tile: every column comes from this CTA's own plane, nothing to wait for, so all six
+        // warps (the copy and MMA warps are idle by now) take columns, four in flight per warp.
+        const int w = warp;
         const int ncols = min(BN, p.T - t0);
         const float* plane = (const float*)smem;
         if (threadIdx.x == 64) TFFN_TRACE(9);
@@ -419,7 +450,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             const int nn = n0 + 2 * lane;
             const bool pair = nn + 1 < p.N && (p.ldo & 1) == 0;
 #pragma unroll 4
-            for (int c = w; c < ncols; c += 4) {
+            for (int c = w; c < ncols; c += kWarps) {
                 const float2 g = *(const float2*)(plane + (size_t)c * BM + 2 * lane);
                 const float2 u = *(const float2*)(plane + (size_t)c * BM + 64 + 2 * lane);
                 const float a0 = silu_mul_bf16(g.x, u.x), a1 = silu_mul_bf16(g.y, u.y);
@@ -435,9 +466,37 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
             const int n = n0 + lane * 4;
             FinalizePre none;
             none.valid = false;
+            if (!p.amax_val) {
 #pragma unroll 4
-            for (int c = w; c < ncols; c += 4)
-                finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4), none);
+                for (int c = w; c < ncols; c += kWarps)
+                    finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4), none);
+            } else if (warp < 2) {
+                // Fused greedy pick: thread = token column, a plain scan down the 128 parked rows (a warp
+                // reduction per column would put 64 shuffle chains into every CTA's epilogue). The scan
+                // starts at a row that depends on the column so that the lanes hit different banks; the
+                // lowest index among equal maxima wins whatever the order.
+                for (int c = (int)threadIdx.x; c < ncols; c += 64) {
+                    float best = -INFINITY;
+                    int bi = 0x7fffffff;
+#pragma unroll 8
+                    for (int j = 0; j < BM / 4; ++j) {
+                        const int r = ((j + c) & (BM / 4 - 1)) * 4;
+                        const float4 v = *(const float4*)(plane + (size_t)c * BM + r);
+                        const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const int idx = n0 + r + q4;
+                            if (idx < p.N && (f[q4] > best || (f[q4] == best && idx < bi))) { best = f[q4]; bi = idx; }
+                        }
+                    }
+                    p.amax_val[(size_t)(t0 + c) * gridDim.x + blockIdx.x] = best;
+                    p.amax_idx[(size_t)(t0 + c) * gridDim.x + blockIdx.x] = bi;
+                }
+            } else if (out) {
+#pragma unroll 4
+                for (int c = w - 2; c < ncols; c += kWarps - 2)
+                    finalize_plain(p, out, n, t0 + c, *(const float4*)(plane + (size_t)c * BM + lane * 4), none);
+            }
         }
     } else if (warp >= 2) {
         const int w = warp - 2;
@@ -467,6 +526,7 @@ __global__ void __launch_bounds__(kGemmThreads, (BN <= 64) ? 2 : 1) k_gemm_tc(co
                                                silu_mul_bf16(acc.w, up.w)), f);
             } else {
                 finalize_plain(p, out, n, t, acc, f);
+                publish_amax(p, n, t, acc, lane);
             }
         };
         const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -608,6 +668,9 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     p.status = ws.status;
     p.trace = c.trace;
     p.tl = c.tl;
+    p.amax_val = c.mode == GEMM_STORE_F32 ? c.amax_val : nullptr;
+    p.amax_idx = c.amax_idx;
+    if (!c.out && !(c.mode == GEMM_STORE_F32 && c.amax_val && c.amax_idx) && c.mode != GEMM_QKV) return (int)cudaErrorInvalidValue;
     if (c.mode == GEMM_QKV) {
         if (!c.qkv || c.op[1].K > 0 || c.out2 || (c.qkv->kv.hd != 64 && c.qkv->kv.hd != 128)) return (int)cudaErrorInvalidValue;
         p.qkv = *c.qkv;
@@ -635,7 +698,7 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
         // shared memory a CTA does not claim lets CTAs of the next kernel of the stream become resident
         // early under programmatic dependent launch and fetch their weights ahead of their grid wait.
         const int iters = (total_kb + splits - 1) / splits;
-        const int plane_stages = (BN * BM * 4 + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
+        const int plane_stages = (BN * BM * 4 + BN * 8 /* per-token maxima of the fused pick */ + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
         const int want = iters > plane_stages ? iters : plane_stages;
         if (p.stages > want) p.stages = want;
     }

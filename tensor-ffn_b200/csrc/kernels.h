@@ -59,6 +59,12 @@ struct GemmCall {
     GemmOperand op2[2];
     void* out2;
     const GemmQkvEpilogue* qkv;  // GEMM_QKV only
+    // GEMM_STORE_F32 only, optional: greedy pick fused into the epilogue. Every CTA leaves, per token, the
+    // maximum of its 128 output rows and its index (lowest index among equal maxima) in
+    // amax_val / amax_idx [t * ceil(N / 128) + tile]; launch_argmax_tiles combines them. With it `out` may
+    // be nullptr: the values themselves are then not stored.
+    float* amax_val;
+    int* amax_idx;
     // optional device buffer of 64 u64 per CTA: globaltimer (ns) at 0 start, 1 weight boxes requested,
     // 2 dependency wait over, 3 last MMA issued, 4 accumulator complete, 5 epilogue/park done,
     // 6 cluster barrier passed, 7 reduction done, 8 end, 16+i stage i arrived (i < 40)
@@ -83,6 +89,9 @@ void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, i
                   bool pdl = false, unsigned long long* tl = nullptr);
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
                     bool pdl = false, unsigned long long* tl = nullptr);
+// per-tile maxima left by the GEMM (GemmCall::amax_val / amax_idx, `tiles` per row) -> argmax per row
+void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s,
+                         bool pdl = false, unsigned long long* tl = nullptr);
 // logits fp32 [R, V] -> argmax (lowest index among maxima). scratch (>= 2 * R * 64 floats) and
 // counters (>= R ints, zero, left zero) let several blocks share a row; without them one block per row.
 void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,

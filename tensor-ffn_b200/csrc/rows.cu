@@ -141,6 +141,36 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ l
     if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
+// second half of the greedy pick when the LM-head GEMM left per-tile maxima: one block per row
+__global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ val, const int* __restrict__ idx, int tiles,
+                                                       int* __restrict__ out, unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) tl_mark(tl, 1);
+    const int r = blockIdx.x;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < tiles; i += 256)
+        argmax_take(best, bi, __ldcg(val + (size_t)r * tiles + i), __ldcg(idx + (size_t)r * tiles + i));
+    __shared__ float sv[8];
+    __shared__ int si[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < 8 ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < 8 ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (threadIdx.x == 0) {
+            out[r] = (bi == 0x7fffffff) ? 0 : bi;
+            tl_mark(tl, 2);
+        }
+    }
+}
+
 __global__ void k_cast_f32_bf16(const float* __restrict__ src, bf16* __restrict__ dst, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -188,6 +218,10 @@ void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, 
     if (S > V / 1024) S = V / 1024;
     if (S < 1 || !scratch || !counters || R > num_counters || (size_t)R * S * 2 > scratch_floats) S = 1;
     launch_k(k_argmax_rows, dim3(R, S), dim3(256), 0, s, pdl, logits, V, S, out, scratch, counters, tl);
+}
+void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s, bool pdl,
+                         unsigned long long* tl) {
+    launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl);
 }
 void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s) {
     int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
