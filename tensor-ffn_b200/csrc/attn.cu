@@ -429,17 +429,22 @@ void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView
 
 }  // namespace
 
+constexpr int kMinSplitRows = 1024;
+
 int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms) {
     // One CTA per SM is the target: a CTA holds 128 KB of K/V in flight and its eight warps keep up with
     // what one SM can take in, and a launch without splits needs no merge (a partial write, a ticket and a
-    // second read-back cost about 6 us per launch when measured with three splits). Splits are used only
-    // when there are fewer (token, kv head) units than half the SMs, with at least one stage per split.
+    // second read-back cost 4 to 6 us per launch, measured with two and three splits). Splits are used only
+    // when there are fewer (token, kv head) units than half the SMs and the context is long: a split
+    // must save more key-loop time (about 0.5 us per 128-key stage) than the merge costs, so each split
+    // gets at least 1024 keys (batch 1 at a few hundred keys of context: 0.94 -> 0.82 ms per token
+    // without splits).
     const int G = nh / nkv;
     const int units = T * nkv;
     int splits = 1;
     if (units * 2 <= num_sms) {
         splits = num_sms / units;
-        const int max_splits = (max_ctx + 127) / 128;
+        const int max_splits = (max_ctx + kMinSplitRows - 1) / kMinSplitRows;
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
         while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))

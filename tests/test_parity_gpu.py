@@ -205,3 +205,34 @@ def test_kv_capacity_and_reset(model_dirs):
 def test_bounded_wait_reports_instead_of_hanging():
     import tffn
     assert tffn.op_wait_selftest() == 5
+
+
+def test_long_context_attention_splits(model_dirs):
+    """Contexts beyond 1024 keys make the batch-1 attention split the context over several CTAs and merge
+    the parts: 3 splits (single-pass merge) against the oracle, then 20 splits (generic merge) and the
+    batched tensor-core path (same attention kernel, one token) against the 3-split result."""
+    import synth
+    import tffn
+    import oracle
+    d, ep, cfg = model_dirs["tiny"]
+    V = cfg["vocab_size"]
+    P, steps = 2100, 3
+    toks = synth.prompts(1, P + steps, 77, V)[0]
+    o = oracle.Oracle(d, P + steps + 8, ep, 0.1)
+    o.forward(toks[:P])
+    ref = np.array([o.forward([int(t)])["logits"][0] for t in toks[P:]])
+    m = tffn.qwen_load(d)
+    e = tffn.checkpoint_load(ep, m, 0.1)
+    got = {}
+    for label, max_seq, bs1 in (("3 splits", 2304, True), ("20 splits", 20480, True), ("batched", 2304, False)):
+        s = tffn.Session(m, e, max_batch=1, max_seq=max_seq)
+        s.set_launch_mode(2)
+        s.set_bs1_path(bs1)
+        s.prefill([toks[:P]])
+        got[label] = np.array([s.decode_step([int(t)], want_logits=True)[1][0].copy() for t in toks[P:]])
+        assert s.status() == 0, label
+        assert s.seq_len(0) == P + steps
+        s.free()
+    assert rel_err(got["3 splits"], ref) <= KERNEL_TOL
+    assert rel_err(got["20 splits"], got["3 splits"]) <= KERNEL_TOL
+    assert rel_err(got["batched"], got["3 splits"]) <= KERNEL_TOL
