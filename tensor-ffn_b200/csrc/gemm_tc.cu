@@ -679,10 +679,11 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     const int total_kb = p.kblocks[0] + p.kblocks[1];
     const int tiles = n_tiles * t_tiles * nprob;
     p.t_tiles = t_tiles;
-    // K splits = cluster size (1, 2, 4 or 8). One CTA sustains roughly one 64-deep k-block per
-    // 0.3 us whatever the ring depth (MMA issue, commit and barrier turn-around, measured), about
-    // 55 GB/s of weights, so a weight-streaming launch needs about as many CTAs as there are SMs:
-    // tiles are split along K until the grid fills the SMs, keeping two k-blocks per split.
+    // K splits = cluster size (1, 2, 4, 8 or 16). Inside a decode step one CTA takes in roughly one
+    // stage (a 16 KB weight box and its activation box) per 0.5 us whatever the ring depth, about 50 GB/s
+    // per SM (measured with the phase stamps; all SMs together about 7 TB/s), so a weight-streaming launch
+    // needs about as many CTAs as there are SMs: tiles are split along K until the grid fills the SMs,
+    // keeping two k-blocks per split.
     int splits = 1;
     if (force_splits > 0) {
         splits = force_splits;
