@@ -116,6 +116,15 @@ int tffn_session_set_launch_mode(tffn_session* s, int mode);
  * inside the overlapped (dependent-launch, graph) schedule, which per-kernel events cannot show.
  * 0 restores normal operation. */
 int tffn_session_set_ablation(tffn_session* s, unsigned mask);
+/* Temperature sampling on the device (the reference samples on the host from a 608 KB logits row per
+ * token: sample(), inference/src/main.cpp:52-63). temperature <= 0 restores greedy picks. Otherwise every
+ * pick of tffn_prefill / tffn_decode_step / tffn_decode_run is drawn as sample() draws it (float maximum,
+ * exp((logit - max) / temperature) in float, sums in double, first index whose running sum reaches
+ * r = u * sum), with u from std::uniform_real_distribution<double> over a std::mt19937(seed) that the
+ * session owns (the reference's CLI seeds 42): one draw per sampled token, the sequences of a batched
+ * step in slot order, the steps of tffn_decode_run in step order. Sampled single-sequence steps run on
+ * the batched path. tffn_forward keeps leaving the greedy token. */
+int tffn_session_set_sampling(tffn_session* s, float temperature, uint32_t seed);
 /* Which path single-token steps take: 1 (default) the fused batch-1 kernels when the shape
  * allows, 0 the batched tensor-core path. */
 int tffn_session_set_bs1_path(tffn_session* s, int enable);

@@ -235,6 +235,12 @@ int tffn_session_set_ablation(tffn_session* s, unsigned mask) {
         s->s->set_ablation(mask);
     });
 }
+int tffn_session_set_sampling(tffn_session* s, float temperature, uint32_t seed) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_sampling(temperature, seed);
+    });
+}
 int tffn_session_set_bs1_path(tffn_session* s, int enable) {
     return guard([&] {
         need(s, "NULL session");

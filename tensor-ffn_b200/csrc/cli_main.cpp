@@ -2,7 +2,8 @@
 // C ABI of include/tffn.h. Same flags, defaults, stdout protocol and exit codes; a leading
 // "inference" word is accepted so that `tensor-ffn inference --model ...` from the
 // reference's README works too. Extra flags (not in the reference): --prompt-ids <file> (raw
-// int32 ids instead of --prompt), --ignore-eos, --device <N>.
+// int32 ids instead of --prompt), --ignore-eos, --device <N>, --host-sampling (with --temperature: sample
+// on the host from downloaded logits as the reference does, instead of on the device).
 #include "../../include/tffn.h"
 #include <algorithm>
 #include <cmath>
@@ -163,14 +164,19 @@ int main(int argc, char** argv) {
 
     std::vector<int32_t> h_tokens(prompt_ids.begin(), prompt_ids.end());
     const int V = cfg.vocab_size;
-    std::vector<float> h_logits(temperature > 0.f ? V : 0);
+    // Temperature sampling runs on the device with the reference's arithmetic and its mt19937(42) stream
+    // (tffn_session_set_sampling); --host-sampling keeps the reference's host loop over a downloaded
+    // logits row instead (608 KB per token), for cross-checks.
+    const bool host_sampling = temperature > 0.f && has_switch(argc, argv, "--host-sampling");
+    if (temperature > 0.f && !host_sampling) CHECK(tffn_session_set_sampling(sess, temperature, 42));
+    std::vector<float> h_logits(host_sampling ? V : 0);
     printf("\nGenerating:\n");
     fflush(stdout);
 
     int32_t next = 0;
-    CHECK(tffn_prefill(sess, h_tokens.data(), &prompt_len, 1, &next, temperature > 0.f ? h_logits.data() : nullptr));
+    CHECK(tffn_prefill(sess, h_tokens.data(), &prompt_len, 1, &next, host_sampling ? h_logits.data() : nullptr));
     std::mt19937 rng(42);
-    if (temperature > 0.f) next = sample_temperature(h_logits.data(), V, temperature, rng);
+    if (host_sampling) next = sample_temperature(h_logits.data(), V, temperature, rng);
 
     for (int step = 0; step < max_new_tokens; ++step) {
         if (!ignore_eos && next == (int32_t)eos) break;
@@ -184,8 +190,8 @@ int main(int argc, char** argv) {
         printf("%s", text);
         fflush(stdout);
         int32_t fed = next;
-        CHECK(tffn_decode_step(sess, &fed, 1, &next, temperature > 0.f ? h_logits.data() : nullptr));
-        if (temperature > 0.f) next = sample_temperature(h_logits.data(), V, temperature, rng);
+        CHECK(tffn_decode_step(sess, &fed, 1, &next, host_sampling ? h_logits.data() : nullptr));
+        if (host_sampling) next = sample_temperature(h_logits.data(), V, temperature, rng);
     }
     printf("\n");
 

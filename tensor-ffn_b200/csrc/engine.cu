@@ -283,12 +283,14 @@ Session::~Session() {
     for (cudaEvent_t e : prof_free_) cudaEventDestroy(e);
     if (h_status_) cudaFreeHost(h_status_);
     if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
+    if (h_sample_u_) cudaFreeHost(h_sample_u_);
     if (own_stream_) cudaStreamDestroy(stream_);
 }
 
 int32_t* Session::pinned_i32(size_t n) {
     if (n > h_pinned_cap_) {
         if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
+    if (h_sample_u_) cudaFreeHost(h_sample_u_);
         h_pinned_i32_ = nullptr;
         size_t cap = std::max<size_t>(n, 4096);
         TFFN_CUDA(cudaMallocHost(&h_pinned_i32_, cap * 4));
@@ -373,6 +375,30 @@ void Session::flush_tables() {
     TFFN_CUDA(cudaMemcpyAsync(block_table_.p, pin, h_block_table_.size() * 4, cudaMemcpyHostToDevice, stream_));
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     table_dirty_ = false;
+}
+
+void Session::set_sampling(float temperature, uint32_t seed) {
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    drop_graphs();  // the pick kernel is part of the captured step
+    sample_temp_ = temperature > 0.f ? temperature : 0.f;
+    sample_rng_.seed(seed);
+}
+
+void Session::upload_draws(size_t n) {
+    if (n > h_sample_cap_) {
+        TFFN_CUDA(cudaStreamSynchronize(stream_));
+        if (h_sample_u_) cudaFreeHost(h_sample_u_);
+        h_sample_u_ = nullptr;
+        const size_t cap = std::max<size_t>(n, 1024);
+        TFFN_CUDA(cudaMallocHost(&h_sample_u_, cap * 8));
+        h_sample_cap_ = cap;
+        sample_u_.alloc(cap * 8);
+    } else {
+        TFFN_CUDA(cudaStreamSynchronize(stream_));  // the staging buffer may still feed an earlier copy
+    }
+    std::uniform_real_distribution<double> canonical(0.0, 1.0);  // r = u * sum, as dist(0, sum) computes it
+    for (size_t i = 0; i < n; ++i) h_sample_u_[i] = canonical(sample_rng_);
+    TFFN_CUDA(cudaMemcpyAsync(sample_u_.p, h_sample_u_, n * 8, cudaMemcpyHostToDevice, stream_));
 }
 
 void Session::set_launch_mode(int mode) {
@@ -630,7 +656,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         // idle by now and serves as scratch.
         const AttnWorkspace aw = attn_ws();
         const int v_tiles = (V + 127) / 128;
-        const bool fused_pick = (size_t)n_logit_rows * v_tiles * 2 <= aw.partial_floats;
+        const bool fused_pick = !sampling() && (size_t)n_logit_rows * v_tiles * 2 <= aw.partial_floats;
         if (fused_pick) {
             g.amax_val = aw.partials;
             g.amax_idx = (int*)(aw.partials + (size_t)n_logit_rows * v_tiles);
@@ -641,6 +667,9 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         if (live(KC_ARGMAX)) {
             if (fused_pick)
                 launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX));
+            else if (sampling())
+                launch_sample(logits_.as<float>(), n_logit_rows, V, sample_temp_, sample_u_.as<double>(),
+                              decode ? step_counter_.as<int>() : nullptr, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX));
             else
                 launch_argmax(logits_.as<float>(), n_logit_rows, V, picks_.as<int>(), aw.partials, aw.partial_floats, aw.counters,
                               aw.num_counters, m_->num_sms, stream_, pdl, tl_next(KC_ARGMAX));
@@ -922,7 +951,8 @@ void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs
         TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * T, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
         if (!last_rows.empty())
             TFFN_CUDA(cudaMemcpyAsync(row_idx_.p, pin + 3 * T, last_rows.size() * 4, cudaMemcpyHostToDevice, stream_));
-        store_logits_ = logits_last != nullptr;
+        store_logits_ = logits_last != nullptr || sampling();
+        if (sampling() && !last_rows.empty()) upload_draws(last_rows.size());  // one draw per sequence, slot order
         run_batched(T, (int)last_rows.size(), false, false, max_ctx);
         if (!last_rows.empty()) {
             std::vector<int> picks(last_rows.size());
@@ -958,6 +988,13 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
     flush_tables();
     const int chunk_cap = std::min(cap_tokens_, 512);  // bounds the all-row logits buffer
     if (logits) ensure_logits(std::min(T, chunk_cap));
+    // qwen_forward returns logits; the token it leaves for a following decode step is the greedy one
+    struct GreedyScope {
+        float& t;
+        float saved;
+        explicit GreedyScope(float& x) : t(x), saved(x) { t = 0.f; }
+        ~GreedyScope() { t = saved; }
+    } greedy_scope(sample_temp_);
     int last_pick = 0;
     for (int c0 = 0; c0 < T; c0 += chunk_cap) {
         const int n = std::min(chunk_cap, T - c0);
@@ -1008,13 +1045,14 @@ void Session::decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_to
     TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
     ensure_ring(n_seqs);
     if (logits) ensure_logits(std::max<size_t>(256, n_seqs));
-    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok;
+    if (sampling()) upload_draws((size_t)n_seqs);
+    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok && !sampling();  // the fused batch-1 LM head picks greedily
     if (bs1) {
         run_bs1(logits != nullptr);
     } else {
         int max_ctx = 1;
         for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + 1);
-        store_logits_ = logits != nullptr;
+        store_logits_ = logits != nullptr || sampling();
         run_decode_batched(n_seqs, max_ctx);
     }
     TFFN_CUDA(cudaMemcpyAsync(pin, dec_tokens_.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, stream_));
@@ -1033,14 +1071,15 @@ void Session::decode_run(int n_seqs, int steps, int32_t* tokens_out) {
     flush_tables();
     ensure_ring(n_seqs * steps);
     TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
-    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok;
+    if (sampling()) upload_draws((size_t)n_seqs * steps);  // step-major, slot order within a step
+    const bool bs1 = n_seqs == 1 && use_bs1_ && m_->bs1_ok && !sampling();
     int max_ctx = 1;
     for (int s = 0; s < n_seqs; ++s) max_ctx = std::max(max_ctx, h_seq_len_[s] + steps);
     for (int it = 0; it < steps; ++it) {
         if (bs1) {
             run_bs1(false);
         } else {
-            store_logits_ = false;  // a device-resident loop hands out tokens only
+            store_logits_ = sampling();  // a device-resident loop hands out tokens only; sampling reads the logits
             run_decode_batched(n_seqs, max_ctx);
         }
     }

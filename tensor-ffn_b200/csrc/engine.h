@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <map>
 #include <string>
+#include <random>
 #include <vector>
 
 namespace tffn {
@@ -95,6 +96,9 @@ public:
     // timing-only: kernel classes (bit = KClass) that the batched path does not launch
     void set_ablation(unsigned mask);
     void set_bs1_path(bool on) { use_bs1_ = on; }
+    // temperature <= 0: greedy. Otherwise every pick is sampled on the device as sample() of the
+    // reference does on the host, with draws from a std::mt19937(seed) owned by the session.
+    void set_sampling(float temperature, uint32_t seed);
     void capture_hidden(int max_rows);
     int get_hidden(int layer, uint16_t* dst, int max_rows);
     int status();
@@ -111,6 +115,13 @@ private:
     bool own_stream_ = false;
     int launch_mode_ = 1;
     unsigned ablate_mask_ = 0;
+    float sample_temp_ = 0.f;
+    std::mt19937 sample_rng_{42};
+    DeviceBuffer sample_u_;
+    double* h_sample_u_ = nullptr;  // pinned staging
+    size_t h_sample_cap_ = 0;
+    void upload_draws(size_t n);  // n canonical draws -> sample_u_[0..n)
+    bool sampling() const { return sample_temp_ > 0.f; }
     bool store_logits_ = true;  // whether the LM head writes its fp32 logits (the greedy pick does not need them)
     bool tl_on_ = false;
     DeviceBuffer tl_buf_;

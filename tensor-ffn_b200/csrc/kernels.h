@@ -89,6 +89,10 @@ void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, i
                   bool pdl = false, unsigned long long* tl = nullptr);
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
                     bool pdl = false, unsigned long long* tl = nullptr);
+// temperature sampling (inference/src/main.cpp:52-63) of R rows of fp32 logits on the device;
+// u[step * R + row] = canonical uniform draws in [0, 1), step = *step_counter (0 if nullptr)
+void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
+                   cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
 // per-tile maxima left by the GEMM (GemmCall::amax_val / amax_idx, `tiles` per row) -> argmax per row
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s,
                          bool pdl = false, unsigned long long* tl = nullptr);

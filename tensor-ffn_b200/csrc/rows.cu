@@ -171,6 +171,85 @@ __global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ 
     }
 }
 
+// Temperature sampling on the device, the arithmetic of sample() (inference/src/main.cpp:52-63): float
+// maximum, p_i = exp((logit_i - max) / temperature) evaluated in float and summed in double, r = u * sum
+// with u the canonical draw of std::uniform_real_distribution<double> (made on the host with the
+// reference's std::mt19937), pick = first i whose running sum reaches r (V - 1 if none does). The running
+// sum is formed per 32-element group and per warp segment instead of strictly left to right, which moves
+// it by rounding errors of the order 1e-16 of the total. One block per row; u[step * rows + row].
+__global__ void __launch_bounds__(1024) k_sample_rows(const float* __restrict__ logits, int V, float temperature,
+                                                       const double* __restrict__ u, const int* __restrict__ step_counter,
+                                                       int* __restrict__ out, unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) tl_mark(tl, 1);
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float* row = logits + (size_t)r * V;
+    const int st = step_counter ? __ldcg(step_counter) : 0;
+    const double uu = __ldcg(u + (size_t)st * gridDim.x + r);
+    __shared__ float s_mx[32];
+    __shared__ double s_seg[32];
+    __shared__ int s_warp;
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += 1024) mx = fmaxf(mx, __ldcg(row + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_mx[warp] = mx;
+    __syncthreads();
+    mx = s_mx[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // warp w owns the contiguous segment [w * S, (w + 1) * S), lanes interleaved inside it (coalesced)
+    const int S = ((V + 31) / 32 + 31) / 32 * 32;
+    const int b0 = warp * S, b1 = min(V, b0 + S);
+    auto prob = [&](int i) { return i < b1 ? (double)expf((__ldcg(row + i) - mx) / temperature) : 0.0; };
+    double seg = 0.0;
+    for (int i = b0 + lane; i < b1; i += 32) seg += prob(i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) seg += __shfl_xor_sync(0xffffffffu, seg, o);
+    if (lane == 0) s_seg[warp] = seg;
+    if (tid == 0) s_warp = 32;
+    __syncthreads();
+    // inclusive scan of the 32 segment sums (every warp does it; cheap), total, threshold
+    double incl = s_seg[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    const double total = __shfl_sync(0xffffffffu, incl, 31);
+    const double rr = uu * total;
+    if (warp == 0) {
+        const unsigned hit = __ballot_sync(0xffffffffu, incl >= rr);
+        if (lane == 0) s_warp = hit ? __ffs(hit) - 1 : 32;
+    }
+    __syncthreads();
+    const int w_hit = s_warp;
+    if (w_hit == 32) {
+        if (tid == 0) out[r] = V - 1;
+    } else if (warp == w_hit) {
+        double acc = __shfl_sync(0xffffffffu, incl, w_hit) - s_seg[w_hit];  // running sum before this segment
+        int pick = b1 - 1;  // rounding may keep the rescan just below r: then the segment's last element
+        for (int i0 = b0; i0 < b1; i0 += 32) {
+            double v = prob(i0 + lane);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, acc + v >= rr && i0 + lane < b1);
+            if (hit) {
+                pick = i0 + __ffs(hit) - 1;
+                break;
+            }
+            acc += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) out[r] = pick;
+    }
+    if (tid == 0) tl_mark(tl, 2);
+}
+
 __global__ void k_cast_f32_bf16(const float* __restrict__ src, bf16* __restrict__ dst, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -222,6 +301,10 @@ void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, 
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s, bool pdl,
                          unsigned long long* tl) {
     launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl);
+}
+void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
+                   cudaStream_t s, bool pdl, unsigned long long* tl) {
+    launch_k(k_sample_rows, dim3(R), dim3(1024), 0, s, pdl, logits, V, temperature, u, step_counter, out, tl);
 }
 void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s) {
     int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);

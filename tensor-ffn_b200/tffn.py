@@ -74,6 +74,7 @@ _SIGS = {
     "tffn_session_seq_len": (_i, [_vp, _i]),
     "tffn_session_set_launch_mode": (_i, [_vp, _i]),
     "tffn_session_set_ablation": (_i, [_vp, ctypes.c_uint]),
+    "tffn_session_set_sampling": (_i, [_vp, _f, ctypes.c_uint32]),
     "tffn_session_set_bs1_path": (_i, [_vp, _i]),
     "tffn_session_capture_hidden": (_i, [_vp, _i]),
     "tffn_session_get_hidden": (_i, [_vp, _i, _vp, _i]),
@@ -276,6 +277,10 @@ class Session:
     def set_ablation(self, mask: int):
         """timing aid: skip the kernel classes whose bit is set (results become meaningless)"""
         _check(_L.tffn_session_set_ablation(self._h, mask))
+
+    def set_sampling(self, temperature: float, seed: int = 42):
+        """temperature sampling on the device as sample() (inference/src/main.cpp:52-63); <= 0: greedy"""
+        _check(_L.tffn_session_set_sampling(self._h, float(temperature), int(seed)))
 
     def set_bs1_path(self, on: bool):
         _check(_L.tffn_session_set_bs1_path(self._h, int(on)))
