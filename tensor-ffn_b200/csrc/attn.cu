@@ -76,6 +76,72 @@ struct AttnCfg {
     static_assert(NST >= 2 && KB >= 1, "");
 };
 
+// One block of 16 cached keys (rows row0 .. row0+15 of a stage buffer, the first n_valid >= 1 of them
+// inside the context) for the query-head group held in qh / ql: S = Q K^T, online softmax of head
+// lane / 4 (this thread: keys nt * 8 + (lane % 4) * 2 + {0, 1}), O += P V. The whole warp calls it.
+template <int HD>
+__device__ __forceinline__ void attn_block16(uint32_t kbuf, uint32_t vbuf, int row0, int n_valid,
+                                             const uint32_t (&qh)[HD / 16][2], const uint32_t (&ql)[HD / 16][2], float scale,
+                                             float& m_run, float& l_run, float (&o)[HD / 8][4], int lane) {
+    using C = AttnCfg<HD>;
+    const int quad = lane & 3;
+    // ---- S = Q K^T for WARP_ROWS keys: NT tiles of 8 keys
+    float s[C::NT][4];
+#pragma unroll
+    for (int nt = 0; nt < C::NT; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const int row = row0 + nt * 8 + (lane & 7);  // this lane's address row for ldmatrix
+#pragma unroll
+        for (int kp = 0; kp < C::KS / 2; ++kp) {
+            uint32_t b[4];  // B fragments of k-steps 2kp and 2kp + 1 (matrix i = granule 4kp + i)
+            const int g = kp * 4 + (lane >> 3);
+            ldmatrix_x4(kbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
+            mma_16816(s[nt], qh[2 * kp][0], ql[2 * kp][0], qh[2 * kp][1], ql[2 * kp][1], b[0], b[1]);
+            mma_16816(s[nt], qh[2 * kp + 1][0], ql[2 * kp + 1][0], qh[2 * kp + 1][1], ql[2 * kp + 1][1], b[2], b[3]);
+        }
+    }
+    // ---- online softmax of head hrow over these keys (this thread: keys nt * 8 + quad * 2 + {0, 1})
+    float mx = kNegBig;
+#pragma unroll
+    for (int nt = 0; nt < C::NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const bool live = nt * 8 + quad * 2 + j < n_valid;
+            s[nt][j] = live ? (s[nt][j] + s[nt][j + 2]) * scale : kNegBig;  // q_hi . k + q_lo . k
+            mx = fmaxf(mx, s[nt][j]);
+        }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m_run, mx);  // finite: the first key of the block is in range
+    const float corr = __expf(m_run - mn);
+    m_run = mn;
+    l_run *= corr;
+#pragma unroll
+    for (int d = 0; d < C::DT; ++d) { o[d][0] *= corr; o[d][1] *= corr; o[d][2] *= corr; o[d][3] *= corr; }
+    uint32_t ph[C::NT], pl[C::NT];
+#pragma unroll
+    for (int nt = 0; nt < C::NT; ++nt) {
+        const float p0 = (nt * 8 + quad * 2 < n_valid) ? __expf(s[nt][0] - mn) : 0.f;
+        const float p1 = (nt * 8 + quad * 2 + 1 < n_valid) ? __expf(s[nt][1] - mn) : 0.f;
+        l_run += p0 + p1;
+        split_bf16x2(p0, p1, ph[nt], pl[nt]);
+    }
+    // ---- O += P V: per 16 keys, per pair of 8-wide output tiles one transposed ldmatrix of V
+#pragma unroll
+    for (int kb = 0; kb < C::KB; ++kb) {
+        const int row = row0 + kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int jp = 0; jp < C::DT / 2; ++jp) {
+            uint32_t b[4];  // keys 0-7 / 8-15 of tile 2jp, then of tile 2jp + 1
+            const int g = jp * 2 + (lane >> 4);
+            ldmatrix_x4_trans(vbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
+            mma_16816(o[2 * jp], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[0], b[1]);
+            mma_16816(o[2 * jp + 1], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[2], b[3]);
+        }
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kAttnCtaThreads) k_attn_decode(const float* __restrict__ q, KvView kv, int layer,
                                                               const int* __restrict__ tok_seq,
@@ -234,61 +300,7 @@ __global__ void __launch_bounds__(kAttnCtaThreads) k_attn_decode(const float* __
         if (w_begin < c_end) {
             const uint32_t kbuf = smem_base + (uint32_t)((st % C::NST) * C::STAGE_BYTES);
             const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
-            // ---- S = Q K^T for WARP_ROWS keys: NT tiles of 8 keys
-            float s[C::NT][4];
-#pragma unroll
-            for (int nt = 0; nt < C::NT; ++nt) {
-                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-                const int row = warp * C::WARP_ROWS + nt * 8 + (lane & 7);  // this lane's address row for ldmatrix
-#pragma unroll
-                for (int kp = 0; kp < C::KS / 2; ++kp) {
-                    uint32_t b[4];  // B fragments of k-steps 2kp and 2kp + 1 (matrix i = granule 4kp + i)
-                    const int g = kp * 4 + (lane >> 3);
-                    ldmatrix_x4(kbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
-                    mma_16816(s[nt], qh[2 * kp][0], ql[2 * kp][0], qh[2 * kp][1], ql[2 * kp][1], b[0], b[1]);
-                    mma_16816(s[nt], qh[2 * kp + 1][0], ql[2 * kp + 1][0], qh[2 * kp + 1][1], ql[2 * kp + 1][1], b[2], b[3]);
-                }
-            }
-            // ---- online softmax of head hrow over these keys (this thread: keys nt * 8 + quad * 2 + {0, 1})
-            float mx = kNegBig;
-#pragma unroll
-            for (int nt = 0; nt < C::NT; ++nt) {
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const bool live = w_begin + nt * 8 + quad * 2 + j < c_end;
-                    s[nt][j] = live ? (s[nt][j] + s[nt][j + 2]) * scale : kNegBig;  // q_hi . k + q_lo . k
-                    mx = fmaxf(mx, s[nt][j]);
-                }
-            }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float mn = fmaxf(m_run, mx);  // finite: the first key of the warp's rows is in range
-            const float corr = __expf(m_run - mn);
-            m_run = mn;
-            l_run *= corr;
-#pragma unroll
-            for (int d = 0; d < C::DT; ++d) { o[d][0] *= corr; o[d][1] *= corr; o[d][2] *= corr; o[d][3] *= corr; }
-            uint32_t ph[C::NT], pl[C::NT];
-#pragma unroll
-            for (int nt = 0; nt < C::NT; ++nt) {
-                const float p0 = (w_begin + nt * 8 + quad * 2 < c_end) ? __expf(s[nt][0] - mn) : 0.f;
-                const float p1 = (w_begin + nt * 8 + quad * 2 + 1 < c_end) ? __expf(s[nt][1] - mn) : 0.f;
-                l_run += p0 + p1;
-                split_bf16x2(p0, p1, ph[nt], pl[nt]);
-            }
-            // ---- O += P V: per 16 keys, per pair of 8-wide output tiles one transposed ldmatrix of V
-#pragma unroll
-            for (int kb = 0; kb < C::KB; ++kb) {
-                const int row = warp * C::WARP_ROWS + kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-#pragma unroll
-                for (int jp = 0; jp < C::DT / 2; ++jp) {
-                    uint32_t b[4];  // keys 0-7 / 8-15 of tile 2jp, then of tile 2jp + 1
-                    const int g = jp * 2 + (lane >> 4);
-                    ldmatrix_x4_trans(vbuf + (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4)), b);
-                    mma_16816(o[2 * jp], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[0], b[1]);
-                    mma_16816(o[2 * jp + 1], ph[2 * kb], pl[2 * kb], ph[2 * kb + 1], pl[2 * kb + 1], b[2], b[3]);
-                }
-            }
+            attn_block16<HD>(kbuf, vbuf, warp * C::WARP_ROWS, c_end - w_begin, qh, ql, scale, m_run, l_run, o, lane);
         }
         __syncwarp();  // every lane is done with the warp's rows of this buffer
         issue_stage(st + C::NST);  // commits a group even when there is nothing left to copy
@@ -414,6 +426,122 @@ __global__ void __launch_bounds__(kAttnCtaThreads) k_attn_decode(const float* __
 #undef ATTN_TRACE
 }
 
+// Prefill: one CTA per (group of up to 8 consecutive prompt tokens of ONE sequence, kv head). The eight
+// warps are the eight query tokens; the K/V stages (128 keys each, copied by all threads) are shared by
+// them, so the cache is read once per 8 tokens instead of once per token; warp w runs the same 16-key
+// blocks as the decode kernel over keys 0 .. pos_w (causal), owns its token's whole context and writes
+// its output rows itself: no merge.
+template <int HD>
+__global__ void __launch_bounds__(kAttnCtaThreads) k_attn_prefill(const float* __restrict__ q, KvView kv, int layer,
+                                                               const int* __restrict__ tok_seq,
+                                                               const int* __restrict__ tok_pos,
+                                                               const int* __restrict__ grp_first,
+                                                               const int* __restrict__ grp_count, bf16* __restrict__ ctx,
+                                                               int nh, int G, int* status, unsigned long long* tl) {
+    using C = AttnCfg<HD>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    if (threadIdx.x == 0) tl_mark(tl, 0);
+    pdl_launch_dependents();
+    pdl_wait();  // the previous kernel wrote q and the K/V rows of these very tokens
+    if (threadIdx.x == 0) tl_mark(tl, 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y, nkv = kv.nkv;
+    const int first = __ldcg(grp_first + blockIdx.x), count = __ldcg(grp_count + blockIdx.x);
+    const int seq = __ldcg(tok_seq + first);
+    const int last_len = __ldcg(tok_pos + first + count - 1) + 1;  // positions ascend within a group
+    const bool active = warp < count;
+    const int t = first + (active ? warp : 0);
+    const int my_len = active ? __ldcg(tok_pos + t) + 1 : 0;
+    const int* bt = kv.block_table + (size_t)seq * kv.max_pages_per_seq;
+    const bf16* kpool = kv.k_pool + (size_t)layer * kv.layer_stride;
+    const bf16* vpool = kv.v_pool + (size_t)layer * kv.layer_stride;
+    const uint32_t smem_base = smem_u32(smem);
+    bool bad = false;
+
+    auto issue_stage = [&](int st) {  // all 256 threads
+        const int s_begin = st * C::STAGE_ROWS;
+        if (s_begin < last_len) {
+            constexpr int PPS = C::STAGE_ROWS / kPageTokens;
+            int pgs[PPS];
+#pragma unroll
+            for (int j = 0; j < PPS; ++j) {
+                const int tok0 = s_begin + j * kPageTokens;
+                const int pg = tok0 < last_len ? __ldg(bt + tok0 / kPageTokens) : -1;
+                if (tok0 < last_len && (pg < 0 || pg >= kv.num_pages)) bad = true;
+                pgs[j] = (pg >= 0 && pg < kv.num_pages) ? pg : -1;
+            }
+            const uint32_t kbuf = smem_base + (uint32_t)((st % C::NST) * C::STAGE_BYTES);
+            const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+            constexpr int ROWS_PER_IT = kAttnCtaThreads / C::GRAN;
+            const int row0 = tid / C::GRAN, g = tid % C::GRAN;
+#pragma unroll
+            for (int i = 0; i < C::STAGE_ROWS / ROWS_PER_IT; ++i) {
+                const int row = i * ROWS_PER_IT + row0;
+                const int pg = pgs[(i * ROWS_PER_IT) / kPageTokens];
+                const bool valid = s_begin + row < last_len && pg >= 0;
+                const size_t off = (((size_t)(valid ? pg : 0) * nkv + kvh) * kPageTokens + row % kPageTokens) * HD + g * 8;
+                const uint32_t dst = (uint32_t)(row * C::ROW_BYTES + ((g ^ (row & 7)) << 4));
+                cp_async16_zfill(kbuf + dst, kpool + off, valid ? 16u : 0u);
+                cp_async16_zfill(vbuf + dst, vpool + off, valid ? 16u : 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    const int n_stages = (last_len + C::STAGE_ROWS - 1) / C::STAGE_ROWS;
+#pragma unroll
+    for (int st = 0; st < C::NST; ++st) issue_stage(st);
+
+    const int hrow = lane >> 2, quad = lane & 3;
+    uint32_t qh[C::KS][2], ql[C::KS][2];
+    {
+        const float* qp = q + (size_t)t * nh * HD + (size_t)(kvh * G + hrow) * HD + quad * 2;
+#pragma unroll
+        for (int ks = 0; ks < C::KS; ++ks) {
+            float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+            if (active && hrow < G) {
+                a = __ldcg((const float2*)(qp + ks * 16));
+                b = __ldcg((const float2*)(qp + ks * 16 + 8));
+            }
+            split_bf16x2(a.x, a.y, qh[ks][0], ql[ks][0]);
+            split_bf16x2(b.x, b.y, qh[ks][1], ql[ks][1]);
+        }
+    }
+    const float scale = rsqrtf((float)HD);
+    float m_run = kNegBig, l_run = 0.f;
+    float o[C::DT][4];
+#pragma unroll
+    for (int d = 0; d < C::DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    for (int st = 0; st < n_stages; ++st) {
+        cp_async_wait<C::NST - 1>();
+        __syncthreads();  // the stage is complete and visible to every warp
+        const uint32_t kbuf = smem_base + (uint32_t)((st % C::NST) * C::STAGE_BYTES);
+        const uint32_t vbuf = kbuf + (uint32_t)(C::STAGE_ROWS * C::ROW_BYTES);
+#pragma unroll 1
+        for (int blk = 0; blk < C::STAGE_ROWS / 16; ++blk) {
+            const int k0 = st * C::STAGE_ROWS + blk * 16;
+            if (k0 >= my_len) break;  // warp-uniform: causal end of this token
+            attn_block16<HD>(kbuf, vbuf, blk * 16, my_len - k0, qh, ql, scale, m_run, l_run, o, lane);
+        }
+        __syncthreads();  // every warp is done with this buffer
+        issue_stage(st + C::NST);
+    }
+    cp_async_wait<0>();
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (active && hrow < G) {
+        const float inv = 1.f / l_run;  // my_len >= 1: at least one key
+        bf16* dst = ctx + (size_t)t * nh * HD + (size_t)(kvh * G + hrow) * HD + quad * 2;
+#pragma unroll
+        for (int d = 0; d < C::DT; ++d) {
+            const float a = (o[d][0] + o[d][2]) * inv, b = (o[d][1] + o[d][3]) * inv;  // P_hi V + P_lo V
+            *(uint32_t*)(dst + d * 8) = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
+        }
+    }
+    if (bad) dev_fail(status, DEV_ERR_BOUNDS);
+    if (tid == 0) tl_mark(tl, 2);
+}
+
 template <int HD>
 void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                const int* tok_pos, bf16* ctx, int nh, int G, int splits, int early, float* ws, int* counters, int* status,
@@ -425,6 +553,19 @@ void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView
     }
     launch_k(k_attn_decode<HD>, grid, dim3(kAttnCtaThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
              nh, G, splits, early, ws, counters, status, tl, trace);
+}
+
+template <int HD>
+void launch_prefill_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
+                       const int* tok_pos, const int* grp_first, const int* grp_count, bf16* ctx, int nh, int G, int* status,
+                       unsigned long long* tl) {
+    static bool configured = false;  // benign race: the call is idempotent
+    if (!configured) {
+        cudaFuncSetAttribute(k_attn_prefill<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
+        configured = true;
+    }
+    launch_k(k_attn_prefill<HD>, grid, dim3(kAttnCtaThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos,
+             grp_first, grp_count, ctx, nh, G, status, tl);
 }
 
 }  // namespace
@@ -464,6 +605,15 @@ void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, 
     if ((long long)units * splits > trace_ctas) trace = nullptr;
     if (kv.hd == 64) launch_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl, trace);
     else if (kv.hd == 128) launch_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx, nh, G, splits, early, ws.partials, ws.counters, status, tl, trace);
+}
+
+void launch_attention_prefill(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, const int* grp_first,
+                              const int* grp_count, int n_groups, bf16* ctx, int nh, int* status, cudaStream_t s, bool pdl,
+                              unsigned long long* tl) {
+    const int G = nh / kv.nkv;
+    dim3 grid(n_groups, kv.nkv);
+    if (kv.hd == 64) launch_prefill_hd<64>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, grp_first, grp_count, ctx, nh, G, status, tl);
+    else if (kv.hd == 128) launch_prefill_hd<128>(grid, s, pdl, q, kv, layer, tok_seq, tok_pos, grp_first, grp_count, ctx, nh, G, status, tl);
 }
 
 }  // namespace tffn

@@ -219,6 +219,8 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     tok_seq_.alloc(T * 4);
     tok_pos_.alloc(T * 4);
     row_idx_.alloc(T * 4);
+    grp_first_.alloc(T * 4);
+    grp_count_.alloc(T * 4);
     picks_.alloc(T * 4);
     dec_tokens_.alloc((size_t)max_batch * 4);
     {
@@ -508,7 +510,22 @@ int Session::read_profile(float* ms, int* counts, int cap) {
 }
 
 // ---------------------------------------------------------------- batched path (tensor-core GEMMs)
-void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx) {
+int Session::build_groups(const int* seq, const int* pos, int T, int32_t* first, int32_t* count) {
+    int n = 0;
+    for (int i = 0; i < T; ++i) {
+        const bool extend = n > 0 && count[n - 1] < 8 && seq[i] == seq[i - 1] && pos[i] == pos[i - 1] + 1;
+        if (extend) {
+            ++count[n - 1];
+        } else {
+            first[n] = i;
+            count[n] = 1;
+            ++n;
+        }
+    }
+    return n;
+}
+
+void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx, int n_groups) {
     const Config& c = m_->cfg;
     const int H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
     const int nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
@@ -573,7 +590,11 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         gemm(g, KC_GEMM_QKV);
         g.qkv = nullptr;
         prof_begin(KC_ATTENTION);
-        if (live(KC_ATTENTION)) {
+        if (live(KC_ATTENTION) && n_groups > 0) {
+            // prompt rows: eight consecutive tokens of a sequence share one pass over its cache
+            launch_attention_prefill(q_.as<float>(), kv_, l, tok_seq, tok_pos, grp_first_.as<int>(), grp_count_.as<int>(), n_groups,
+                                     ctx_.as<bf16>(), nh, status, stream_, pdl, tl_next(KC_ATTENTION));
+        } else if (live(KC_ATTENTION)) {
             unsigned long long* tl = tl_next(KC_ATTENTION);
             const bool traced = tl_on_ && (int)tl_cls_.size() - 1 == tl_trace_launch_;
             launch_attention(q_.as<float>(), kv_, l, tok_seq, tok_pos, ctx_.as<bf16>(), T, nh, max_ctx, attn_ws(), m_->num_sms,
@@ -932,7 +953,7 @@ void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs
     }
     for (size_t c0 = 0; c0 < total; c0 += cap_tokens_) {
         const int T = (int)std::min<size_t>(cap_tokens_, total - c0);
-        int32_t* pin = pinned_i32((size_t)T * 4);
+        int32_t* pin = pinned_i32((size_t)T * 6);
         std::vector<int> last_rows, last_slots;
         int max_ctx = 1;
         for (int i = 0; i < T; ++i) {
@@ -951,9 +972,12 @@ void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs
         TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * T, (size_t)T * 4, cudaMemcpyHostToDevice, stream_));
         if (!last_rows.empty())
             TFFN_CUDA(cudaMemcpyAsync(row_idx_.p, pin + 3 * T, last_rows.size() * 4, cudaMemcpyHostToDevice, stream_));
+        const int n_groups = build_groups(pin + T, pin + 2 * T, T, pin + 4 * T, pin + 5 * T);
+        TFFN_CUDA(cudaMemcpyAsync(grp_first_.p, pin + 4 * T, (size_t)n_groups * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(grp_count_.p, pin + 5 * T, (size_t)n_groups * 4, cudaMemcpyHostToDevice, stream_));
         store_logits_ = logits_last != nullptr || sampling();
         if (sampling() && !last_rows.empty()) upload_draws(last_rows.size());  // one draw per sequence, slot order
-        run_batched(T, (int)last_rows.size(), false, false, max_ctx);
+        run_batched(T, (int)last_rows.size(), false, false, max_ctx, n_groups);
         if (!last_rows.empty()) {
             std::vector<int> picks(last_rows.size());
             TFFN_CUDA(cudaMemcpyAsync(picks.data(), picks_.p, picks.size() * 4, cudaMemcpyDeviceToHost, stream_));
@@ -998,24 +1022,27 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
     int last_pick = 0;
     for (int c0 = 0; c0 < T; c0 += chunk_cap) {
         const int n = std::min(chunk_cap, T - c0);
-        int32_t* pin = pinned_i32((size_t)n * 3);
+        int32_t* pin = pinned_i32((size_t)n * 5);
         for (int i = 0; i < n; ++i) {
             pin[i] = tokens[c0 + i];
             pin[n + i] = slot;
             pin[2 * n + i] = h_seq_len_[slot] + c0 + i;
         }
+        const int n_groups = build_groups(pin + n, pin + 2 * n, n, pin + 3 * n, pin + 4 * n);
+        TFFN_CUDA(cudaMemcpyAsync(grp_first_.p, pin + 3 * n, (size_t)n_groups * 4, cudaMemcpyHostToDevice, stream_));
+        TFFN_CUDA(cudaMemcpyAsync(grp_count_.p, pin + 4 * n, (size_t)n_groups * 4, cudaMemcpyHostToDevice, stream_));
         TFFN_CUDA(cudaMemcpyAsync(tokens_.p, pin, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
         TFFN_CUDA(cudaMemcpyAsync(tok_seq_.p, pin + n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
         TFFN_CUDA(cudaMemcpyAsync(tok_pos_.p, pin + 2 * n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
         store_logits_ = logits != nullptr;
         if (logits) {
-            run_batched(n, n, true, false, h_seq_len_[slot] + c0 + n);
+            run_batched(n, n, true, false, h_seq_len_[slot] + c0 + n, n_groups);
             TFFN_CUDA(cudaMemcpyAsync(logits + (size_t)c0 * V, logits_.p, (size_t)n * V * 4, cudaMemcpyDeviceToHost, stream_));
             TFFN_CUDA(cudaMemcpyAsync(pin, picks_.as<int>() + (n - 1), 4, cudaMemcpyDeviceToHost, stream_));
             TFFN_CUDA(cudaStreamSynchronize(stream_));
             last_pick = pin[0];
         } else {
-            run_batched(n, 0, true, false, h_seq_len_[slot] + c0 + n);
+            run_batched(n, 0, true, false, h_seq_len_[slot] + c0 + n, n_groups);
             TFFN_CUDA(cudaStreamSynchronize(stream_));
         }
     }

@@ -144,6 +144,7 @@ private:
 
     // token metadata and activations of the batched path
     DeviceBuffer tokens_, tok_seq_, tok_pos_, row_idx_, picks_, identity_, dec_tokens_;
+    DeviceBuffer grp_first_, grp_count_;  // prefill attention: groups of up to 8 consecutive rows of one sequence
     DeviceBuffer h_, xn_, q_, ctx_, act_b_, act_e_, xn_last_, logits_;
     size_t logits_rows_ = 0;
     DeviceBuffer attn_partials_, attn_counters_;
@@ -187,7 +188,9 @@ private:
     void ensure_logits(size_t rows);
     void ensure_ring(int entries);
     // runs T tokens already staged in tokens_/tok_seq_/tok_pos_ (or decode state when decode=true)
-    void run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx);
+    void run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx, int n_groups = 0);
+    // groups for launch_attention_prefill from the rows' (slot, position) lists; fills pin[0..2*n) and returns n
+    static int build_groups(const int* seq, const int* pos, int T, int32_t* first, int32_t* count);
     void run_bs1(bool want_logits);
     void launch_bs1_step(bool want_logits, bool pdl);
     Bs1Ctx bs1_ctx(bool want_logits) const;

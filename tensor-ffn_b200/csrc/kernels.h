@@ -119,6 +119,12 @@ void launch_attention(const float* q, KvView kv, int layer, const int* tok_seq, 
                       bool only_newest_row_fresh = false, unsigned long long* tl = nullptr,
                       unsigned long long* trace = nullptr, int trace_ctas = 0);  // trace: 16 u64 per CTA, see attn.cu
 
+// Prompt tokens: rows grp_first[g] .. grp_first[g] + grp_count[g] - 1 (at most 8, consecutive positions of
+// one sequence) share one pass over that sequence's cache; n_groups groups cover the T rows of the call.
+void launch_attention_prefill(const float* q, KvView kv, int layer, const int* tok_seq, const int* tok_pos, const int* grp_first,
+                              const int* grp_count, int n_groups, bf16* ctx, int nh, int* status, cudaStream_t s,
+                              bool pdl = false, unsigned long long* tl = nullptr);
+
 // ------------------------------------------------------------------ batch-1 fused decode kernels
 struct Bs1Layer {
     const bf16 *wqkv, *bqkv;  // [(nh+2nkv)*hd, H] rows q|k|v ; bias or null
