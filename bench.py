@@ -451,6 +451,42 @@ def run_kernel_case(a):
     print(json.dumps(out))
 
 
+def run_expert_forward_case(a):
+    """tffn_expert_forward (the trainer's expert_forward on the inference kernels) on a training-shaped
+    batch of the bench model: 4096 tokens per layer, all layers; prints dense bf16 TFLOP/s against the
+    measured GEMM peak (a tensor-bound case, unlike the decode path)."""
+    import torch
+    import synth
+    import tffn
+    d, ep, cfg = ensure_model(a.shape)
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    T = 4096
+    model = tffn.qwen_load(d, device=0)
+    expert = tffn.checkpoint_load(ep, model, 0.01)
+    x = torch.randn((L, T, H), device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    out = torch.empty((L, T, H), device="cuda", dtype=torch.float32)
+    for _ in range(3):
+        expert.expert_forward(x.data_ptr(), out.data_ptr(), T)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        expert.expert_forward(x.data_ptr(), out.data_ptr(), T)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    flops = 6.0 * L * T * H * I
+    peak = None
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            peak = float(json.load(f).get("bf16_tflops", 0)) or None
+    tf = flops / (ms / 1e3) / 1e12
+    print(json.dumps({"kernel_case": "expert_forward", "layers": L, "batch_tokens": T, "hidden": H, "intermediate": I,
+                      "ms": ms, "tflops": tf, "peak_tflops": peak, "peak_kind": "measured" if peak else None,
+                      "frac": tf / peak if peak else None, "finite": bool(torch.isfinite(out).all().item())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,13 +503,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-prompt", type=int, default=64)
     ap.add_argument("--cpu-tokens", type=int, default=128)
-    ap.add_argument("--kernel-case", default="", choices=["", "gemm"],
+    ap.add_argument("--kernel-case", default="", choices=["", "gemm", "expert_forward"],
                     help="run only the tensor-core GEMM on the decode step's two largest shapes (gate|up rows, LM head) "
                          "through the op-level entry point and exit: the small program that ncu captures are taken from")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), if known")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    if a.kernel_case == "expert_forward":
+        run_expert_forward_case(a)
+        return
     if a.kernel_case:
         run_kernel_case(a)
         return

@@ -93,6 +93,13 @@ uint64_t tffn_model_weight_bytes(const tffn_model* m, int with_expert);
  * on the device. The shape must match the model. */
 int tffn_expert_load(const tffn_model* m, const char* path, float scale, tffn_expert** out);
 int tffn_expert_set_scale(tffn_expert* e, float scale); /* ExpertModel::output_scale */
+/* expert_forward of the trainer (trainer/src/model/ffn_expert.cu:151-175) on the inference kernels, for
+ * training-shaped batches: d_x_norm = DEVICE bf16 [num_layers][batch_tokens][hidden] (the normalised FFN
+ * input of every layer), d_out_delta = DEVICE fp32 [num_layers][batch_tokens][hidden] =
+ * scale * (bf16(silu(bf16(x Wg^T)) * bf16(x Wu^T)) Wd^T), scale = the expert's output scale (the trainer
+ * uses kExpertOutputScale = 0.01: set it with tffn_expert_set_scale). Runs on `stream` (0: the default
+ * stream) and returns when the result is complete. */
+int tffn_expert_forward(const tffn_expert* e, const void* d_x_norm, float* d_out_delta, int batch_tokens, void* stream);
 float tffn_expert_get_scale(const tffn_expert* e);
 void tffn_expert_free(tffn_expert* e); /* expert_free (expert.cu:33-42) */
 

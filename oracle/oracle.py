@@ -205,3 +205,26 @@ class Oracle:
 
 if __name__ == "__main__":
     print(build(force=True))
+
+
+def expert_forward_ref(x_norm_bf16, gate_bf16, up_bf16, down_bf16, scale):
+    """CPU restatement of the trainer's expert_forward for ONE layer (trainer/src/model/ffn_expert.cu:151-175;
+    test infrastructure, never on the product path). All matrices as bf16 bit patterns (uint16):
+    x_norm [T,H], gate/up [I,H], down [H,I]. gemm_bf16_out rounds the fp32 accumulators of gate and up to
+    bf16 (:162-165), silu_mul_bf16 forms bf16(silu(g) * u) in fp32 (:166), gemm_bf16 keeps the down
+    projection in fp32 (:167-169) and scale_fp32 multiplies it by the output scale (:171). Returns fp32 [T,H]."""
+    import numpy as np
+
+    def f32(u):
+        return (np.asarray(u).astype(np.uint32) << 16).view(np.float32)
+
+    def bf16r(a):  # round to nearest even to bf16, back to fp32
+        b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint32) << 16
+        return r.view(np.float32)
+
+    x = f32(x_norm_bf16)
+    g = bf16r(x @ f32(gate_bf16).T)
+    u = bf16r(x @ f32(up_bf16).T)
+    act = bf16r((g / (1.0 + np.exp(-g.astype(np.float64))).astype(np.float32)) * u)
+    return (act @ f32(down_bf16).T).astype(np.float32) * np.float32(scale)

@@ -192,6 +192,12 @@ int tffn_expert_set_scale(tffn_expert* e, float scale) {
     });
 }
 float tffn_expert_get_scale(const tffn_expert* e) { return e ? e->e->scale : 0.f; }
+int tffn_expert_forward(const tffn_expert* e, const void* d_x_norm, float* d_out_delta, int batch_tokens, void* stream) {
+    return guard([&] {
+        need(e, "NULL expert");
+        e->e->forward_layers(d_x_norm, d_out_delta, batch_tokens, (cudaStream_t)stream);
+    });
+}
 void tffn_expert_free(tffn_expert* e) {
     if (!e) return;
     delete e->e;

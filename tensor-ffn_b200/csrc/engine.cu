@@ -53,6 +53,56 @@ __global__ void k_copy_rows_bf16(const bf16* __restrict__ src, bf16* __restrict_
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------ Expert op
+void Expert::forward_layers(const void* d_x, float* d_out, int T, cudaStream_t stream) const {
+    if (!d_x || !d_out || T < 1) throw Error(kErrInvalid, "bad expert_forward arguments");
+    const Config& c = model->cfg;
+    const int H = c.hidden_size, I = c.intermediate_size;
+    TFFN_CUDA(cudaSetDevice(model->device));
+    cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
+    DeviceBuffer act, status;
+    act.alloc((size_t)T * I * 2);
+    status.alloc(4);
+    TFFN_CUDA(cudaMemsetAsync(status.p, 0, 4, stream));
+    const GemmWorkspace ws{status.as<int>(), model->num_sms};
+    auto run = [&](GemmCall& g) {
+        const int rc = launch_gemm(g, ws, stream);
+        if (rc == -1000) throw Error(kErrCuda, "cuTensorMapEncodeTiled failed or is unavailable");
+        if (rc != 0) cuda_check((cudaError_t)rc, "tensor-core GEMM launch", __FILE__, __LINE__);
+    };
+    for (size_t l = 0; l < layers.size(); ++l) {
+        const bf16* x = (const bf16*)d_x + l * (size_t)T * H;
+        const bf16* rec = layers[l].packed.as<bf16>();
+        GemmCall g;
+        memset(&g, 0, sizeof g);
+        g.x_rows_alloc = T;
+        g.T = T;
+        g.alpha = 1.f;
+        // gate | up with the SwiGLU epilogue (gemm_bf16_out x2 + silu_mul_bf16, ffn_expert.cu:162-166)
+        g.op[0] = {rec, (int64_t)3 * H, x, H, H};
+        g.op[1] = {rec + H, (int64_t)3 * H, x, H, H};
+        g.N = I;
+        g.mode = GEMM_SWIGLU;
+        g.out = act.p;
+        g.ldo = I;
+        run(g);
+        // down projection, fp32 out, scaled (gemm_bf16 + scale_fp32, ffn_expert.cu:167-171)
+        g.op[0] = {layers[l].down.as<bf16>(), I, act.as<bf16>(), I, I};
+        g.op[1] = {nullptr, 0, nullptr, 0, 0};
+        g.N = H;
+        g.mode = GEMM_STORE_F32;
+        g.out = d_out + l * (size_t)T * H;
+        g.ldo = H;
+        g.out_scale = scale;
+        run(g);
+        g.out_scale = 0.f;
+    }
+    int st = 0;
+    TFFN_CUDA(cudaMemcpyAsync(&st, status.p, 4, cudaMemcpyDeviceToHost, stream));
+    TFFN_CUDA(cudaStreamSynchronize(stream));
+    if (st != 0) throw Error(kErrDevice, "device status " + std::to_string(st) + " in expert_forward");
+}
+
 // ------------------------------------------------------------------------------------------ Model
 Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size) {
     if (tp_size != 1 || tp_rank != 0) throw Error(kErrUnsupported, "tensor parallel loading is not available: tp_size must be 1");

@@ -60,6 +60,10 @@ struct Expert {
     std::vector<FfnWeights> layers;
     uint64_t weight_bytes = 0;
     static Expert* load(const Model* m, const std::string& path, float scale);
+    // The trainer's expert_forward (trainer/src/model/ffn_expert.cu:151-175) on the inference kernels:
+    // d_x device bf16 [layers][T][hidden] (the normalised FFN inputs of every layer), d_out device fp32
+    // [layers][T][hidden] = scale * down(silu(gate x) * up x), scale = this expert's output scale.
+    void forward_layers(const void* d_x, float* d_out, int T, cudaStream_t stream) const;
 };
 
 // kernel classes of the per-launch profile (tffn_session_profile_*)

@@ -40,7 +40,7 @@ struct GemmDev {
     int kblocks[2];
     int N, T, splits, mode, t_tiles, stages;
     int tile_n;          // output indices per tile: 128, or 64 for GEMM_SWIGLU (64 gate rows + 64 up rows per tile)
-    float alpha;
+    float alpha, out_scale;
     void* out[2];        // per problem
     long long ldo;
     int* status;
@@ -183,9 +183,9 @@ __device__ __forceinline__ void finalize_plain(const GemmDev& p, void* out, int 
         case GEMM_STORE_F32:
             if (!out) break;  // only the fused arg-max was asked for
             if (vec) {
-                *(float4*)((float*)out + o) = v;
+                *(float4*)((float*)out + o) = make_float4(p.out_scale * v.x, p.out_scale * v.y, p.out_scale * v.z, p.out_scale * v.w);
             } else {
-                for (int j = 0; j < 4 && n + j < p.N; ++j) ((float*)out)[o + j] = f[j];
+                for (int j = 0; j < 4 && n + j < p.N; ++j) ((float*)out)[o + j] = p.out_scale * f[j];
             }
             break;
         case GEMM_RESIDUAL: {
@@ -662,6 +662,7 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     p.T = c.T;
     p.mode = c.mode;
     p.alpha = c.alpha;
+    p.out_scale = c.out_scale == 0.f ? 1.f : c.out_scale;
     p.out[0] = c.out;
     p.out[1] = c.out2 ? c.out2 : c.out;
     p.ldo = c.ldo;

@@ -58,6 +58,7 @@ struct GemmCall {
     // gate/up next to the base's): its operands and its output; out2 == nullptr means none
     GemmOperand op2[2];
     void* out2;
+    float out_scale;  // GEMM_STORE_F32: the stored value is out_scale * sum (0 means 1)
     const GemmQkvEpilogue* qkv;  // GEMM_QKV only
     // GEMM_STORE_F32 only, optional: greedy pick fused into the epilogue. Every CTA leaves, per token, the
     // maximum of its 128 output rows and its index (lowest index among equal maxima) in

@@ -73,6 +73,7 @@ _SIGS = {
     "tffn_session_reset": (_i, [_vp, _i]),
     "tffn_session_seq_len": (_i, [_vp, _i]),
     "tffn_session_set_launch_mode": (_i, [_vp, _i]),
+    "tffn_expert_forward": (_i, [_vp, _vp, _vp, _i, _vp]),
     "tffn_session_set_ablation": (_i, [_vp, ctypes.c_uint]),
     "tffn_session_set_sampling": (_i, [_vp, _f, ctypes.c_uint32]),
     "tffn_session_set_bs1_path": (_i, [_vp, _i]),
@@ -196,6 +197,12 @@ class ExpertModel:
     @output_scale.setter
     def output_scale(self, v: float):
         _check(_L.tffn_expert_set_scale(self._h, v))
+
+    def expert_forward(self, x_norm_ptr: int, out_delta_ptr: int, batch_tokens: int, stream: int = 0):
+        """expert_forward of the trainer (trainer/src/model/ffn_expert.cu:151-175): DEVICE pointers to
+        bf16 [layers, batch_tokens, hidden] in and fp32 [layers, batch_tokens, hidden] out"""
+        _check(_L.tffn_expert_forward(self._h, ctypes.c_void_p(x_norm_ptr), ctypes.c_void_p(out_delta_ptr), batch_tokens,
+                                      ctypes.c_void_p(stream)))
 
     def free(self):
         if self._h:
