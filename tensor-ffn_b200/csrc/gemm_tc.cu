@@ -690,6 +690,11 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
         splits = force_splits;
     } else {
         while (splits < kMaxSplits && tiles * splits * 2 <= ws.num_sms + ws.num_sms / 8 && total_kb / (splits * 2) >= 1) splits *= 2;
+        // A long K extent: the stage cadence is a property of the CTA (about 0.45 us per stage), so two
+        // CTAs per SM stream twice as much as one until HBM is the limit; keep splitting while every CTA
+        // still gets eight k-blocks and the grid fits two per SM (measured at 16 tokens, N 2048, K 22016:
+        // 8 splits 49.5 us, half of the 8-CTA clusters waiting for a second wave; 16 splits 18.0 us).
+        while (splits < kMaxSplits && tiles * splits * 2 <= 2 * ws.num_sms && total_kb / (splits * 2) >= 8) splits *= 2;
     }
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return (int)cudaErrorInvalidValue;
     if (splits > total_kb) return (int)cudaErrorInvalidValue;
