@@ -753,10 +753,10 @@ int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream,
     if (c.T <= 0 || c.N <= 0 || c.op[0].K <= 0) return (int)cudaErrorInvalidValue;
     // A short K extent with few output tiles (the attention projections of a small model): the grid is
     // filled by splitting K, and the cost of such a launch is the exchange of the partial tiles (measured:
-    // 28 KB per CTA over distributed shared memory take 2 to 3.6 us). Halving the token tile halves the
-    // split factor and shrinks that exchange to 12 KB per CTA for one or two more k-blocks per CTA; the
-    // weights are then read twice, from L2 (measured on the 0.5B shape at 64 tokens: q|k|v 8.5 -> 7.2 us,
-    // o_proj 8.0 -> 7.2 us per launch inside a step).
+    // 28 KB per CTA over distributed shared memory take 2 to 3.6 us). Halving the token tile (two token
+    // tiles, the same split factor, twice the CTAs) halves the plane a CTA parks and the exchange: 14 KB per
+    // CTA; the weights are then read twice, the second time from L2 (measured on the 0.5B shape at 64
+    // tokens: q|k|v 8.5 -> 7.2 us, o_proj 8.0 -> 7.2 us per launch inside a step).
     {
         const int total_kb = (c.op[0].K + BK - 1) / BK + (c.op[1].K > 0 ? (c.op[1].K + BK - 1) / BK : 0);
         const int n_tiles = (c.N + BM - 1) / BM;
