@@ -93,3 +93,24 @@ def test_sampled_decode_run_matches_stepwise(model_dirs):
             outs.append(np.asarray(s.decode_run(2, 8)))
         s.free()
     assert (outs[0] == outs[1]).all()
+
+
+def test_cli_device_sampling_equals_host_sampling(model_dirs, tmp_path):
+    """tensor-ffn-inference --temperature: picks drawn on the device == the reference's host loop over
+    downloaded logits (--host-sampling), token for token, same mt19937(42) stream"""
+    import os
+    import subprocess
+    import synth
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli = os.path.join(root, "tensor-ffn_b200", "tensor-ffn-inference")
+    d, ep, cfg = model_dirs["mini05"]
+    ids = tmp_path / "prompt.i32"
+    np.asarray(synth.prompts(1, 12, 5, cfg["vocab_size"])[0], dtype=np.int32).tofile(ids)
+    outs = []
+    for extra in ([], ["--host-sampling"]):
+        cmd = [cli, "--model", d, "--expert", ep, "--prompt-ids", str(ids), "--max-tokens", "12", "--temperature", "0.9",
+               "--ignore-eos", "--max-seq", "64"] + extra + ["--device", "0"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        outs.append(r.stdout.split("Generating:")[1])
+    assert outs[0] == outs[1] and len(outs[0].strip()) > 0
