@@ -2,7 +2,7 @@
 kernels (tffn_expert_forward) for training-shaped batches [layers, batch_tokens, hidden], against a numpy
 restatement (oracle.expert_forward_ref). Tolerance: fp32 accumulation order differs between the tensor
 cores and numpy, so single bf16 rounding flips of gate / up / act occur; the maximum error is held to
-2e-2 of the largest reference value (the bar of BASELINE for hidden states), the mean error to 1e-3."""
+2e-2 of the largest reference value (the bar stated for hidden states on the inference path), the mean error to 1e-3."""
 import numpy as np
 import pytest
 

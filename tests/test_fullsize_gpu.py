@@ -1,7 +1,7 @@
 """-m gpu: BASELINE.json configs[0] at full size — Qwen2.5-0.5B shape, bf16, batch 1, 128-token
 prompt then 128 greedy tokens, with and without the expert — against (a) the reference's own code
 (oracle/_ref/ref_driver, when it was built) and (b) the CPU oracle, teacher-forced on the
-reference's token stream. Bars from BASELINE: per-layer hidden states and logits within
+reference's token stream. Stated bars: per-layer hidden states and logits within
 max|a-b| / max|b| <= 2e-2, top-1 agreement >= 99 %.
 """
 import os
@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DRIVER = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
 P, N = 128, 128
-TOL = 2e-2        # BASELINE's bar, applied to logits (max-abs-normalised) and to hidden states (relative L2)
+TOL = 2e-2        # the stated bar, applied to logits (max-abs-normalised) and to hidden states (relative L2)
 HIDDEN_MAX_TOL = 4e-2
 # Hidden states are bf16: one rounding flip on the largest element of a row is 0.8 % of the
 # maximum, and flips accumulate over 24 layers. The reference and a rounding-exact restatement of

@@ -33,7 +33,7 @@ def test_golden_fixtures_exist():
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[4:-4] for p in GOLDEN])
 def test_oracle_matches_reference_outputs(path, tmp_path):
-    """Tolerances from BASELINE: max|a-b| / max|b| <= 2e-2 for hidden states and logits.
+    """Tolerance stated for this path: max|a-b| / max|b| <= 2e-2 for hidden states and logits.
     The reference runs attention in TF32 with fast-math and cuBLAS' summation order, so bit
     equality is not on offer; observed distances are 4e-3..6e-3 (logits), <= 1.1e-2 (hidden)."""
     import oracle
