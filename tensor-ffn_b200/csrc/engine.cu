@@ -18,7 +18,12 @@ void DeviceBuffer::alloc(size_t n) {
     if (n == 0) return;
     TFFN_CUDA(cudaMalloc(&p, n));
     bytes = n;
+    // The fill runs on the default stream and returns before it has finished, while the sessions work
+    // on non-blocking streams that are not ordered after it: without the wait a buffer's first kernel
+    // could run before the fill and have its output zeroed (seen as a rare change of sampled tokens when
+    // a session was used right after it was created).
     TFFN_CUDA(cudaMemset(p, 0, n));
+    TFFN_CUDA(cudaStreamSynchronize(0));
 }
 void DeviceBuffer::release() {
     if (p) cudaFree(p);
@@ -886,6 +891,7 @@ int Session::timeline(int n_seqs, uint64_t* out, int max_launches, int trace_lau
     if (want_trace) {
         tl_trace_buf_.alloc((size_t)trace_ctas * 64 * 8);
         TFFN_CUDA(cudaMemset(tl_trace_buf_.p, 0, tl_trace_buf_.bytes));
+        TFFN_CUDA(cudaStreamSynchronize(0));
     }
     tl_trace_launch_ = want_trace ? trace_launch : -1;
     if (n_seqs == 1 && use_bs1_ && m_->bs1_ok) throw Error(kErrUnsupported, "the timeline covers the batched path only");

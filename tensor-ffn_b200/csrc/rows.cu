@@ -38,35 +38,44 @@ __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x
     const int r = blockIdx.x;
     const int src_row = row_idx ? row_idx[r] : r;
     const uint4* xr = (const uint4*)(x + (size_t)src_row * H);
+    // The first 128 16-byte pieces of the row (all of it up to H = 1024) and of the norm weights stay in
+    // registers between the two passes; both loads are in flight together.
+    const int n16 = H / 8;
+    const uint4* wr = (const uint4*)w;
+    const bool own = (int)threadIdx.x < n16;
+    const uint4 v0 = own ? __ldcg(xr + threadIdx.x) : make_uint4(0, 0, 0, 0);
+    const uint4 g0 = own ? __ldg(wr + threadIdx.x) : make_uint4(0, 0, 0, 0);
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H / 8; i += 128) {
-        uint4 v = __ldcg(xr + i);
-        uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    auto sq = [&](const uint4& q) {
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float a = bf16_lo(u[j]), b = bf16_hi(u[j]);
+            const float a = bf16_lo(u[j]), b = bf16_hi(u[j]);
             ss += a * a + b * b;
         }
-    }
+    };
+    sq(v0);
+    for (int i = threadIdx.x + 128; i < n16; i += 128) sq(__ldcg(xr + i));
     __shared__ float red[4];
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     ss = red[0] + red[1] + red[2] + red[3];
     const float rinv = rsqrtf(ss / (float)H + eps);
-    const uint4* wr = (const uint4*)w;
     uint4* orow = (uint4*)(out + (size_t)r * H);
-    for (int i = threadIdx.x; i < H / 8; i += 128) {
-        uint4 v = __ldcg(xr + i), g = __ldg(wr + i);
-        uint32_t u[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w}, o[4];
+    auto scale = [&](const uint4& q, const uint4& g) {
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w}, gw[4] = {g.x, g.y, g.z, g.w};
+        uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float a = bf16_lo(u[j]) * rinv * bf16_lo(gw[j]);
-            float b = bf16_hi(u[j]) * rinv * bf16_hi(gw[j]);
+            const float a = bf16_lo(u[j]) * rinv * bf16_lo(gw[j]);
+            const float b = bf16_hi(u[j]) * rinv * bf16_hi(gw[j]);
             o[j] = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
         }
-        orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+        return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    if (own) orow[threadIdx.x] = scale(v0, g0);
+    for (int i = threadIdx.x + 128; i < n16; i += 128) orow[i] = scale(__ldcg(xr + i), __ldg(wr + i));
     if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 

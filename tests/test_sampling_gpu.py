@@ -81,18 +81,24 @@ def test_sampled_decode_run_matches_stepwise(model_dirs):
     m = tffn.qwen_load(d)
     e = tffn.checkpoint_load(ep, m, 0.1)
     prompts = [synth.prompts(1, 9 + i, 60 + i, cfg["vocab_size"])[0] for i in range(2)]
-    outs = []
-    for stepwise in (False, True):
+    def run(stepwise):
         s = tffn.Session(m, e, max_batch=2, max_seq=96)
         s.set_launch_mode(2)
         s.set_sampling(1.3, 7)
         s.prefill(prompts)
         if stepwise:
-            outs.append(np.array([s.decode_step(None, n_seqs=2)[0] for _ in range(8)]))
+            out = np.array([s.decode_step(None, n_seqs=2)[0] for _ in range(8)])
         else:
-            outs.append(np.asarray(s.decode_run(2, 8)))
+            out = np.asarray(s.decode_run(2, 8)).copy()
+        assert s.status() == 0
         s.free()
-    assert (outs[0] == outs[1]).all()
+        return out
+
+    a, b = run(False), run(True)
+    if not (a == b).all():  # say which of the two is unstable before failing
+        a2, b2 = run(False), run(True)
+        raise AssertionError(("run", a.T.tolist(), "stepwise", b.T.tolist(), "run again", a2.T.tolist(), "stepwise again",
+                              b2.T.tolist()))
 
 
 def test_cli_device_sampling_equals_host_sampling(model_dirs, tmp_path):
