@@ -36,6 +36,9 @@ namespace {
 void upload(DeviceBuffer& dst, const void* src, size_t bytes) {
     dst.alloc(bytes);
     TFFN_CUDA(cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice));
+    // from pageable memory the call may return once the data is staged: wait for it to reach the device,
+    // the streams that will read it are not ordered after the default stream
+    TFFN_CUDA(cudaStreamSynchronize(0));
 }
 
 // one block: publish the picks as the next step's inputs, advance the sequence lengths
@@ -239,6 +242,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     h_block_table_.assign((size_t)max_batch * max_pages_per_seq_, -1);
     block_table_.alloc(h_block_table_.size() * 4);
     TFFN_CUDA(cudaMemcpy(block_table_.p, h_block_table_.data(), h_block_table_.size() * 4, cudaMemcpyHostToDevice));
+    TFFN_CUDA(cudaStreamSynchronize(0));  // staged copies have reached the device before the session's own stream is used
     h_seq_len_.assign(max_batch, 0);
     h_pages_used_.assign(max_batch, 0);
     seq_len_dev_.alloc((size_t)max_batch * 4);
@@ -905,6 +909,7 @@ int Session::timeline(int n_seqs, uint64_t* out, int max_launches, int trace_lau
         for (int rep = 0; rep < 3; ++rep) {  // with graphs the first step captures, the last one is reported
             if (launch_mode_ < 2 || rep == 0) tl_cls_.clear();
             TFFN_CUDA(cudaMemcpy(tl_buf_.p, init.data(), init.size() * 8, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaStreamSynchronize(0));
             decode_run(n_seqs, 1, nullptr);
         }
     } catch (...) {
