@@ -114,15 +114,8 @@ void tffn_session_free(tffn_session* s);
 int tffn_session_reset(tffn_session* s, int slot);
 int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */
 /* 0: plain stream launches. 1: programmatic dependent launch between the batch-1 kernels.
- * 2: 1 + every decode step (batch-1 and batched) replayed from a CUDA graph.
- * 3: 2, and batch-1 steps run as ONE persistent cooperative kernel per token where the shape has an
- *    instantiation (otherwise as in 2). Default 1. */
+ * 2: 1 + every decode step (batch-1 and batched) replayed from a CUDA graph. Default 1. */
 int tffn_session_set_launch_mode(tffn_session* s, int mode);
-/* Timing aid: kernel classes (bit i = class i of tffn_profile_class_name) that the batched path
- * skips from now on. The step then computes garbage; the drop in step time is what that class costs
- * inside the overlapped (dependent-launch, graph) schedule, which per-kernel events cannot show.
- * 0 restores normal operation. */
-int tffn_session_set_ablation(tffn_session* s, unsigned mask);
 /* Temperature sampling on the device (the reference samples on the host from a 608 KB logits row per
  * token: sample(), inference/src/main.cpp:52-63). temperature <= 0 restores greedy picks. Otherwise every
  * pick of tffn_prefill / tffn_decode_step / tffn_decode_run is drawn as sample() draws it (float maximum,
@@ -160,29 +153,6 @@ int tffn_decode_run(tffn_session* s, int n_seqs, int steps, int32_t* tokens_out)
 /* Device status word (0 = none) and kernel launches issued by the session so far. */
 int tffn_session_status(tffn_session* s);
 uint64_t tffn_session_launch_count(const tffn_session* s);
-/* Per-kernel timing for benchmarks: while enabled, every kernel launch of the session is
- * bracketed by CUDA events on the session's stream (this serialises kernels that would
- * otherwise overlap, so never time throughput with it on). tffn_session_profile_read returns the
- * number of kernel classes and fills ms[i] (device time) and launches[i] for i < cap;
- * tffn_profile_class_name(i) names class i. No counterpart in the reference. */
-int tffn_session_profile(tffn_session* s, int enable);
-int tffn_session_profile_read(tffn_session* s, float* ms, int32_t* launches, int cap);
-const char* tffn_profile_class_name(int cls);
-/* Profiling aid (no counterpart in the reference): runs three batched decode steps of slots
- * 0..n_seqs-1 in the session's launch mode (the sequences advance by three tokens) and reports the
- * timeline of the last one. out[i*7] = kernel class of launch i (tffn_profile_class_name), then the
- * minimum and maximum over the launch's CTAs of: kernel entry, return from the grid-dependency wait,
- * exit (globaltimer, ns). Unlike per-kernel events this shows the overlapped schedule as it runs.
- * If trace_out is not NULL and launch number trace_launch is a tensor-core GEMM of at most trace_ctas
- * CTAs, trace_out[cta*64 + k] receives that launch's per-CTA phase timestamps (k as documented for
- * tffn_op_gemm_trace). Returns the number of launches (at most max_launches are recorded). */
-int tffn_session_timeline(tffn_session* s, int n_seqs, uint64_t* out, int max_launches, int trace_launch,
-                          uint64_t* trace_out, int trace_ctas);
-/* Profiling aid (no counterpart in the reference): runs ONE batch-1 decode step of slot 0 on the
- * persistent kernel, feeding the slot's previous pick, and returns per-CTA device timestamps
- * (globaltimer, ns) of layer 1 in out[cta*16 + k]: k = 0 layer start, 1/2 before/after the barrier that
- * ends QKV, 3/4 attention, 5/6 o_proj, 7/8 SwiGLU, 9/10 partial-sum fold. Returns the CTA count. */
-int tffn_session_mega_trace(tffn_session* s, uint64_t* out, int max_ctas);
 /* the stream the session launches on (a cudaStream_t) */
 void* tffn_session_stream(const tffn_session* s);
 
@@ -191,13 +161,6 @@ void* tffn_session_stream(const tffn_session* s);
  * fp32 out, host pointers); splits = 0 lets the launcher choose the K split.
  * Stands in for gemm_bf16 (inference/src/backend/cuda_ops.cu:18-29). */
 int tffn_op_gemm(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits);
-/* Same, and additionally returns 64 device timestamps (globaltimer, ns) per CTA in trace[trace_ctas*64]
- * (CTA order: split-major, then token tile, then row tile): 0 start, 1 weight boxes requested,
- * 2 dependency wait over, 3 last MMA issued, 4 accumulator complete, 5 epilogue done, 6 cluster
- * barrier passed, 7 cluster reduction done, 8 end, 16+i pipeline stage i arrived. A profiling aid with
- * no counterpart in the reference. */
-int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* out, int T, int N, int K, int splits,
-                       uint64_t* trace, int trace_ctas);
 /* The fused batch-1 SwiGLU kernel alone (host pointers, bf16 bits): h_out = bf16(h + FFN(rmsnorm(h)))
  * with FFN = base + expert_scale * expert (packed_expert may be NULL). packed_* use the record
  * layout [I][3][H] = gate row, up row, down column per intermediate index. Stands in for the FFN
@@ -205,25 +168,19 @@ int tffn_op_gemm_trace(int device, const uint16_t* X, const uint16_t* W, float* 
  * (inference/src/model/expert.cu:44-59) at T = 1. */
 int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
                        const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out);
-/* Same, and additionally returns 16 device timestamps (globaltimer, ns) per CTA of a second, warm
- * launch in trace[trace_ctas*16] (trace_ctas >= SM count): 0 start, 1 RMSNorm done, 2 first record
- * arrived, 3 last record consumed, 4 CTA partial written, 5 group ticket taken, 6 group fold done,
- * 7 residual updated. A profiling aid with no counterpart in the reference. */
-int tffn_op_swiglu_bs1_trace(int device, const uint16_t* h_in, const uint16_t* norm_w, const uint16_t* packed_base,
-                             const uint16_t* packed_expert, float expert_scale, float eps, int H, int I, uint16_t* h_out,
-                             uint64_t* trace, int trace_ctas);
 /* tffn_op_swiglu_bs1 for callers that must not allocate device memory (no counterpart in the
  * reference, whose every buffer comes from cudaMalloc): a host thread in a latency-critical loop
- * that may not take the allocator's lock or cause an implicit synchronisation, a plugin inside a
- * process whose device memory is owned and reserved by someone else, a deployment with a memory
- * budget fixed at start-up. All pointers are DEVICE pointers supplied by the caller (h_io is
- * updated in place); the kernel's scratch is a fixed array inside the library (about 1.4 MB per
- * GPU that loads it), so hidden <= 2048 and at most 160 SMs, larger requests return
- * TFFN_ERR_CAPACITY. The function calls no cudaMalloc / cudaFree; it clears the part of the
- * scratch that must start at zero, launches on `cuda_stream` and waits for the result. Calls that
- * could overlap on one GPU share the scratch and must be serialised by the caller. The first
- * call on a device does a one-time set-up (address look-up of the array): make it before any
- * stream capture. */
+ * that may not take the allocator's lock or cause a device-wide implicit synchronisation, a plugin
+ * inside a process whose device memory is owned and reserved by someone else, a deployment with a
+ * memory budget fixed at start-up. All pointers are DEVICE pointers supplied by the caller, each
+ * 16-byte aligned (TFFN_ERR_INVALID otherwise); h_io is updated in place. The kernel's scratch is a
+ * fixed array inside the library (about 1.4 MB per GPU that loads it), so hidden <= 2048 and at most
+ * 160 SMs; larger requests return TFFN_ERR_CAPACITY. The function calls no cudaMalloc / cudaFree; it
+ * clears the part of the scratch that must start at zero, launches on `cuda_stream`, and BLOCKS until
+ * that stream has finished the call (it synchronises only that stream, nothing device-wide), so it
+ * must not be called while the stream is being captured. Calls that could overlap on one GPU share
+ * the scratch and must be serialised by the caller. The first call on a device also looks up the
+ * array's device address. The calling thread's current device is left as it was. */
 int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* norm_w, const void* packed_base,
                                const void* packed_expert, float expert_scale, float eps, int H, int I, void* cuda_stream);
 /* Runs a kernel that waits on a barrier nothing signals; returns the device status it

@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtffn.so")
 CLI = os.path.join(HERE, "tensor-ffn-inference")
-LIB_SOURCES = ["host_io.cpp", "c_api.cpp", "engine.cu", "gemm_tc.cu", "rows.cu", "attn.cu", "decode_bs1.cu", "mega_bs1.cu", "noalloc.cu"]
+LIB_SOURCES = ["host_io.cpp", "c_api.cpp", "engine.cu", "gemm_tc.cu", "rows.cu", "attn.cu", "decode_bs1.cu", "noalloc.cu"]
 CLI_SOURCES = ["cli_main.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr"]
@@ -29,7 +29,7 @@ def _newer(target: str, deps: list[str]) -> bool:
 
 def _headers() -> list[str]:
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    hs.append(os.path.join(HERE, "..", "include", "tffn.h"))
+    hs += [os.path.join(HERE, "..", "include", f) for f in ("tffn.h", "tffn_diag.h")]
     return hs
 
 

@@ -546,11 +546,6 @@ template <int HD>
 void launch_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                const int* tok_pos, bf16* ctx, int nh, int G, int splits, int early, float* ws, int* counters, int* status,
                unsigned long long* tl, unsigned long long* trace) {
-    static bool configured = false;  // benign race: the call is idempotent
-    if (!configured) {
-        cudaFuncSetAttribute(k_attn_decode<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
-        configured = true;
-    }
     launch_k(k_attn_decode<HD>, grid, dim3(kAttnCtaThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos, ctx,
              nh, G, splits, early, ws, counters, status, tl, trace);
 }
@@ -559,16 +554,21 @@ template <int HD>
 void launch_prefill_hd(dim3 grid, cudaStream_t s, bool pdl, const float* q, const KvView& kv, int layer, const int* tok_seq,
                        const int* tok_pos, const int* grp_first, const int* grp_count, bf16* ctx, int nh, int G, int* status,
                        unsigned long long* tl) {
-    static bool configured = false;  // benign race: the call is idempotent
-    if (!configured) {
-        cudaFuncSetAttribute(k_attn_prefill<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM);
-        configured = true;
-    }
     launch_k(k_attn_prefill<HD>, grid, dim3(kAttnCtaThreads), (size_t)AttnCfg<HD>::SMEM, s, pdl, q, kv, layer, tok_seq, tok_pos,
              grp_first, grp_count, ctx, nh, G, status, tl);
 }
 
 }  // namespace
+
+// The dynamic shared-memory opt-in is a per-device attribute of a kernel: every session makes it for
+// its own device (with that device current), outside of stream capture.
+int attn_prepare() {
+    cudaError_t e = cudaFuncSetAttribute(k_attn_decode<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<64>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_decode<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_prefill<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<64>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_prefill<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
+    return (int)e;
+}
 
 constexpr int kMinSplitRows = 1024;
 

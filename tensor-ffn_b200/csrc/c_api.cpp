@@ -1,6 +1,7 @@
 // The C ABI (include/tffn.h): translates exceptions into status codes and keeps the last
 // message per thread. No torch types, plain pointers and sizes only.
 #include "../../include/tffn.h"
+#include "../../include/tffn_diag.h"
 #include "engine.h"
 #include <cstring>
 #include <memory>
@@ -313,14 +314,6 @@ int tffn_session_timeline(tffn_session* s, int n_seqs, uint64_t* out, int max_la
     int rc = guard([&] {
         need(s, "NULL session");
         n = s->s->timeline(n_seqs, out, max_launches, trace_launch, trace_out, trace_ctas);
-    });
-    return rc < 0 ? rc : n;
-}
-int tffn_session_mega_trace(tffn_session* s, uint64_t* out, int max_ctas) {
-    int n = 0;
-    int rc = guard([&] {
-        need(s, "NULL session");
-        n = s->s->mega_trace(out, max_ctas);
     });
     return rc < 0 ? rc : n;
 }

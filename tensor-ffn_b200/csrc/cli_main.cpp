@@ -4,6 +4,10 @@
 // reference's README works too. Extra flags (not in the reference): --prompt-ids <file> (raw
 // int32 ids instead of --prompt), --ignore-eos, --device <N>, --host-sampling (with --temperature: sample
 // on the host from downloaded logits as the reference does, instead of on the device).
+// The usage text, the flag scanning, the ChatML sequence, the stdout protocol and the host sampler
+// are the reference's own (inference/src/main.cpp:17-63, 127-144, 157-198), reproduced on purpose:
+// they ARE the command-line contract. What differs is what runs underneath: the six calls into the
+// reference's model code are replaced by calls into the C ABI.
 #include "../../include/tffn.h"
 #include <algorithm>
 #include <cmath>

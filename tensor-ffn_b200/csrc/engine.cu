@@ -303,6 +303,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     *h_status_ = 0;
 
     cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
+    cuda_check((cudaError_t)attn_prepare(), "attn_prepare", __FILE__, __LINE__);
     if (m->bs1_ok) cuda_check((cudaError_t)bs1_prepare((int)H, true), "bs1_prepare", __FILE__, __LINE__);
     bs1_h_.alloc(H * 2);
     bs1_q_.alloc(nh * hd * 4);
@@ -311,28 +312,6 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     bs1_tickets_.alloc(256 * 4);
     bs1_lm_val_.alloc((size_t)m->num_sms * 2 * 4);
     bs1_lm_idx_.alloc((size_t)m->num_sms * 2 * 4);
-    mega_ok_ = m->bs1_ok && bs1_mega_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
-    if (mega_ok_) {
-        int coop = 0;
-        TFFN_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
-        mega_ok_ = coop != 0;
-    }
-    if (mega_ok_) {
-        std::vector<Bs1Layer> ls(L);
-        for (size_t l = 0; l < L; ++l) {
-            const LayerWeights& lw = m->layers[l];
-            ls[l].wqkv = lw.wqkv.as<bf16>();
-            ls[l].bqkv = lw.has_bias ? lw.bqkv.as<bf16>() : nullptr;
-            ls[l].wo = lw.wo.as<bf16>();
-            ls[l].attn_norm = lw.attn_norm.as<bf16>();
-            ls[l].ffn_norm = lw.ffn_norm.as<bf16>();
-            ls[l].ffn_base = lw.ffn.packed.as<bf16>();
-            ls[l].ffn_expert = e ? e->layers[l].packed.as<bf16>() : nullptr;
-        }
-        upload(bs1_layers_dev_, ls.data(), L * sizeof(Bs1Layer));
-        mega_attn_part_.alloc(bs1_mega_attn_part_floats((int)nkv, (int)hd, (int)(nh / nkv)) * 4);
-        mega_barrier_.alloc(64);
-    }
     (void)V;
 }
 
@@ -351,7 +330,6 @@ Session::~Session() {
 int32_t* Session::pinned_i32(size_t n) {
     if (n > h_pinned_cap_) {
         if (h_pinned_i32_) cudaFreeHost(h_pinned_i32_);
-    if (h_sample_u_) cudaFreeHost(h_sample_u_);
         h_pinned_i32_ = nullptr;
         size_t cap = std::max<size_t>(n, 4096);
         TFFN_CUDA(cudaMallocHost(&h_pinned_i32_, cap * 4));
@@ -454,6 +432,7 @@ void Session::upload_draws(size_t n) {
         TFFN_CUDA(cudaMallocHost(&h_sample_u_, cap * 8));
         h_sample_cap_ = cap;
         sample_u_.alloc(cap * 8);
+        drop_graphs();  // captured steps hold the old address of the draws
     } else {
         TFFN_CUDA(cudaStreamSynchronize(stream_));  // the staging buffer may still feed an earlier copy
     }
@@ -463,7 +442,7 @@ void Session::upload_draws(size_t n) {
 }
 
 void Session::set_launch_mode(int mode) {
-    if (mode < 0 || mode > 3) throw Error(kErrInvalid, "launch mode must be 0, 1, 2 or 3");
+    if (mode < 0 || mode > 2) throw Error(kErrInvalid, "launch mode must be 0, 1 or 2");
     launch_mode_ = mode;
 }
 
@@ -826,16 +805,6 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
 }
 
 void Session::run_bs1(bool want_logits) {
-    if (launch_mode_ == 3 && mega_ok_ && !profile_) {
-        // one persistent cooperative kernel per token
-        const Bs1Ctx x = bs1_ctx(want_logits);
-        const int rc = launch_bs1_mega(x, (const Bs1Layer*)bs1_layers_dev_.p, m_->cfg.num_layers, m_->embed.as<bf16>(),
-                                       m_->final_norm.as<bf16>(), m_->lm_head, kv_, mega_attn_part_.as<float>(),
-                                       (unsigned*)mega_barrier_.p, stream_);
-        if (rc != 0) cuda_check((cudaError_t)rc, "persistent batch-1 kernel launch", __FILE__, __LINE__);
-        launches_ += 1;
-        return;
-    }
     if (launch_mode_ == 2 && !profile_) {
         if (!bs1_graph_ || bs1_graph_logits_ != want_logits) {
             if (bs1_graph_) {
@@ -859,28 +828,6 @@ void Session::run_bs1(bool want_logits) {
         launch_bs1_step(want_logits, launch_mode_ >= 1);
     }
     TFFN_CUDA(cudaGetLastError());
-}
-
-int Session::mega_trace(uint64_t* out, int max_ctas) {
-    if (!mega_ok_) throw Error(kErrUnsupported, "no persistent batch-1 kernel for this shape");
-    if (!out || max_ctas < m_->num_sms) throw Error(kErrInvalid, "trace buffer too small");
-    ensure_pages(0, h_seq_len_[0] + 1);
-    flush_tables();
-    ensure_ring(1);
-    TFFN_CUDA(cudaMemsetAsync(step_counter_.p, 0, 4, stream_));
-    DeviceBuffer tr;
-    tr.alloc((size_t)max_ctas * 16 * 8);
-    Bs1Ctx x = bs1_ctx(false);
-    x.trace = tr.as<unsigned long long>();
-    const int rc = launch_bs1_mega(x, (const Bs1Layer*)bs1_layers_dev_.p, m_->cfg.num_layers, m_->embed.as<bf16>(),
-                                   m_->final_norm.as<bf16>(), m_->lm_head, kv_, mega_attn_part_.as<float>(),
-                                   (unsigned*)mega_barrier_.p, stream_);
-    if (rc != 0) cuda_check((cudaError_t)rc, "persistent batch-1 kernel launch", __FILE__, __LINE__);
-    TFFN_CUDA(cudaStreamSynchronize(stream_));
-    h_seq_len_[0] += 1;
-    TFFN_CUDA(cudaMemcpy(out, tr.p, (size_t)max_ctas * 16 * 8, cudaMemcpyDeviceToHost));
-    check_status();
-    return m_->num_sms;
 }
 
 unsigned long long* Session::tl_next(int cls) {
@@ -1083,7 +1030,7 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
     int last_pick = 0;
     for (int c0 = 0; c0 < T; c0 += chunk_cap) {
         const int n = std::min(chunk_cap, T - c0);
-        int32_t* pin = pinned_i32((size_t)n * 5);
+        int32_t* pin = pinned_i32((size_t)n * 5 + 2);  // the last two: row index in, pick out
         for (int i = 0; i < n; ++i) {
             pin[i] = tokens[c0 + i];
             pin[n + i] = slot;
@@ -1102,9 +1049,18 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
             TFFN_CUDA(cudaMemcpyAsync(pin, picks_.as<int>() + (n - 1), 4, cudaMemcpyDeviceToHost, stream_));
             TFFN_CUDA(cudaStreamSynchronize(stream_));
             last_pick = pin[0];
-        } else {
+        } else if (c0 + n < T) {
             run_batched(n, 0, true, false, h_seq_len_[slot] + c0 + n, n_groups);
             TFFN_CUDA(cudaStreamSynchronize(stream_));
+        } else {
+            // no logits wanted: the LM head still runs for the last row, whose greedy pick feeds a
+            // following decode step that passes no tokens
+            pin[5 * n] = n - 1;
+            TFFN_CUDA(cudaMemcpyAsync(row_idx_.p, pin + 5 * n, 4, cudaMemcpyHostToDevice, stream_));
+            run_batched(n, 1, false, false, h_seq_len_[slot] + c0 + n, n_groups);
+            TFFN_CUDA(cudaMemcpyAsync(pin + 5 * n + 1, picks_.p, 4, cudaMemcpyDeviceToHost, stream_));
+            TFFN_CUDA(cudaStreamSynchronize(stream_));
+            last_pick = pin[5 * n + 1];
         }
     }
     h_seq_len_[slot] += T;

@@ -75,9 +75,6 @@ const char* kclass_name(int c);
 
 class Session {
 public:
-    // one persistent-kernel batch-1 step (feeds the previous pick) with phase timestamps of layer 1:
-    // out[cta*16 + k], k = 0 layer start, then before/after each of the five grid barriers
-    int mega_trace(uint64_t* out, int max_ctas);
     // Runs three batched decode steps of n_seqs slots (the sequences advance) and reports the last one:
     // per kernel launch 7 u64 = class, then min / max over its CTAs of entry, grid-wait return and exit
     // (globaltimer ns). Returns the number of launches. If launch number trace_launch is a tensor-core
@@ -160,8 +157,6 @@ private:
 
     // batch-1 path
     DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
-    DeviceBuffer bs1_layers_dev_, mega_attn_part_, mega_barrier_;  // persistent batch-1 kernel (launch mode 3)
-    bool mega_ok_ = false;
     cudaGraphExec_t bs1_graph_ = nullptr;
     bool bs1_graph_logits_ = false;
     // batched decode steps captured per (sequences, attention splits)

@@ -109,6 +109,8 @@ struct AttnWorkspace {
     int* counters;    // [T*nkv]
     int num_counters;
 };
+// opt the attention kernels into their dynamic shared memory (once per device, outside stream capture)
+int attn_prepare();
 // context splits launch_attention will use (a CUDA-graph key: the grid depends on it)
 int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWorkspace& ws, int num_sms);
 // one query token per (t): context = tok_pos[t] + 1 cached tokens of sequence tok_seq[t].
@@ -167,13 +169,6 @@ void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvVi
 void launch_bs1_oproj(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl);
 void launch_bs1_ffn(const Bs1Ctx& c, const Bs1Layer& ly, cudaStream_t s, bool pdl);
 void launch_bs1_lmhead(const Bs1Ctx& c, const bf16* final_norm, const bf16* lm_head, cudaStream_t s, bool pdl);
-
-// Batch-1 decode as one persistent cooperative kernel per token (mega_bs1.cu). Supported for the
-// shapes that have an instantiation and whose ring fits shared memory; `barrier` is one u32.
-bool bs1_mega_supported(int H, int I, int hd, int nh, int nkv);
-size_t bs1_mega_attn_part_floats(int nkv, int hd, int g);
-int launch_bs1_mega(const Bs1Ctx& c, const Bs1Layer* layers_dev, int L, const bf16* embed, const bf16* final_norm,
-                    const bf16* lm_head, KvView kv, float* attn_part, unsigned* barrier, cudaStream_t s);
 
 // fp32 -> bf16 (RNE) on device, used by the expert loader (inference/src/io/checkpoint.cpp:33-62)
 void launch_cast_f32_bf16(const float* src, bf16* dst, size_t n, cudaStream_t s);

@@ -17,7 +17,12 @@
 //    overwritten by the kernel before they are read. Two calls whose kernels overlap on the GPU
 //    (different streams, or different host threads) race on the scratch: serialise them.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
-//    opts the kernel into its shared-memory size. Make that first call outside of any stream capture.
+//    opts the kernel into its shared-memory size.
+//  * The call blocks until `cuda_stream` has finished it (it synchronises that stream only, never
+//    the device), so it cannot be part of a stream capture.
+//  * The caller's pointers go to the kernel as they are; bulk copies and 16-byte vector loads
+//    need them 16-byte aligned, which is checked here because a misaligned access would fault.
+//  * The calling thread's current device is restored before return.
 #include "../../include/tffn.h"
 #include "engine.h"
 #include <mutex>
@@ -64,7 +69,17 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
         return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: hidden must be a multiple of 8 and at most " +
                                            std::to_string(kMaxHidden) + " (the built-in scratch is sized for that)");
     if (device < 0 || device >= kMaxDevices) return fail(TFFN_ERR_INVALID, "device index out of range");
-    cudaError_t e = cudaSetDevice(device);
+    for (const void* ptr : {(const void*)h_io, norm_w, packed_base, packed_expert})
+        if (((uintptr_t)ptr & 15u) != 0)
+            return fail(TFFN_ERR_INVALID, "tffn_op_swiglu_bs1_noalloc: every device pointer must be 16-byte aligned");
+    int prev_device = -1;
+    cudaError_t e = cudaGetDevice(&prev_device);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    struct RestoreDevice {
+        int d;
+        ~RestoreDevice() { cudaSetDevice(d); }
+    } restore{prev_device};
+    e = cudaSetDevice(device);
     if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
     Scratch* scratch = nullptr;
     int sms = 0;
@@ -115,11 +130,13 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
     launch_bs1_ffn(x, ly, stream, false);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+    // status read-back on the caller's stream: a plain cudaMemcpy would run on the legacy default
+    // stream and synchronise with every blocking stream of the process
+    int st = 0;
+    e = cudaMemcpyAsync(&st, &scratch->status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaMemcpyAsync: ") + cudaGetErrorString(e));
     e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
-    int st = 0;
-    e = cudaMemcpy(&st, &scratch->status, sizeof(int), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(e));
     if (st != 0) return fail(TFFN_ERR_DEVICE, "FFN kernel reported device status " + std::to_string(st));
     return TFFN_OK;
 }

@@ -51,9 +51,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait for the phase with the given parity to complete.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait for the phase with the given parity to complete: after `limit` polls the code is
+// recorded in the status word and the caller unwinds.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 1024) __nanosleep(64);
     }

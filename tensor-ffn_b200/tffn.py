@@ -86,7 +86,6 @@ _SIGS = {
     "tffn_session_profile": (_i, [_vp, _i]),
     "tffn_session_profile_read": (_i, [_vp, _vp, _vp, _i]),
     "tffn_profile_class_name": (_cp, [_i]),
-    "tffn_session_mega_trace": (_i, [_vp, _vp, _i]),
     "tffn_session_timeline": (_i, [_vp, _i, _vp, _i, _i, _vp, _i]),
     "tffn_session_status": (_i, [_vp]),
     "tffn_session_launch_count": (ctypes.c_uint64, [_vp]),
@@ -354,12 +353,6 @@ class Session:
         if trace_ctas > 0:
             return names, out[:n, 1:], tr
         return names, out[:n, 1:]
-
-    def mega_trace(self, max_ctas: int = 256) -> np.ndarray:
-        """one persistent-kernel batch-1 step with phase timestamps of layer 1: uint64 [ctas, 16]"""
-        out = np.zeros((max_ctas, 16), dtype=np.uint64)
-        n = _check(_L.tffn_session_mega_trace(self._h, out.ctypes.data, max_ctas))
-        return out[:n]
 
     def status(self) -> int:
         return _check(_L.tffn_session_status(self._h))

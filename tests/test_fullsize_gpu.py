@@ -126,10 +126,6 @@ def test_config0_against_reference_and_oracle(full_model, expert, tmp_path):
             "oracle_vs_reference_top1_raw": top1(orc, ref_logits)[0], "oracle_vs_reference_top1": top1(orc, ref_logits)[1],
         })
     print("PARITY", "expert" if expert else "base", report)
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", f"parity_config0_{'expert' if expert else 'base'}.json"), "w") as f:
-        import json
-        json.dump(report, f)
     assert report["ours_vs_oracle_logits"] <= TOL
     assert report["ours_vs_oracle_hidden_l2"] <= TOL
     assert report["ours_vs_oracle_hidden_max"] <= HIDDEN_MAX_TOL

@@ -14,9 +14,10 @@ CLI = os.path.join(ROOT, "tensor-ffn_b200", "tensor-ffn-inference")
 
 
 def test_library_exports_every_declared_symbol():
-    """every function include/tffn.h declares is exported by libtffn.so and bound by the Python mirror"""
+    """every function include/*.h declares is exported by libtffn.so and bound by the Python mirror"""
     import tffn
-    header = open(os.path.join(ROOT, "include", "tffn.h")).read()
+    inc = os.path.join(ROOT, "include")
+    header = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
     declared = sorted(set(re.findall(r"\b(tffn_[a-z0-9_]+)\s*\(", header)))
     assert len(declared) >= 40

@@ -61,7 +61,7 @@ def test_bs1_decode_path_teacher_forced(model_dirs, name, expert):
     m, e, s, o, cfg = _mk(model_dirs, name, expert)
     toks = synth.prompts(1, 40, 7, cfg["vocab_size"])[0]
     ref = o.forward(toks)["logits"]
-    for mode in (0, 1, 2, 3):  # 3 = one persistent kernel per token where the shape has an instantiation
+    for mode in (0, 1, 2):
         s.qwen_reset()
         s.set_launch_mode(mode)
         ours = []
@@ -236,3 +236,19 @@ def test_long_context_attention_splits(model_dirs):
     assert rel_err(got["3 splits"], ref) <= KERNEL_TOL
     assert rel_err(got["20 splits"], got["3 splits"]) <= KERNEL_TOL
     assert rel_err(got["batched"], got["3 splits"]) <= KERNEL_TOL
+
+
+def test_forward_without_logits_leaves_the_greedy_pick(model_dirs):
+    """tffn_forward(logits = NULL) followed by tffn_decode_step(tokens_in = NULL) feeds the greedy pick
+    of the last forwarded row, exactly as when the logits were asked for"""
+    import synth
+    m, e, s, o, cfg = _mk(model_dirs, "mini05", True)
+    toks = synth.prompts(1, 23, 17, cfg["vocab_size"])[0]
+    lg = s.qwen_forward(toks, want_logits=True)
+    a = [int(s.decode_step(None, n_seqs=1)[0][0]) for _ in range(3)]
+    assert lg.shape[0] == len(toks)
+    s.qwen_reset()
+    s.qwen_forward(toks, want_logits=False)
+    b = [int(s.decode_step(None, n_seqs=1)[0][0]) for _ in range(3)]
+    assert a == b
+    assert s.status() == 0

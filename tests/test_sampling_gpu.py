@@ -120,3 +120,60 @@ def test_cli_device_sampling_equals_host_sampling(model_dirs, tmp_path):
         assert r.returncode == 0, r.stderr
         outs.append(r.stdout.split("Generating:")[1])
     assert outs[0] == outs[1] and len(outs[0].strip()) > 0
+
+
+def test_sampling_survives_growth_of_the_token_staging_buffer(model_dirs):
+    """A prompt of more than ~700 tokens regrows the pinned int32 staging buffer after the pinned buffer
+    of the draws already exists; the draws' buffer must stay valid (it was once freed there) and the
+    sampled picks must keep following the host sampler."""
+    import synth
+    import tffn
+    d, ep, cfg = model_dirs["tiny"]
+    m = tffn.qwen_load(d)
+    e = tffn.checkpoint_load(ep, m, 0.1)
+    s = tffn.Session(m, e, max_batch=1, max_seq=1024)
+    T = 0.8
+    s.set_sampling(T, 42)
+    draws = canonical_draws(42, 16)
+    k = 0
+    nxt, lg = s.prefill([synth.prompts(1, 5, 90, cfg["vocab_size"])[0]], want_logits=True)
+    assert int(nxt[0]) == host_sample(lg[0], T, draws[k]); k += 1
+    nxt, lg = s.decode_step(nxt, want_logits=True)
+    assert int(nxt[0]) == host_sample(lg[0], T, draws[k]); k += 1
+    s.qwen_reset()
+    nxt, lg = s.prefill([synth.prompts(1, 800, 91, cfg["vocab_size"])[0]], want_logits=True)  # 800 * 6 ints > 4096
+    assert int(nxt[0]) == host_sample(lg[0], T, draws[k]); k += 1
+    for _ in range(4):
+        nxt, lg = s.decode_step(nxt, want_logits=True)
+        assert int(nxt[0]) == host_sample(lg[0], T, draws[k]); k += 1
+    assert s.status() == 0
+    s.free()
+
+
+def test_sampled_graph_is_rebuilt_when_the_draw_buffer_grows(model_dirs):
+    """decode_run with more than 1024 draws reallocates the device buffer of the draws; a decode graph
+    captured before (same key) holds the old address and has to be dropped, not replayed"""
+    import synth
+    import tffn
+    d, ep, cfg = model_dirs["tiny"]
+    m = tffn.qwen_load(d)
+    e = tffn.checkpoint_load(ep, m, 0.1)
+    prompts = [synth.prompts(1, 6 + (i % 3), 120 + i, cfg["vocab_size"])[0] for i in range(64)]
+    steps = 17  # 64 * 17 = 1088 draws > 1024
+
+    def run(stepwise):
+        s = tffn.Session(m, e, max_batch=64, max_seq=64)
+        s.set_launch_mode(2)
+        s.set_sampling(1.1, 11)
+        s.prefill(prompts)
+        first = np.asarray(s.decode_step(None, n_seqs=64)[0]).copy()  # captures the graph with the small buffer
+        if stepwise:
+            rest = np.array([s.decode_step(None, n_seqs=64)[0] for _ in range(steps)])
+        else:
+            rest = np.asarray(s.decode_run(64, steps)).copy()
+        assert s.status() == 0
+        s.free()
+        return first, rest
+
+    (fa, a), (fb, b) = run(False), run(True)
+    assert (fa == fb).all() and (a == b).all()

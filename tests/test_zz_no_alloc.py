@@ -40,7 +40,7 @@ def test_no_alloc_entry_matches_allocating_entry_twice_in_a_row():
         return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()
 
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, H, I, expert in ((1, 896, 4864, True), (2, 448, 640, False), (3, 896, 4864, True)):
+    for seed, H, I, expert in ((1, 896, 4864, True), (2, 448, 640, False), (3, 896, 4864, True), (4, 2048, 1184, True)):  # last: the largest hidden size the built-in scratch covers
         h, w, pb, pe = _case(seed, H, I)
         want = tffn.op_swiglu_bs1(h, w, pb, pe if expert else None, 0.1, 1e-6)
         d_h, d_w, d_pb, d_pe = dev(h), dev(w), dev(pb), dev(pe)
@@ -60,3 +60,18 @@ def test_no_alloc_entry_rejects_sizes_beyond_its_scratch():
     with pytest.raises(tffn.TffnError) as ei:
         tffn.op_swiglu_bs1_noalloc(buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), None, 4096, 8)
     assert ei.value.code == -6 and "2048" in ei.value.msg
+
+
+def test_no_alloc_entry_rejects_misaligned_pointers():
+    """the caller's pointers reach 16-byte vector loads and bulk copies unchanged: an address that is
+    not 16-byte aligned is refused on the host instead of faulting on the device"""
+    import torch
+    import tffn
+    buf = torch.zeros(1 << 16, dtype=torch.int16, device="cuda")
+    base = buf.data_ptr()
+    for bad in range(4):
+        ptrs = [base, base + 4096, base + 8192, base + 65536]
+        ptrs[bad] += 2
+        with pytest.raises(tffn.TffnError) as ei:
+            tffn.op_swiglu_bs1_noalloc(ptrs[0], ptrs[1], ptrs[2], ptrs[3], 256, 8)
+        assert ei.value.code == -1 and "aligned" in ei.value.msg
