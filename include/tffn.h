@@ -174,8 +174,8 @@ int tffn_op_swiglu_bs1(int device, const uint16_t* h_in, const uint16_t* norm_w,
  * inside a process whose device memory is owned and reserved by someone else, a deployment with a
  * memory budget fixed at start-up. All pointers are DEVICE pointers supplied by the caller, each
  * 16-byte aligned (TFFN_ERR_INVALID otherwise); h_io is updated in place. The kernel's scratch is a
- * fixed array inside the library (about 1.4 MB per GPU that loads it), so hidden <= 2048 and at most
- * 160 SMs; larger requests return TFFN_ERR_CAPACITY. The function calls no cudaMalloc / cudaFree; it
+ * fixed array inside the library (about 33 KB per GPU that loads it), so hidden <= 2048 (a multiple of
+ * 64); larger requests return TFFN_ERR_CAPACITY. The function calls no cudaMalloc / cudaFree; it
  * clears the part of the scratch that must start at zero, launches on `cuda_stream`, and BLOCKS until
  * that stream has finished the call (it synchronises only that stream, nothing device-wide), so it
  * must not be called while the stream is being captured. Calls that could overlap on one GPU share

@@ -567,6 +567,10 @@ int attn_prepare() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_decode<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_prefill<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<64>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_prefill<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::SMEM);
+    if (e == cudaSuccess) e = prefer_max_shared(k_attn_decode<64>);
+    if (e == cudaSuccess) e = prefer_max_shared(k_attn_decode<128>);
+    if (e == cudaSuccess) e = prefer_max_shared(k_attn_prefill<64>);
+    if (e == cudaSuccess) e = prefer_max_shared(k_attn_prefill<128>);
     return (int)e;
 }
 

@@ -1,4 +1,5 @@
 #include "engine.h"
+#include "launch.h"
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -304,11 +305,13 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
 
     cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
     cuda_check((cudaError_t)attn_prepare(), "attn_prepare", __FILE__, __LINE__);
+    cuda_check((cudaError_t)rows_prepare(), "rows_prepare", __FILE__, __LINE__);
+    cuda_check(prefer_max_shared(k_decode_advance), "carveout", __FILE__, __LINE__);
     if (m->bs1_ok) cuda_check((cudaError_t)bs1_prepare((int)H, true), "bs1_prepare", __FILE__, __LINE__);
-    bs1_h_.alloc(H * 2);
+    bs1_h_.alloc(2 * H * 2);  // the residual stream alternates between two buffers from layer to layer
+    bs1_acc_.alloc(2 * bs1_acc_words((int)H) * 8);
     bs1_q_.alloc(nh * hd * 4);
     bs1_ctx_.alloc(nh * hd * 2);
-    bs1_part_.alloc(bs1_ffn_part_floats((int)H, m->num_sms) * 4);
     bs1_tickets_.alloc(256 * 4);
     bs1_lm_val_.alloc((size_t)m->num_sms * 2 * 4);
     bs1_lm_idx_.alloc((size_t)m->num_sms * 2 * 4);
@@ -757,7 +760,6 @@ Bs1Ctx Session::bs1_ctx(bool want_logits) const {
     x.token = dec_tokens_.as<int>();
     x.seq_len = seq_len_dev_.as<int>();
     x.slot = 0;
-    x.ffn_part = bs1_part_.as<float>();
     x.tickets = bs1_tickets_.as<int>();
     x.lm_val = bs1_lm_val_.as<float>();
     x.lm_idx = bs1_lm_idx_.as<int>();
@@ -771,8 +773,16 @@ Bs1Ctx Session::bs1_ctx(bool want_logits) const {
 
 void Session::launch_bs1_step(bool want_logits, bool pdl) {
     const Config& c = m_->cfg;
-    const Bs1Ctx x = bs1_ctx(want_logits);
+    Bs1Ctx x = bs1_ctx(want_logits);
+    const size_t acc_words = bs1_acc_words(c.hidden_size);
+    auto hbuf = [&](int k) { return bs1_h_.as<bf16>() + (size_t)(k & 1) * c.hidden_size; };
+    auto accbuf = [&](int k) { return bs1_acc_.as<long long>() + (size_t)(k & 1) * acc_words; };
     for (int l = 0; l < c.num_layers; ++l) {
+        // layer l reads the residual stream of layer l - 1 plus the sums its FFN left, and owns the other buffer
+        x.h_in = hbuf(l);
+        x.h = hbuf(l + 1);
+        x.acc_in = l > 0 ? accbuf(l - 1) : nullptr;
+        x.acc_out = accbuf(l);
         const LayerWeights& lw = m_->layers[l];
         Bs1Layer ly;
         ly.wqkv = lw.wqkv.as<bf16>();
@@ -782,6 +792,7 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
         ly.ffn_norm = lw.ffn_norm.as<bf16>();
         ly.ffn_base = lw.ffn.packed.as<bf16>();
         ly.ffn_expert = e_ ? e_->layers[l].packed.as<bf16>() : nullptr;
+        x.tl = tl_next(KC_BS1_QKV);
         prof_begin(KC_BS1_QKV);
         // the first kernel of a step is a full dependency: what earlier steps wrote (sequence length,
         // older cache rows) is then stable for every kernel of this step, also ahead of its grid wait
@@ -789,15 +800,24 @@ void Session::launch_bs1_step(bool want_logits, bool pdl) {
         prof_end();
         prof_begin(KC_ATTENTION);
         launch_attention(x.q, kv_, l, identity_.as<int>(), seq_len_dev_.as<int>(), x.ctx, 1, c.num_heads, max_seq_, attn_ws(),
-                         m_->num_sms, status_.as<int>(), stream_, pdl, true);
+                         m_->num_sms, status_.as<int>(), stream_, pdl, true, tl_next(KC_ATTENTION));
         prof_end();
+        x.tl = tl_next(KC_BS1_OPROJ);
         prof_begin(KC_BS1_OPROJ);
         launch_bs1_oproj(x, ly, stream_, pdl);
         prof_end();
+        x.tl = tl_next(KC_BS1_FFN);
+        // per-CTA phase stamps of this launch if the timeline call asked for it (16 u64 per CTA)
+        x.trace = (tl_on_ && (int)tl_cls_.size() - 1 == tl_trace_launch_) ? tl_trace_buf_.as<unsigned long long>() : nullptr;
         prof_begin(KC_BS1_FFN);
         launch_bs1_ffn(x, ly, stream_, pdl);
         prof_end();
     }
+    x.h_in = hbuf(c.num_layers);
+    x.h = nullptr;
+    x.acc_in = accbuf(c.num_layers - 1);
+    x.acc_out = nullptr;
+    x.tl = tl_next(KC_BS1_LMHEAD);
     prof_begin(KC_BS1_LMHEAD);
     launch_bs1_lmhead(x, m_->final_norm.as<bf16>(), m_->lm_head, stream_, pdl);
     prof_end();
@@ -845,7 +865,6 @@ int Session::timeline(int n_seqs, uint64_t* out, int max_launches, int trace_lau
         TFFN_CUDA(cudaStreamSynchronize(0));
     }
     tl_trace_launch_ = want_trace ? trace_launch : -1;
-    if (n_seqs == 1 && use_bs1_ && m_->bs1_ok) throw Error(kErrUnsupported, "the timeline covers the batched path only");
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     drop_graphs();
     tl_buf_.alloc((size_t)max_launches * 48);

@@ -156,7 +156,7 @@ private:
     size_t h_pinned_cap_ = 0;
 
     // batch-1 path
-    DeviceBuffer bs1_h_, bs1_q_, bs1_ctx_, bs1_part_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
+    DeviceBuffer bs1_h_, bs1_acc_, bs1_q_, bs1_ctx_, bs1_tickets_, bs1_lm_val_, bs1_lm_idx_;
     cudaGraphExec_t bs1_graph_ = nullptr;
     bool bs1_graph_logits_ = false;
     // batched decode steps captured per (sequences, attention splits)

@@ -19,6 +19,7 @@
 // k_add_fp32_to_bf16 inference/src/model/qwen.cu:282-285).
 #include "kernels.h"
 #include "ptx.cuh"
+#include "launch.h"
 #include <cstdio>
 #include <cstring>
 #include <functional>
@@ -743,6 +744,8 @@ int gemm_prepare() {
     e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem); \
     if (e != cudaSuccess) return (int)e;                                                                             \
     e = cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);                     \
+    if (e != cudaSuccess) return (int)e;                                                                             \
+    e = prefer_max_shared(k_gemm_tc<BN>);                                                                            \
     if (e != cudaSuccess) return (int)e;
     TFFN_PREP(16) TFFN_PREP(32) TFFN_PREP(64) TFFN_PREP(128) TFFN_PREP(256)
 #undef TFFN_PREP

@@ -86,6 +86,8 @@ int launch_gemm(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream,
 // ------------------------------------------------------------------ row kernels of the batched path
 // (pdl: launch with programmatic dependent launch; every kernel here waits before reading its inputs)
 // tl: optional 6 u64 of the step timeline (see tl_mark): min / max over the CTAs of entry, grid-wait return, exit
+// the row kernels share the step's shared-memory carveout with the large kernels (see prefer_max_shared)
+int rows_prepare();
 void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s,
                   bool pdl = false, unsigned long long* tl = nullptr);
 void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float eps, const int* row_idx, cudaStream_t s,
@@ -141,14 +143,19 @@ struct Bs1Ctx {
     float eps, expert_scale;
     const float *rope_cos, *rope_sin;
     int max_pos;
-    bf16* h;          // [H] residual stream
+    bf16* h;          // [H] residual stream of this layer: published by the q|k|v kernel, updated by o_proj, read by the FFN
+    const bf16* h_in; // [H] residual stream the q|k|v kernel (or the LM head) starts from: the previous layer's `h`
+    // The FFN leaves its output as fixed-point sums (see bs1_acc_words): acc_out is where this layer's FFN
+    // adds, acc_in what the previous layer's FFN left (null: nothing to fold in). The consumer of the
+    // residual stream forms h = bf16(h_in + acc_in) itself; the q|k|v kernel also clears acc_out.
+    const long long* acc_in;
+    long long* acc_out;
     float* q;         // [nh*hd]
     bf16* ctx;        // [nh*hd]
     int* token;       // device: current input token (slot 0)
     int* seq_len;     // device: cached tokens of the slot = position of the new token
     int slot;
-    float* ffn_part;  // [ffn_grid][H] per-CTA partial sums + group partials
-    int* tickets;     // zeroed tickets
+    int* tickets;     // zeroed tickets (LM head)
     float* lm_val;    // [lm_grid] candidates
     int* lm_idx;
     float* logits;    // optional fp32 [V] or null
@@ -157,12 +164,19 @@ struct Bs1Ctx {
     int* status;
     int num_sms;
     // optional profiling aid for k_bs1_ffn: 16 u64 per CTA, globaltimer ns at 0 start, 1 rmsnorm done,
-    // 2 first record arrived, 3 last record consumed, 4 CTA partial written, 5 group ticket taken,
-    // 6 group fold done (last CTA of a group only), 7 residual updated (last group only)
+    // 2 first record arrived, 3 last record consumed, 4 this CTA's sums added to acc_out
     unsigned long long* trace;
+    unsigned long long* tl;  // optional 6 u64 of the step timeline for this launch (see tl_mark)
 };
 bool bs1_supported(int H, int I, int hd, int nh, int nkv);
-size_t bs1_ffn_part_floats(int H, int num_sms);
+// 64-bit words of one FFN accumulator: a few replicas (CTAs spread over them to thin out same-address
+// atomics) of H fixed-point sums, value * 2^32 as int64. Integer addition is associative, so the sum of
+// the CTAs' contributions does not depend on the order in which the atomics land: results stay
+// bit-reproducible although no CTA waits for another.
+size_t bs1_acc_words(int H);
+// h[i] = bf16(h[i] + acc[i]) and acc cleared: closes a stand-alone launch_bs1_ffn (inside a decode step
+// the next kernel folds the sums in instead)
+void launch_bs1_ffn_finalize(bf16* h, long long* acc, int H, cudaStream_t s);
 int bs1_prepare(int H, bool expert);  // dynamic shared memory opt-in for this shape (outside stream capture)
 void launch_bs1_qkv(const Bs1Ctx& c, const Bs1Layer& ly, const bf16* embed, KvView kv, int layer, bool first, cudaStream_t s,
                     bool pdl);

@@ -21,4 +21,14 @@ inline cudaError_t launch_k(Kern k, dim3 grid, dim3 block, size_t smem, cudaStre
     return cudaLaunchKernelEx(&cfg, k, args...);
 }
 
+// Ask for the largest shared-memory carveout for a kernel, whatever it uses itself. The kernels of a
+// decode step are resident together (dependent launches let the next ones start early and fetch their
+// weights). An SM cannot change its L1 / shared-memory split while CTAs are resident on it: if the small
+// kernels ran with a small carveout, a CTA that needs 200 KB of shared memory could only start once the
+// SM had drained, i.e. without its head start. With one common carveout they co-reside.
+template <typename Kern>
+inline cudaError_t prefer_max_shared(Kern k) {
+    return cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
 }  // namespace tffn

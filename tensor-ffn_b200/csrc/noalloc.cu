@@ -5,17 +5,17 @@
 // trigger an implicit device synchronisation (cudaMalloc and cudaFree can do both), a plugin
 // loaded into a process whose memory pool is owned and fully reserved by someone else, or a
 // caller running under a strict memory budget fixed at start-up. Such callers hand in device
-// pointers for inputs and outputs that they obtained earlier; the kernel's scratch (per-CTA
-// partial sums, group sums and reduction tickets) lives in a fixed array inside this library's
-// device image instead of a buffer from cudaMalloc.
+// pointers for inputs and outputs that they obtained earlier; the kernel's scratch (the fixed-point
+// accumulator that collects every CTA's share of the FFN output, and the status word) lives in a
+// fixed array inside this library's device image instead of a buffer from cudaMalloc.
 //
 // Consequences the caller has to know:
-//  * Every GPU that loads the library holds the array (about 1.4 MB) until the process exits.
-//  * The size is fixed: hidden <= 2048 and a GPU with at most 160 SMs; larger requests are refused.
-//  * All calls on one device share the array and it keeps the previous call's contents. The entry
-//    point clears the tickets and the status word before every launch; the partial sums are fully
-//    overwritten by the kernel before they are read. Two calls whose kernels overlap on the GPU
-//    (different streams, or different host threads) race on the scratch: serialise them.
+//  * Every GPU that loads the library holds the array (about 33 KB) until the process exits.
+//  * The size is fixed: hidden <= 2048 (a multiple of 64); larger requests are refused.
+//  * All calls on one device share the array and it keeps the previous call's contents. The sums
+//    must start at zero: the entry point clears them and the status word before every launch. Two
+//    calls whose kernels overlap on the GPU (different streams, or different host threads) would add
+//    into the same sums: serialise them.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
 //    opts the kernel into its shared-memory size.
 //  * The call blocks until `cuda_stream` has finished it (it synchronises that stream only, never
@@ -34,14 +34,12 @@ void set_last_error(const std::string& msg);  // c_api.cpp
 namespace {
 
 constexpr int kMaxHidden = 2048;
-constexpr int kMaxCtas = 160;
-constexpr int kGroups = (kMaxCtas + 15) / 16 + 1;
+constexpr int kMaxAccWords = 2 * kMaxHidden;  // >= bs1_acc_words(kMaxHidden), checked at set-up
 constexpr int kMaxDevices = 64;
 
 struct Scratch {
-    float part[(size_t)(kMaxCtas + kGroups) * kMaxHidden];  // per-CTA partial sums, then per-group sums
-    int tickets[64];                                       // reduction tickets, zero before each launch
-    int status;                                            // device status word of the launch
+    long long acc[kMaxAccWords];  // fixed-point sums of the FFN output, zero before each launch
+    int status;                   // device status word of the launch
     int pad[63];
 };
 
@@ -65,8 +63,8 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
                                           void* cuda_stream) {
     using namespace tffn;
     if (!h_io || !norm_w || !packed_base || I < 1) return fail(TFFN_ERR_INVALID, "NULL pointer or empty intermediate size");
-    if (H < 8 || H % 8 != 0 || H > kMaxHidden)
-        return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: hidden must be a multiple of 8 and at most " +
+    if (H < 64 || H % 64 != 0 || H > kMaxHidden)
+        return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: hidden must be a multiple of 64 and at most " +
                                            std::to_string(kMaxHidden) + " (the built-in scratch is sized for that)");
     if (device < 0 || device >= kMaxDevices) return fail(TFFN_ERR_INVALID, "device index out of range");
     for (const void* ptr : {(const void*)h_io, norm_w, packed_base, packed_expert})
@@ -92,6 +90,8 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
             int n = 0;
             e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
             if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+            if (bs1_acc_words(kMaxHidden) > (size_t)kMaxAccWords)
+                return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: built-in scratch smaller than the kernel's accumulator");
             const int rc = bs1_prepare(kMaxHidden, true);
             if (rc != 0) return fail(TFFN_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString((cudaError_t)rc));
             g_dev_sms[device] = n;
@@ -100,16 +100,13 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
         scratch = g_dev_ptr[device];
         sms = g_dev_sms[device];
     }
-    if (sms > kMaxCtas)
-        return fail(TFFN_ERR_CAPACITY, "tffn_op_swiglu_bs1_noalloc: this GPU has more SMs than the built-in scratch covers (" +
-                                           std::to_string(kMaxCtas) + ")");
     {
         const int rc = bs1_prepare(H, true);  // shared-memory opt-in for this hidden size (no allocation)
         if (rc != 0) return fail(TFFN_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString((cudaError_t)rc));
     }
     cudaStream_t stream = (cudaStream_t)cuda_stream;
-    // the array keeps the last call's contents: tickets and status must start at zero
-    e = cudaMemsetAsync(scratch->tickets, 0, sizeof(scratch->tickets) + sizeof(int), stream);
+    // the array keeps the last call's contents: the sums and the status word must start at zero
+    e = cudaMemsetAsync(scratch, 0, sizeof(scratch->acc) + sizeof(int), stream);
     if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
     Bs1Ctx x;
     memset(&x, 0, sizeof x);
@@ -118,8 +115,7 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
     x.eps = eps;
     x.expert_scale = expert_scale;
     x.h = (bf16*)h_io;
-    x.ffn_part = scratch->part;
-    x.tickets = scratch->tickets;
+    x.acc_out = scratch->acc;
     x.status = &scratch->status;
     x.num_sms = sms;
     Bs1Layer ly;
@@ -128,6 +124,7 @@ extern "C" int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* no
     ly.ffn_base = (const bf16*)packed_base;
     ly.ffn_expert = (const bf16*)packed_expert;
     launch_bs1_ffn(x, ly, stream, false);
+    launch_bs1_ffn_finalize(x.h, x.acc_out, H, stream);  // h_io = bf16(h_io + sums)
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TFFN_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
     // status read-back on the caller's stream: a plain cudaMemcpy would run on the legacy default

@@ -290,6 +290,15 @@ __global__ void k_wait_selftest(int* status) {
 
 }  // namespace
 
+int rows_prepare() {
+    cudaError_t e = prefer_max_shared(k_embed_rows);
+    if (e == cudaSuccess) e = prefer_max_shared(k_rmsnorm_rows);
+    if (e == cudaSuccess) e = prefer_max_shared(k_argmax_rows);
+    if (e == cudaSuccess) e = prefer_max_shared(k_argmax_tiles);
+    if (e == cudaSuccess) e = prefer_max_shared(k_sample_rows);
+    return (int)e;
+}
+
 void launch_embed(const int* tokens, const bf16* table, bf16* h, int T, int H, int V, int* status, cudaStream_t s, bool pdl,
                   unsigned long long* tl) {
     launch_k(k_embed_rows, dim3(T), dim3(128), 0, s, pdl, tokens, table, h, T, H, V, status, tl);

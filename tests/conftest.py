@@ -39,6 +39,9 @@ SHAPES = {
     # the 0.5B head geometry (7 query heads per kv head, hidden not a multiple of 128) at small size
     "mini05": (dict(hidden_size=448, num_hidden_layers=3, num_attention_heads=7, num_key_value_heads=1,
                     intermediate_size=608, vocab_size=1000, tie_word_embeddings=True), True),
+    # the same head geometry with an intermediate size that is a multiple of 256
+    "mini_s": (dict(hidden_size=448, num_hidden_layers=3, num_attention_heads=7, num_key_value_heads=1,
+                    intermediate_size=768, vocab_size=1000, tie_word_embeddings=True), True),
 }
 
 
