@@ -53,19 +53,26 @@ NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 17643264 / 17432576
 NCU_LMHEAD_LOGIT_WRITE_FRACTION = 26198016 / 38895616
 
 
-def model_dir(shape: str) -> str:
-    base = "/dev/shm" if os.path.isdir("/dev/shm") and shutil.disk_usage("/dev/shm").free > (8 << 30) else "/tmp"
-    return os.path.join(base, f"tffn_bench_{shape}")
+def model_dir(shape: str, variant: str = "") -> str:
+    name = f"tffn_bench_{shape}" + (f"_{variant}" if variant else "")
+    for base in ("/dev/shm", "/tmp"):  # an existing copy wins; else the first place with room
+        if os.path.exists(os.path.join(base, name, ".complete")):
+            return os.path.join(base, name)
+    base = "/dev/shm" if os.path.isdir("/dev/shm") and shutil.disk_usage("/dev/shm").free > (40 << 30) else "/tmp"
+    return os.path.join(base, name)
 
 
-def ensure_model(shape: str) -> tuple[str, str, dict]:
+def ensure_model(shape: str, variant: str = "") -> tuple[str, str, dict]:
+    """Seeded synthetic model dir + expert .bin of the shape, written once per machine. variant "peaked":
+    vocabulary rows with log-normal norms (synth.write_model head_norm_sigma), whose logits have a clear
+    winner; used by the parity tests that assert raw top-1 agreement."""
     import synth
-    d = model_dir(shape)
+    d = model_dir(shape, variant)
     ep = os.path.join(d, "expert.bin")
     marker = os.path.join(d, ".complete")
     if not os.path.exists(marker):
         shutil.rmtree(d, ignore_errors=True)
-        cfg = synth.write_model(d, shape, seed=1234)
+        cfg = synth.write_model(d, shape, seed=1234, head_norm_sigma=1.5 if variant == "peaked" else 0.0)
         synth.write_expert(ep, cfg, seed=4321)
         with open(marker, "w") as f:
             f.write("ok")

@@ -81,7 +81,10 @@ int tffn_tokenizer_special(const tffn_tokenizer* t, uint32_t* eos, uint32_t* bos
 /* ---- model / expert -------------------------------------------------------------------- */
 /* qwen_load minus the KV cache and scratch (inference/src/model/qwen.cu:80-132): reads
  * config.json and every *.safetensors of the directory, uploads the weights to `device`,
- * builds the layouts the kernels stream. tp_rank/tp_size must be 0/1. */
+ * builds the layouts the kernels stream. tp_rank / tp_size = 0 / 1 loads the whole model; otherwise
+ * this process is one rank of a tensor-parallel group and loads only its slices (tffn_tp_partition):
+ * query / kv heads, the intermediate dimension of the FFN, rows of the LM head. Such a model needs
+ * tffn_session_create_tp. */
 int tffn_model_load(const char* model_dir, int device, int tp_rank, int tp_size, tffn_model** out);
 void tffn_model_free(tffn_model* m); /* qwen_free (qwen.cu:176-209) */
 int tffn_model_config(const tffn_model* m, tffn_config* out);
@@ -110,6 +113,29 @@ void tffn_expert_free(tffn_expert* e); /* expert_free (expert.cu:33-42) */
 int tffn_session_create(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
                         tffn_session** out);
 void tffn_session_free(tffn_session* s);
+
+/* ---- tensor parallelism (the reference is single-GPU: no counterpart) -------------------- */
+/* One process per GPU. Rank 0 makes an id (tffn_tp_unique_id, 128 bytes) and hands it to the other
+ * ranks by any means; every rank then calls tffn_tp_create (collective: returns when all tp_size
+ * ranks have joined), loads its slice with tffn_model_load(dir, device, tp_rank, tp_size) /
+ * tffn_expert_load, and creates its session with tffn_session_create_tp. All ranks then make the
+ * same tffn_prefill / tffn_decode_step / tffn_decode_run calls with the same arguments; each returns
+ * the same tokens (and full logits) on every rank. Inside a step the ranks' partial sums of o_proj
+ * and of the down projections (base + scale * expert, summed locally first) are all-reduced in
+ * fp32 with NCCL over NVLink before the one bf16 rounding of the residual add, and the greedy pick
+ * exchanges one (max, index) pair per sequence and rank. Sampling and tffn_expert_forward are not
+ * available on a tensor-parallel model. NCCL (libnccl.so.2) is opened at run time. */
+typedef struct tffn_tp tffn_tp;
+int tffn_tp_unique_id(uint8_t* id128);
+int tffn_tp_create(const uint8_t* id128, int tp_rank, int tp_size, int device, tffn_tp** out);
+void tffn_tp_free(tffn_tp* tp);
+/* Host-only: what rank tp_rank of tp_size owns of a model with this config (only the dimensions of cfg
+ * are read): out8 = {first query head, query heads, first kv head, kv heads, first intermediate row,
+ * intermediate rows, first LM-head row, LM-head rows}. With more ranks than kv heads, tp_size / kv_heads
+ * ranks share a kv head and split its query heads (7 heads over 2 ranks: 3 + 4). */
+int tffn_tp_partition(const tffn_config* cfg, int tp_rank, int tp_size, int32_t* out8);
+int tffn_session_create_tp(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
+                           tffn_tp* tp, tffn_session** out);
 /* qwen_reset (qwen.cu:174) for one slot, or for all with slot = -1: frees the slot's pages. */
 int tffn_session_reset(tffn_session* s, int slot);
 int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */

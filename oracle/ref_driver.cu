@@ -9,11 +9,13 @@
 //
 // usage: ref_driver --model DIR [--expert BIN --expert-scale F] --max-seq N
 //                   --tokens FILE.i32 --prompt-len P --new N --out PREFIX
-//                   [--teacher] [--all-logits] [--hidden] [--time REPS]
-// FILE.i32 holds P prompt ids, then (with --teacher) N ids to feed instead of the greedy pick.
-// writes PREFIX.logits.f32  [(P or 1) + N, V]   rows: prompt rows (all or last), then one per decode step
-//        PREFIX.tokens.i32  [1 + N]             greedy pick after the prompt and after every step
-//        PREFIX.hidden.bf16 [L, P, H]           residual stream after each layer for the prompt
+//                   [--teacher] [--all-logits] [--hidden] [--time REPS] [--seqs K]
+// FILE.i32 holds P prompt ids, then (with --teacher) N ids to feed instead of the greedy pick; with
+// --seqs K it holds K such records back to back and the sequences run one after the other with
+// qwen_reset in between (the reference has no batching), their outputs concatenated.
+// writes PREFIX.logits.f32  [K][(P or 1) + N, V] rows: prompt rows (all or last), then one per decode step
+//        PREFIX.tokens.i32  [K][1 + N]           greedy pick after the prompt and after every step
+//        PREFIX.hidden.bf16 [L, P, H]            residual stream after each layer for the first prompt
 //        PREFIX.time.json                       decode timing of the reference's own loop
 #include "backend/cuda_ops.h"
 #include "backend/memory.h"
@@ -60,6 +62,7 @@ int main(int argc, char** argv) {
     int P = atoi(flag(argc, argv, "--prompt-len", "0"));
     int N = atoi(flag(argc, argv, "--new", "0"));
     int reps = atoi(flag(argc, argv, "--time", "0"));
+    int nseq = atoi(flag(argc, argv, "--seqs", "1"));
     bool teacher = sw(argc, argv, "--teacher"), all = sw(argc, argv, "--all-logits"), hid = sw(argc, argv, "--hidden");
     if (dir.empty() || tokf.empty() || out.empty() || P <= 0) {
         fprintf(stderr, "ref_driver: --model --tokens --prompt-len --out are required\n");
@@ -76,7 +79,8 @@ int main(int argc, char** argv) {
         if (fread(toks.data(), 4, n, f) != (size_t)n) return 2;
         fclose(f);
     }
-    if ((int)toks.size() < P + (teacher ? N : 0)) { fprintf(stderr, "token file too short\n"); return 2; }
+    const int rec = P + (teacher ? N : 0);
+    if (nseq < 1 || (int)toks.size() < nseq * rec) { fprintf(stderr, "token file too short\n"); return 2; }
 
     cublasHandle_t cublas;
     CUBLAS_CHECK(cublasCreate(&cublas));
@@ -114,30 +118,35 @@ int main(int argc, char** argv) {
         dump(out + ".hidden.bf16", hbuf.data(), hbuf.size() * 2);
     }
 
-    // prompt + decode, as main.cpp:159-197 (no EOS break, no text)
+    // prompt + decode, as main.cpp:159-197 (no EOS break, no text), one sequence after the other
     std::vector<float> logits;
     std::vector<int32_t> picks;
-    model::qwen_reset(mdl);
-    backend::host_to_device(d_tokens, toks.data(), (size_t)P * 4);
-    model::qwen_forward(mdl, cublas, d_tokens, P, ep, d_logits);
-    if (all) {
-        logits.resize((size_t)P * V);
-        backend::device_to_host(logits.data(), d_logits, (size_t)P * V * 4);
-        memcpy(row.data(), &logits[(size_t)(P - 1) * V], (size_t)V * 4);
-    } else {
-        backend::device_to_host(row.data(), d_logits + (size_t)(P - 1) * V, (size_t)V * 4);
-        logits.assign(row.begin(), row.end());
-    }
-    int next = greedy(row.data(), V);
-    picks.push_back(next);
-    for (int s = 0; s < N; ++s) {
-        int32_t one = teacher ? toks[P + s] : next;
-        backend::host_to_device(d_tokens, &one, 4);
-        model::qwen_forward(mdl, cublas, d_tokens, 1, ep, d_logits);
-        backend::device_to_host(row.data(), d_logits, (size_t)V * 4);
-        logits.insert(logits.end(), row.begin(), row.end());
+    int next = 0;
+    for (int q = 0; q < nseq; ++q) {
+        const int32_t* tk = toks.data() + (size_t)q * rec;
+        model::qwen_reset(mdl);
+        backend::host_to_device(d_tokens, tk, (size_t)P * 4);
+        model::qwen_forward(mdl, cublas, d_tokens, P, ep, d_logits);
+        if (all) {
+            const size_t at = logits.size();
+            logits.resize(at + (size_t)P * V);
+            backend::device_to_host(&logits[at], d_logits, (size_t)P * V * 4);
+            memcpy(row.data(), &logits[at + (size_t)(P - 1) * V], (size_t)V * 4);
+        } else {
+            backend::device_to_host(row.data(), d_logits + (size_t)(P - 1) * V, (size_t)V * 4);
+            logits.insert(logits.end(), row.begin(), row.end());
+        }
         next = greedy(row.data(), V);
         picks.push_back(next);
+        for (int s = 0; s < N; ++s) {
+            int32_t one = teacher ? tk[P + s] : next;
+            backend::host_to_device(d_tokens, &one, 4);
+            model::qwen_forward(mdl, cublas, d_tokens, 1, ep, d_logits);
+            backend::device_to_host(row.data(), d_logits, (size_t)V * 4);
+            logits.insert(logits.end(), row.begin(), row.end());
+            next = greedy(row.data(), V);
+            picks.push_back(next);
+        }
     }
     dump(out + ".logits.f32", logits.data(), logits.size() * 4);
     dump(out + ".tokens.i32", picks.data(), picks.size() * 4);

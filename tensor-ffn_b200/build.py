@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtffn.so")
 CLI = os.path.join(HERE, "tensor-ffn-inference")
-LIB_SOURCES = ["host_io.cpp", "c_api.cpp", "engine.cu", "gemm_tc.cu", "rows.cu", "attn.cu", "decode_bs1.cu", "noalloc.cu"]
+LIB_SOURCES = ["host_io.cpp", "c_api.cpp", "tp_comm.cpp", "engine.cu", "gemm_tc.cu", "rows.cu", "attn.cu", "decode_bs1.cu", "noalloc.cu"]
 CLI_SOURCES = ["cli_main.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr"]
@@ -52,7 +52,7 @@ def build(verbose: bool = False, ptxas_verbose: bool = False) -> str:
         objs = list(ex.map(lambda s: _compile(s, verbose, extra), lib_sources))
         cli_objs = list(ex.map(lambda s: _compile(s, verbose, extra), CLI_SOURCES))
     if _newer(LIB, objs):
-        subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
+        subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ldl"])
     if _newer(CLI, cli_objs + [LIB]):
         subprocess.check_call(["nvcc", "-o", CLI] + cli_objs + ["-L" + HERE, "-ltffn", "-Xlinker", "-rpath,$ORIGIN",
                                                               "-gencode", "arch=compute_100a,code=sm_100a"])

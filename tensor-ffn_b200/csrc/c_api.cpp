@@ -13,6 +13,7 @@ struct tffn_model { Model* m; };
 struct tffn_expert { Expert* e; };
 struct tffn_session { Session* s; };
 struct tffn_tokenizer { Tokenizer t; };
+struct tffn_tp { TpComm* c; };
 
 static thread_local std::string g_last_error;
 namespace tffn {
@@ -174,8 +175,8 @@ int tffn_model_config(const tffn_model* m, tffn_config* out) {
 uint64_t tffn_model_weight_bytes(const tffn_model* m, int with_expert) {
     if (!m) return 0;
     const Config& c = m->m->cfg;
-    uint64_t b = m->m->weight_bytes_base;
-    if (with_expert) b += (uint64_t)c.num_layers * 3 * c.hidden_size * c.intermediate_size * 2;
+    uint64_t b = m->m->weight_bytes_base;  // this rank's share under tensor parallelism
+    if (with_expert) b += (uint64_t)c.num_layers * 3 * c.hidden_size * m->m->I * 2;
     return b;
 }
 
@@ -207,10 +208,44 @@ void tffn_expert_free(tffn_expert* e) {
 
 int tffn_session_create(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
                         tffn_session** out) {
+    return tffn_session_create_tp(m, expert, max_batch, max_seq, cuda_stream, nullptr, out);
+}
+int tffn_session_create_tp(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
+                           tffn_tp* tp, tffn_session** out) {
     return guard([&] {
         need(m && out, "NULL argument");
-        std::unique_ptr<Session> s(new Session(m->m, expert ? expert->e : nullptr, max_batch, max_seq, (cudaStream_t)cuda_stream));
+        std::unique_ptr<Session> s(new Session(m->m, expert ? expert->e : nullptr, max_batch, max_seq, (cudaStream_t)cuda_stream,
+                                               tp ? tp->c : nullptr));
         *out = new tffn_session{s.release()};
+    });
+}
+int tffn_tp_unique_id(uint8_t* id128) {
+    return guard([&] {
+        need(id128, "NULL argument");
+        tp_comm_unique_id(id128);
+    });
+}
+int tffn_tp_create(const uint8_t* id128, int tp_rank, int tp_size, int device, tffn_tp** out) {
+    return guard([&] {
+        need(id128 && out, "NULL argument");
+        *out = new tffn_tp{tp_comm_create(id128, tp_rank, tp_size, device)};
+    });
+}
+void tffn_tp_free(tffn_tp* tp) {
+    if (!tp) return;
+    tp_comm_free(tp->c);
+    delete tp;
+}
+int tffn_tp_partition(const tffn_config* cfg, int tp_rank, int tp_size, int32_t* out8) {
+    return guard([&] {
+        need(cfg && out8, "NULL argument");
+        Config c;
+        c.hidden_size = cfg->hidden_size; c.intermediate_size = cfg->intermediate_size; c.num_layers = cfg->num_layers;
+        c.num_heads = cfg->num_heads; c.num_kv_heads = cfg->num_kv_heads; c.head_dim = cfg->head_dim;
+        c.vocab_size = cfg->vocab_size;
+        const TpPartition p = tp_partition(c, tp_rank, tp_size);
+        const int32_t v[8] = {p.q_head0, p.n_q_heads, p.kv_head0, p.n_kv_heads, p.i0, p.n_i, p.v0, p.n_v};
+        memcpy(out8, v, sizeof v);
     });
 }
 void tffn_session_free(tffn_session* s) {

@@ -66,6 +66,7 @@ __global__ void k_copy_rows_bf16(const bf16* __restrict__ src, bf16* __restrict_
 void Expert::forward_layers(const void* d_x, float* d_out, int T, cudaStream_t stream) const {
     if (!d_x || !d_out || T < 1) throw Error(kErrInvalid, "bad expert_forward arguments");
     const Config& c = model->cfg;
+    if (model->tp.tp_size != 1) throw Error(kErrUnsupported, "expert_forward is not split across tensor-parallel ranks");
     const int H = c.hidden_size, I = c.intermediate_size;
     TFFN_CUDA(cudaSetDevice(model->device));
     cuda_check((cudaError_t)gemm_prepare(), "gemm_prepare", __FILE__, __LINE__);
@@ -113,8 +114,12 @@ void Expert::forward_layers(const void* d_x, float* d_out, int T, cudaStream_t s
 }
 
 // ------------------------------------------------------------------------------------------ Model
+// column slice [c0, c0 + nc) of a row-major [rows, cols] bf16 host matrix -> dense [rows, nc] on the device
+static void upload_cols(void* dst, const uint16_t* src, size_t rows, size_t cols, size_t c0, size_t nc) {
+    TFFN_CUDA(cudaMemcpy2D(dst, nc * 2, src + c0, cols * 2, nc * 2, rows, cudaMemcpyHostToDevice));
+}
+
 Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size) {
-    if (tp_size != 1 || tp_rank != 0) throw Error(kErrUnsupported, "tensor parallel loading is not available: tp_size must be 1");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
     if (device < 0 || device >= ndev) throw Error(kErrInvalid, "device index out of range");
@@ -127,16 +132,26 @@ Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size)
     m->num_sms = prop.multiProcessorCount;
     m->cfg = read_config(dir);
     const Config& c = m->cfg;
-    const size_t H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
-    const size_t nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    m->tp = tp_partition(c, tp_rank, tp_size);
+    const TpPartition& tp = m->tp;
+    m->nh = tp.n_q_heads;
+    m->nkv = tp.n_kv_heads;
+    m->I = tp.n_i;
+    m->V = tp.n_v;
+    const size_t H = c.hidden_size, Ifull = c.intermediate_size, V = c.vocab_size, hd = c.head_dim;
+    const size_t nh_full = c.num_heads;
+    const size_t nh = m->nh, nkv = m->nkv, I = m->I;
     if (!(hd == 64 || hd == 128)) throw Error(kErrUnsupported, "head_dim must be 64 or 128");
     if (H % 8 || I % 8) throw Error(kErrUnsupported, "hidden and intermediate sizes must be multiples of 8");
-    if (nh / nkv > 8) throw Error(kErrUnsupported, "more than 8 query heads per kv head");
+    if (nh / nkv > 8 || nh % nkv != 0) throw Error(kErrUnsupported, "more than 8 query heads per kv head");
 
     SafeTensorsDir st(dir);
-    upload(m->embed, st.bf16("model.embed_tokens.weight", V * H), V * H * 2);
+    upload(m->embed, st.bf16("model.embed_tokens.weight", V * H), V * H * 2);  // replicated: a row gather only
     m->layers.resize(c.num_layers);
+    // this rank's rows of q / k / v (whole heads), columns of o_proj, rows of gate / up, columns of down
     const size_t nq = nh * hd, nk = nkv * hd, nqkv = nq + 2 * nk;
+    const size_t q0 = (size_t)tp.q_head0 * hd, k0 = (size_t)tp.kv_head0 * hd;
+    const size_t nq_full = nh_full * hd, nk_full = (size_t)c.num_kv_heads * hd;
     DeviceBuffer gate_tmp, up_tmp;
     gate_tmp.alloc(I * H * 2);
     up_tmp.alloc(I * H * 2);
@@ -144,41 +159,48 @@ Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size)
         LayerWeights& ly = m->layers[l];
         const std::string p = "model.layers." + std::to_string(l) + ".";
         ly.wqkv.alloc(nqkv * H * 2);
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.weight", nq * H), nq * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + nq * H, st.bf16(p + "self_attn.k_proj.weight", nk * H), nk * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + (nq + nk) * H, st.bf16(p + "self_attn.v_proj.weight", nk * H), nk * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.weight", nq_full * H) + q0 * H, nq * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + nq * H, st.bf16(p + "self_attn.k_proj.weight", nk_full * H) + k0 * H, nk * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + (nq + nk) * H, st.bf16(p + "self_attn.v_proj.weight", nk_full * H) + k0 * H, nk * H * 2, cudaMemcpyHostToDevice));
         if (st.has(p + "self_attn.q_proj.bias")) {  // same test as inference/src/model/qwen.cu:99
             ly.has_bias = true;
             ly.bqkv.alloc(nqkv * 2);
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.bias", nq), nq * 2, cudaMemcpyHostToDevice));
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq, st.bf16(p + "self_attn.k_proj.bias", nk), nk * 2, cudaMemcpyHostToDevice));
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq + nk, st.bf16(p + "self_attn.v_proj.bias", nk), nk * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.bias", nq_full) + q0, nq * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq, st.bf16(p + "self_attn.k_proj.bias", nk_full) + k0, nk * 2, cudaMemcpyHostToDevice));
+            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq + nk, st.bf16(p + "self_attn.v_proj.bias", nk_full) + k0, nk * 2, cudaMemcpyHostToDevice));
         }
-        upload(ly.wo, st.bf16(p + "self_attn.o_proj.weight", H * nq), H * nq * 2);
+        ly.wo.alloc(H * nq * 2);
+        upload_cols(ly.wo.p, st.bf16(p + "self_attn.o_proj.weight", H * nq_full), H, nq_full, q0, nq);
         upload(ly.attn_norm, st.bf16(p + "input_layernorm.weight", H), H * 2);
         upload(ly.ffn_norm, st.bf16(p + "post_attention_layernorm.weight", H), H * 2);
-        TFFN_CUDA(cudaMemcpy(gate_tmp.p, st.bf16(p + "mlp.gate_proj.weight", I * H), I * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(up_tmp.p, st.bf16(p + "mlp.up_proj.weight", I * H), I * H * 2, cudaMemcpyHostToDevice));
-        upload(ly.ffn.down, st.bf16(p + "mlp.down_proj.weight", H * I), H * I * 2);
+        TFFN_CUDA(cudaMemcpy(gate_tmp.p, st.bf16(p + "mlp.gate_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2, cudaMemcpyHostToDevice));
+        TFFN_CUDA(cudaMemcpy(up_tmp.p, st.bf16(p + "mlp.up_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2, cudaMemcpyHostToDevice));
+        ly.ffn.down.alloc(H * I * 2);
+        upload_cols(ly.ffn.down.p, st.bf16(p + "mlp.down_proj.weight", H * Ifull), H, Ifull, tp.i0, I);
+        TFFN_CUDA(cudaStreamSynchronize(0));
         ly.ffn.packed.alloc(I * 3 * H * 2);
         launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), ly.ffn.down.as<bf16>(), ly.ffn.packed.as<bf16>(), (int)I, (int)H, 0);
         TFFN_CUDA(cudaGetLastError());
         TFFN_CUDA(cudaDeviceSynchronize());
     }
     upload(m->final_norm, st.bf16("model.norm.weight", H), H * 2);
+    // LM head: this rank's rows of the vocabulary
     if (c.tie_embeddings) {
-        m->lm_head = m->embed.as<bf16>();
+        m->lm_head = m->embed.as<bf16>() + (size_t)tp.v0 * H;
     } else {
-        upload(m->lm_head_own, st.bf16("lm_head.weight", V * H), V * H * 2);
+        upload(m->lm_head_own, st.bf16("lm_head.weight", V * H) + (size_t)tp.v0 * H, (size_t)m->V * H * 2);
         m->lm_head = m->lm_head_own.as<bf16>();
     }
-    m->bs1_ok = bs1_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
+    m->bs1_ok = tp_size == 1 && bs1_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
     const uint64_t per_layer = (nqkv * H + H * nq + 3 * I * H) * 2 + 2 * H * 2 + (uint64_t)(m->layers[0].has_bias ? nqkv * 2 : 0);
-    m->weight_bytes_base = per_layer * c.num_layers + V * H * 2 + H * 2;
+    m->weight_bytes_base = per_layer * c.num_layers + (uint64_t)m->V * H * 2 + H * 2;
     return m.release();
 }
 
 // ------------------------------------------------------------------------------------------ Expert
+// Reads only this rank's slice of every matrix from the memory-mapped file (rows of gate / up, columns of
+// down): a tensor-parallel rank touches 1 / tp_size of the file (inference/src/io/checkpoint.cpp:40-61 reads
+// whole matrices through three device allocations per layer).
 Expert* Expert::load(const Model* m, const std::string& path, float scale) {
     if (!m) throw Error(kErrInvalid, "model is NULL");
     TFFN_CUDA(cudaSetDevice(m->device));
@@ -194,7 +216,7 @@ Expert* Expert::load(const Model* m, const std::string& path, float scale) {
     std::unique_ptr<Expert> e(new Expert());
     e->model = m;
     e->scale = scale;
-    const size_t H = c.hidden_size, I = c.intermediate_size, n = H * I;
+    const size_t H = c.hidden_size, Ifull = c.intermediate_size, I = m->I, i0 = m->tp.i0, n = H * I;
     e->layers.resize(c.num_layers);
     DeviceBuffer stage, gate_tmp, up_tmp;
     stage.alloc(n * 4);
@@ -206,7 +228,10 @@ Expert* Expert::load(const Model* m, const std::string& path, float scale) {
         f.packed.alloc(n * 3 * 2);
         bf16* dst[3] = {gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>()};
         for (int k = 0; k < 3; ++k) {
-            TFFN_CUDA(cudaMemcpy(stage.p, ef.matrix(l, k), n * 4, cudaMemcpyHostToDevice));
+            if (k < 2)  // rows i0 .. i0 + I of [Ifull, H]
+                TFFN_CUDA(cudaMemcpy(stage.p, ef.matrix(l, k) + i0 * H, n * 4, cudaMemcpyHostToDevice));
+            else        // columns i0 .. i0 + I of [H, Ifull]
+                TFFN_CUDA(cudaMemcpy2D(stage.p, I * 4, ef.matrix(l, k) + i0, Ifull * 4, I * 4, H, cudaMemcpyHostToDevice));
             launch_cast_f32_bf16(stage.as<float>(), dst[k], n, 0);
             TFFN_CUDA(cudaGetLastError());
             TFFN_CUDA(cudaDeviceSynchronize());
@@ -220,9 +245,16 @@ Expert* Expert::load(const Model* m, const std::string& path, float scale) {
 }
 
 // ------------------------------------------------------------------------------------------ Session
-Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream)
-    : m_(m), e_(e), max_batch_(max_batch), max_seq_(max_seq), stream_(stream) {
+Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream, TpComm* tp)
+    : m_(m), e_(e), tp_(tp), max_batch_(max_batch), max_seq_(max_seq), stream_(stream) {
     if (!m) throw Error(kErrInvalid, "model is NULL");
+    if (m->tp.tp_size > 1) {
+        if (!tp) throw Error(kErrInvalid, "the model was loaded as one tensor-parallel rank: the session needs the group's communicator");
+        if (tp_comm_size(tp) != m->tp.tp_size || tp_comm_rank(tp) != m->tp.tp_rank)
+            throw Error(kErrInvalid, "communicator rank / size differ from the model's tensor-parallel rank / size");
+    } else {
+        tp_ = nullptr;
+    }
     if (e && e->model != m) throw Error(kErrInvalid, "expert was loaded for a different model");
     if (max_batch < 1 || max_batch > 4096) throw Error(kErrInvalid, "max_batch must be in [1, 4096]");
     if (max_seq < 2) throw Error(kErrInvalid, "max_seq must be at least 2");
@@ -232,8 +264,9 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
         own_stream_ = true;
     }
     const Config& c = m->cfg;
-    const size_t H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
-    const size_t nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim, L = c.num_layers;
+    // this rank's sizes (the whole model without tensor parallelism)
+    const size_t H = c.hidden_size, I = m->I, V = c.vocab_size;
+    const size_t nh = m->nh, nkv = m->nkv, hd = c.head_dim, L = c.num_layers;
 
     max_pages_per_seq_ = (max_seq + kPageTokens - 1) / kPageTokens;
     num_pages_ = max_batch * max_pages_per_seq_;
@@ -295,6 +328,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     act_b_.alloc(T * I * 2);
     if (e_) act_e_.alloc(T * I * 2);
     xn_last_.alloc(T * H * 2);
+    if (tp_) delta_.alloc(T * H * 4);
     ensure_logits(std::max<size_t>(256, max_batch));
     attn_partials_.alloc((size_t)32 << 20);
     attn_counters_.alloc(16384 * 4);
@@ -359,10 +393,28 @@ AttnWorkspace Session::attn_ws() const {
 void Session::ensure_logits(size_t rows) {
     if (rows <= logits_rows_) return;
     TFFN_CUDA(cudaStreamSynchronize(stream_));
-    logits_.alloc(rows * (size_t)m_->cfg.vocab_size * 4);
+    logits_.alloc(rows * (size_t)m_->V * 4);  // this rank's vocabulary slice
+    if (tp_) tp_logits_.alloc(rows * (size_t)m_->V * 4 * m_->tp.tp_size);
     logits_rows_ = rows;
     drop_graphs();  // captured steps hold the old pointer
 }
+// fp32 logits rows [0, rows) of the last LM-head launch -> host [rows, vocab]. With tensor parallelism
+// every rank holds its slice of the vocabulary: the slices are all-gathered on the device and laid out
+// side by side by the copies. Asynchronous on the session's stream.
+void Session::copy_logits_to_host(float* dst, size_t rows) {
+    const size_t V = m_->cfg.vocab_size, Vl = m_->V;
+    if (!tp_) {
+        TFFN_CUDA(cudaMemcpyAsync(dst, logits_.p, rows * V * 4, cudaMemcpyDeviceToHost, stream_));
+        return;
+    }
+    const int n = m_->tp.tp_size;
+    if (Vl * n != V) throw Error(kErrUnsupported, "tensor parallel: the vocabulary does not split evenly, logits cannot be gathered");
+    tp_all_gather_bytes(tp_, logits_.p, tp_logits_.p, rows * Vl * 4, stream_);
+    for (int r = 0; r < n; ++r)
+        TFFN_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * Vl, V * 4, tp_logits_.as<float>() + (size_t)r * rows * Vl, Vl * 4, Vl * 4, rows,
+                                    cudaMemcpyDeviceToHost, stream_));
+}
+
 void Session::ensure_ring(int entries) {
     if (entries <= out_ring_cap_) return;
     TFFN_CUDA(cudaStreamSynchronize(stream_));
@@ -493,7 +545,7 @@ void Session::check_status() {
 const char* kclass_name(int c) {
     static const char* names[KC_COUNT] = {"embed_rows", "rmsnorm_rows", "gemm_tc:qkv", "attn_decode",
                                           "gemm_tc:o_proj", "gemm_tc:gate_up_swiglu", "gemm_tc:down", "gemm_tc:lm_head",
-                                          "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead"};
+                                          "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead", "nccl_all_reduce"};
     return (c >= 0 && c < KC_COUNT) ? names[c] : "?";
 }
 void Session::set_profile(bool on) {
@@ -568,9 +620,22 @@ int Session::build_groups(const int* seq, const int* pos, int T, int32_t* first,
 
 void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool decode, int max_ctx, int n_groups) {
     const Config& c = m_->cfg;
-    const int H = c.hidden_size, I = c.intermediate_size, V = c.vocab_size;
-    const int nh = c.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    // this rank's slice of the heads, of the intermediate dimension and of the LM head (everything without
+    // tensor parallelism); the vocabulary of the embedding is always the whole one
+    const int H = c.hidden_size, I = m_->I, V = c.vocab_size, Vl = m_->V;
+    const int nh = m_->nh, nkv = m_->nkv, hd = c.head_dim;
     const int nqkv = (nh + 2 * nkv) * hd;
+    const bool tp = tp_ != nullptr;
+    // Tensor parallel: the projections that end a block (o_proj, down) leave fp32 partial sums over this
+    // rank's heads / intermediate slice; they are all-reduced in fp32 (NCCL, on this stream, this GPU's own
+    // buffer) and only then added into the bf16 residual stream, one rounding as in the single-GPU order
+    // (inference/src/model/qwen.cu:282-285). The row kernel that adds them also forms the next RMSNorm.
+    auto all_reduce_delta = [&](int rows) {
+        prof_begin(KC_ALLREDUCE);
+        tp_all_reduce_f32(tp_, delta_.as<float>(), (size_t)rows * H, stream_);
+        prof_end();
+        launches_++;
+    };
     const int* tokens = decode ? dec_tokens_.as<int>() : tokens_.as<int>();
     const int* tok_seq = decode ? identity_.as<int>() : tok_seq_.as<int>();
     const int* tok_pos = decode ? seq_len_dev_.as<int>() : tok_pos_.as<int>();
@@ -598,11 +663,13 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     launches_++;
     for (int l = 0; l < c.num_layers; ++l) {
         const LayerWeights& ly = m_->layers[l];
-        prof_begin(KC_RMSNORM);
-        if (live(KC_RMSNORM))
-            launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl,
-                           tl_next(KC_RMSNORM));
-        prof_end();
+        if (!tp || l == 0) {  // with tensor parallelism the later layers' norm comes out of the residual kernel
+            prof_begin(KC_RMSNORM);
+            if (live(KC_RMSNORM))
+                launch_rmsnorm(h_.as<bf16>(), ly.attn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl,
+                               tl_next(KC_RMSNORM));
+            prof_end();
+        }
         GemmCall g;
         memset(&g, 0, sizeof g);
         g.x_rows_alloc = cap_tokens_;
@@ -646,14 +713,21 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         // o_proj + residual
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
         g.N = H;
-        g.mode = GEMM_RESIDUAL;
-        g.out = h_.p;
+        g.mode = tp ? GEMM_STORE_F32 : GEMM_RESIDUAL;
+        g.out = tp ? delta_.p : h_.p;
         g.ldo = H;
         gemm(g, KC_GEMM_OPROJ);
         prof_begin(KC_RMSNORM);
-        if (live(KC_RMSNORM))
+        if (tp) {
+            prof_end();
+            all_reduce_delta(T);
+            prof_begin(KC_RMSNORM);
+            launch_residual_norm(h_.as<bf16>(), delta_.as<float>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps,
+                                 stream_, pdl);
+        } else if (live(KC_RMSNORM)) {
             launch_rmsnorm(h_.as<bf16>(), ly.ffn_norm.as<bf16>(), xn_.as<bf16>(), T, H, c.rms_norm_eps, nullptr, stream_, pdl,
                            tl_next(KC_RMSNORM));
+        }
         prof_end();
         launches_ += 3;
         // gate|up with the SwiGLU epilogue: strided views of the [I][3][H] records; the expert's
@@ -684,11 +758,19 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
             g.op[1] = {nullptr, 0, nullptr, 0, 0};
         }
         g.N = H;
-        g.mode = GEMM_RESIDUAL;
-        g.out = h_.p;
+        g.mode = tp ? GEMM_STORE_F32 : GEMM_RESIDUAL;
+        g.out = tp ? delta_.p : h_.p;
         g.ldo = H;
         gemm(g, KC_GEMM_DOWN);
         g.alpha = 1.f;
+        if (tp) {
+            all_reduce_delta(T);
+            const bf16* next_norm = l + 1 < c.num_layers ? m_->layers[l + 1].attn_norm.as<bf16>() : nullptr;
+            prof_begin(KC_RMSNORM);
+            launch_residual_norm(h_.as<bf16>(), delta_.as<float>(), next_norm, xn_.as<bf16>(), T, H, c.rms_norm_eps, stream_, pdl);
+            prof_end();
+            launches_++;
+        }
         if (hidden_rows_cap_ > 0) {
             const int rows = std::min(T, hidden_rows_cap_);
             const size_t n16 = (size_t)rows * H / 8;
@@ -710,15 +792,16 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.T = n_logit_rows;
         g.alpha = 1.f;
         g.op[0] = {m_->lm_head, H, xn_last_.as<bf16>(), H, H};
-        g.N = V;
+        g.N = Vl;  // this rank's rows of the vocabulary
         g.mode = GEMM_STORE_F32;
-        g.ldo = V;
+        g.ldo = Vl;
         // The greedy pick rides in the LM head's epilogue (per-tile maxima, combined by a tiny kernel); the
         // fp32 logits themselves are written only when the caller asked for them. The attention workspace is
         // idle by now and serves as scratch.
         const AttnWorkspace aw = attn_ws();
-        const int v_tiles = (V + 127) / 128;
+        const int v_tiles = (Vl + 127) / 128;
         const bool fused_pick = !sampling() && (size_t)n_logit_rows * v_tiles * 2 <= aw.partial_floats;
+        if (tp && !fused_pick) throw Error(kErrUnsupported, "tensor parallel: sampling and very large logit batches are not split across ranks");
         if (fused_pick) {
             g.amax_val = aw.partials;
             g.amax_idx = (int*)(aw.partials + (size_t)n_logit_rows * v_tiles);
@@ -727,7 +810,22 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         gemm(g, KC_GEMM_LMHEAD);
         prof_begin(KC_ARGMAX);
         if (live(KC_ARGMAX)) {
-            if (fused_pick)
+            if (fused_pick && tp) {
+                // every rank's best of its vocabulary slice, exchanged (8 bytes per row and rank), then the same
+                // pick on every rank: largest value, lowest global index among equals (main.cpp:45-51)
+                const size_t bytes = (size_t)n_logit_rows * 8;
+                if (tp_pick_send_.bytes < bytes) {
+                    TFFN_CUDA(cudaStreamSynchronize(stream_));
+                    tp_pick_send_.alloc(bytes);
+                    tp_pick_recv_.alloc(bytes * m_->tp.tp_size);
+                    drop_graphs();
+                }
+                launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),
+                                    tp_pick_send_.p, m_->tp.v0);
+                tp_all_gather_bytes(tp_, tp_pick_send_.p, tp_pick_recv_.p, bytes, stream_);
+                launch_tp_pick(tp_pick_recv_.p, m_->tp.tp_size, n_logit_rows, picks_.as<int>(), stream_, pdl);
+                launches_ += 2;
+            } else if (fused_pick)
                 launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX));
             else if (sampling())
                 launch_sample(logits_.as<float>(), n_logit_rows, V, sample_temp_, sample_u_.as<double>(),
@@ -1007,16 +1105,19 @@ void Session::prefill(const int32_t* tokens, const int32_t* seq_lens, int n_seqs
         run_batched(T, (int)last_rows.size(), false, false, max_ctx, n_groups);
         if (!last_rows.empty()) {
             std::vector<int> picks(last_rows.size());
+            std::vector<float> rows_host;
             TFFN_CUDA(cudaMemcpyAsync(picks.data(), picks_.p, picks.size() * 4, cudaMemcpyDeviceToHost, stream_));
+            if (logits_last) {
+                rows_host.resize(last_rows.size() * (size_t)V);
+                copy_logits_to_host(rows_host.data(), last_rows.size());
+            }
             TFFN_CUDA(cudaStreamSynchronize(stream_));
             for (size_t i = 0; i < last_rows.size(); ++i) {
                 if (next_tokens) next_tokens[last_slots[i]] = picks[i];
                 int32_t* one = pinned_i32(4);
                 one[0] = picks[i];
                 TFFN_CUDA(cudaMemcpyAsync(dec_tokens_.as<int>() + last_slots[i], one, 4, cudaMemcpyHostToDevice, stream_));
-                if (logits_last)
-                    TFFN_CUDA(cudaMemcpyAsync(logits_last + (size_t)last_slots[i] * V, logits_.as<float>() + i * (size_t)V,
-                                              (size_t)V * 4, cudaMemcpyDeviceToHost, stream_));
+                if (logits_last) memcpy(logits_last + (size_t)last_slots[i] * V, rows_host.data() + i * (size_t)V, (size_t)V * 4);
                 TFFN_CUDA(cudaStreamSynchronize(stream_));
             }
         } else {
@@ -1064,7 +1165,7 @@ void Session::forward(int slot, const int32_t* tokens, int T, float* logits) {
         store_logits_ = logits != nullptr;
         if (logits) {
             run_batched(n, n, true, false, h_seq_len_[slot] + c0 + n, n_groups);
-            TFFN_CUDA(cudaMemcpyAsync(logits + (size_t)c0 * V, logits_.p, (size_t)n * V * 4, cudaMemcpyDeviceToHost, stream_));
+            copy_logits_to_host(logits + (size_t)c0 * V, (size_t)n);
             TFFN_CUDA(cudaMemcpyAsync(pin, picks_.as<int>() + (n - 1), 4, cudaMemcpyDeviceToHost, stream_));
             TFFN_CUDA(cudaStreamSynchronize(stream_));
             last_pick = pin[0];
@@ -1119,7 +1220,7 @@ void Session::decode_step(const int32_t* tokens_in, int n_seqs, int32_t* next_to
         run_decode_batched(n_seqs, max_ctx);
     }
     TFFN_CUDA(cudaMemcpyAsync(pin, dec_tokens_.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, stream_));
-    if (logits) TFFN_CUDA(cudaMemcpyAsync(logits, logits_.p, (size_t)n_seqs * V * 4, cudaMemcpyDeviceToHost, stream_));
+    if (logits) copy_logits_to_host(logits, (size_t)n_seqs);
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     if (next_tokens)
         for (int s = 0; s < n_seqs; ++s) next_tokens[s] = pin[s];

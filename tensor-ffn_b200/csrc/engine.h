@@ -43,8 +43,21 @@ struct LayerWeights {
     FfnWeights ffn;
 };
 
+// NCCL communicator of a tensor-parallel group (the library is opened at run time; see tp_comm.cpp)
+struct TpComm;
+TpComm* tp_comm_create(const uint8_t id[128], int rank, int size, int device);
+void tp_comm_unique_id(uint8_t id[128]);
+void tp_comm_free(TpComm* c);
+int tp_comm_size(const TpComm* c);
+int tp_comm_rank(const TpComm* c);
+void tp_all_reduce_f32(TpComm* c, float* buf, size_t n, cudaStream_t s);                 // in place, sum
+void tp_all_gather_bytes(TpComm* c, const void* send, void* recv, size_t bytes, cudaStream_t s);  // recv[rank * bytes ...]
+
 struct Model {
-    Config cfg;
+    Config cfg;         // the whole model, as config.json states it
+    TpPartition tp;     // this rank's slices (everything when tp_size == 1)
+    // this rank's sizes: query heads, kv heads, intermediate rows, LM-head rows
+    int nh = 0, nkv = 0, I = 0, V = 0;
     int device = 0, num_sms = 0;
     DeviceBuffer embed, final_norm, lm_head_own;
     const bf16* lm_head = nullptr;
@@ -69,7 +82,7 @@ struct Expert {
 // kernel classes of the per-launch profile (tffn_session_profile_*)
 enum KClass : int {
     KC_EMBED = 0, KC_RMSNORM, KC_GEMM_QKV, KC_ATTENTION, KC_GEMM_OPROJ, KC_GEMM_GATEUP, KC_GEMM_DOWN,
-    KC_GEMM_LMHEAD, KC_ARGMAX, KC_ADVANCE, KC_BS1_QKV, KC_BS1_OPROJ, KC_BS1_FFN, KC_BS1_LMHEAD, KC_COUNT
+    KC_GEMM_LMHEAD, KC_ARGMAX, KC_ADVANCE, KC_BS1_QKV, KC_BS1_OPROJ, KC_BS1_FFN, KC_BS1_LMHEAD, KC_ALLREDUCE, KC_COUNT
 };
 const char* kclass_name(int c);
 
@@ -85,7 +98,7 @@ public:
     void set_profile(bool on);
     // accumulated device time (ms) and launches per class since set_profile(true); returns KC_COUNT
     int read_profile(float* ms, int* counts, int cap);
-    Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream);
+    Session(const Model* m, const Expert* e, int max_batch, int max_seq, cudaStream_t stream, TpComm* tp = nullptr);
     ~Session();
     void reset(int slot);
     int seq_len(int slot) const { return h_seq_len_[slot]; }
@@ -110,6 +123,9 @@ public:
 private:
     const Model* m_;
     const Expert* e_;
+    TpComm* tp_ = nullptr;  // not owned
+    DeviceBuffer delta_, tp_pick_send_, tp_pick_recv_, tp_logits_;  // tensor parallel: fp32 partial sums, pick exchange, gathered logits
+    void copy_logits_to_host(float* dst, size_t rows);  // rows of logits_ (this rank's vocabulary slice) -> full rows on the host
     int max_batch_, max_seq_, max_pages_per_seq_, num_pages_;
     int cap_tokens_;  // rows of the activation buffers
     cudaStream_t stream_;

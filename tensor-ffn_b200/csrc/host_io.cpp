@@ -64,6 +64,41 @@ Config read_config(const std::string& dir) {
     return c;
 }
 
+TpPartition tp_partition(const Config& c, int rank, int size) {
+    if (size < 1 || rank < 0 || rank >= size) throw Error(kErrInvalid, "tensor-parallel rank / size out of range");
+    TpPartition p;
+    p.tp_rank = rank;
+    p.tp_size = size;
+    const int nh = c.num_heads, nkv = c.num_kv_heads, G = nh / nkv;
+    if (size <= nkv) {
+        if (nkv % size != 0) throw Error(kErrUnsupported, "tensor parallel: the kv heads do not divide among the ranks");
+        p.n_kv_heads = nkv / size;
+        p.kv_head0 = rank * p.n_kv_heads;
+        p.q_head0 = p.kv_head0 * G;
+        p.n_q_heads = p.n_kv_heads * G;
+    } else {
+        if (size % nkv != 0) throw Error(kErrUnsupported, "tensor parallel: the ranks do not divide among the kv heads");
+        const int R = size / nkv, sub = rank % R;  // R ranks share kv head rank / R
+        if (R > G) throw Error(kErrUnsupported, "tensor parallel: more ranks per kv head than query heads in its group");
+        p.n_kv_heads = 1;
+        p.kv_head0 = rank / R;
+        const int a = G * sub / R, b = G * (sub + 1) / R;
+        p.q_head0 = p.kv_head0 * G + a;
+        p.n_q_heads = b - a;
+    }
+    if (c.intermediate_size % 64 != 0 && size > 1)
+        throw Error(kErrUnsupported, "tensor parallel: the intermediate size must be a multiple of 64");
+    const int iu = c.intermediate_size / 64;
+    if (size > 1 && iu < size) throw Error(kErrUnsupported, "tensor parallel: intermediate size too small for this many ranks");
+    p.i0 = size > 1 ? (int)((long long)iu * rank / size) * 64 : 0;
+    p.n_i = size > 1 ? (int)((long long)iu * (rank + 1) / size) * 64 - p.i0 : c.intermediate_size;
+    if (size > 1 && c.vocab_size % 8 != 0) throw Error(kErrUnsupported, "tensor parallel: the vocabulary size must be a multiple of 8");
+    const int vu = c.vocab_size / 8;
+    p.v0 = size > 1 ? (int)((long long)vu * rank / size) * 8 : 0;
+    p.n_v = size > 1 ? (int)((long long)vu * (rank + 1) / size) * 8 - p.v0 : c.vocab_size;
+    return p;
+}
+
 // ---------------------------------------------------------------- safetensors
 static void* map_file(const std::string& path, size_t* size, int* fd_out) {
     int fd = ::open(path.c_str(), O_RDONLY);

@@ -30,6 +30,22 @@ struct Config {
 };
 Config read_config(const std::string& model_dir);
 
+// What one tensor-parallel rank owns. The reference is single-GPU; these are the slices of its matrices
+// (q/k/v rows by head: inference/src/model/qwen.cu:317-319; o_proj columns: :413-415; gate/up rows and down
+// columns on the intermediate dimension for the base FFN: :431-437 and for the expert:
+// inference/src/model/expert.cu:51-58; LM-head rows on the vocabulary: qwen.cu:450-454).
+// Heads are kept together with their kv head: with tp_size <= kv heads every rank takes whole kv groups;
+// with more ranks than kv heads, tp_size / kv_heads ranks share a kv head (each computes its K/V row
+// itself) and split its query heads as evenly as they go (7 heads over 2 ranks: 3 + 4).
+struct TpPartition {
+    int tp_rank = 0, tp_size = 1;
+    int q_head0 = 0, n_q_heads = 0;    // first global query head, count (all of one kv group when kv heads are shared)
+    int kv_head0 = 0, n_kv_heads = 0;  // first global kv head, count
+    int i0 = 0, n_i = 0;               // rows of gate/up and columns of down (multiples of 64)
+    int v0 = 0, n_v = 0;               // rows of the LM head (multiples of 8)
+};
+TpPartition tp_partition(const Config& c, int tp_rank, int tp_size);  // kErrUnsupported if the shape does not split
+
 // One memory-mapped .safetensors file: u64 LE header length, JSON header, raw data
 // (inference/src/io/safetensors.cpp:41-78). "__metadata__" is skipped.
 struct TensorInfo {

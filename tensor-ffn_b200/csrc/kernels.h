@@ -97,8 +97,14 @@ void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
 // per-tile maxima left by the GEMM (GemmCall::amax_val / amax_idx, `tiles` per row) -> argmax per row
+// pack (optional, 8 bytes per row): {the row's maximum, idx_offset + its index} for the exchange between
+// tensor-parallel ranks, which launch_tp_pick resolves (cand = `ranks` such arrays of R rows back to back)
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s,
-                         bool pdl = false, unsigned long long* tl = nullptr);
+                         bool pdl = false, unsigned long long* tl = nullptr, void* pack = nullptr, int idx_offset = 0);
+void launch_tp_pick(const void* cand, int ranks, int R, int* out, cudaStream_t s, bool pdl = false);
+// tensor parallel: h = bf16(h + delta) and, if w != null, out = rmsnorm(h) * w, per row
+void launch_residual_norm(bf16* h, const float* delta, const bf16* w, bf16* out, int T, int H, float eps, cudaStream_t s,
+                          bool pdl = false);
 // logits fp32 [R, V] -> argmax (lowest index among maxima). scratch (>= 2 * R * 64 floats) and
 // counters (>= R ints, zero, left zero) let several blocks share a row; without them one block per row.
 void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, size_t scratch_floats, int* counters,

@@ -151,8 +151,10 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ l
 }
 
 // second half of the greedy pick when the LM-head GEMM left per-tile maxima: one block per row
+// (pack: optional {value, idx_offset + index} per row for the exchange between tensor-parallel ranks)
 __global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ val, const int* __restrict__ idx, int tiles,
-                                                       int* __restrict__ out, unsigned long long* tl) {
+                                                       int* __restrict__ out, unsigned long long* tl, float2* __restrict__ pack,
+                                                       int idx_offset) {
     if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
@@ -175,8 +177,57 @@ __global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ 
         for (int o = 4; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
         if (threadIdx.x == 0) {
             out[r] = (bi == 0x7fffffff) ? 0 : bi;
+            if (pack) pack[r] = make_float2(best, __int_as_float(bi == 0x7fffffff ? 0x7fffffff : bi + idx_offset));
             tl_mark(tl, 2);
         }
+    }
+}
+
+// Tensor parallel: the ranks' candidates {maximum of the rank's vocabulary slice, its global index} ->
+// the pick: the largest value, the lowest index among equal values (inference/src/main.cpp:45-51).
+__global__ void k_tp_pick(const float2* __restrict__ cand, int ranks, int R, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < ranks; ++k) {
+        const float2 c = __ldcg(cand + (size_t)k * R + r);
+        argmax_take(best, bi, c.x, __float_as_int(c.y));
+    }
+    out[r] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// Tensor parallel: h = bf16(float(h) + delta) (delta = the all-reduced fp32 sum of the ranks' projection
+// outputs; the residual add of inference/src/model/qwen.cu:282-285), and, when w is given, the RMSNorm of
+// the new row (inference/src/backend/cuda_ops.cu:75-96) in the same pass. One block of 128 threads per row.
+__global__ void __launch_bounds__(128) k_residual_norm_rows(bf16* __restrict__ h, const float* __restrict__ delta,
+                                                             const bf16* __restrict__ w, bf16* __restrict__ out, int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    bf16* hr = h + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
+    __shared__ float s_red[4];
+    float ss = 0.f;
+    for (int i = threadIdx.x * 2; i < H; i += 256) {
+        const uint32_t hv = *(const uint32_t*)(hr + i);
+        const float2 d = __ldcg((const float2*)(dr + i));
+        const float a = bf16_round(bf16_lo(hv) + d.x), b = bf16_round(bf16_hi(hv) + d.y);
+        *(uint32_t*)(hr + i) = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
+        ss += a * a + b * b;
+    }
+    if (!w) return;
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float rinv = rsqrtf((s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)H + eps);
+    for (int i = threadIdx.x * 2; i < H; i += 256) {  // each thread re-reads only what it wrote itself
+        const uint32_t hv = *(const uint32_t*)(hr + i);
+        const uint32_t wv = __ldg((const uint32_t*)(w + i));
+        const float x0 = bf16_lo(hv) * rinv * bf16_lo(wv), x1 = bf16_hi(hv) * rinv * bf16_hi(wv);
+        *(uint32_t*)(out + (size_t)r * H + i) = (uint32_t)bf16_bits(x0) | ((uint32_t)bf16_bits(x1) << 16);
     }
 }
 
@@ -296,6 +347,8 @@ int rows_prepare() {
     if (e == cudaSuccess) e = prefer_max_shared(k_argmax_rows);
     if (e == cudaSuccess) e = prefer_max_shared(k_argmax_tiles);
     if (e == cudaSuccess) e = prefer_max_shared(k_sample_rows);
+    if (e == cudaSuccess) e = prefer_max_shared(k_tp_pick);
+    if (e == cudaSuccess) e = prefer_max_shared(k_residual_norm_rows);
     return (int)e;
 }
 
@@ -316,8 +369,14 @@ void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, 
     launch_k(k_argmax_rows, dim3(R, S), dim3(256), 0, s, pdl, logits, V, S, out, scratch, counters, tl);
 }
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s, bool pdl,
-                         unsigned long long* tl) {
-    launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl);
+                         unsigned long long* tl, void* pack, int idx_offset) {
+    launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl, (float2*)pack, idx_offset);
+}
+void launch_tp_pick(const void* cand, int ranks, int R, int* out, cudaStream_t s, bool pdl) {
+    launch_k(k_tp_pick, dim3((R + 127) / 128), dim3(128), 0, s, pdl, (const float2*)cand, ranks, R, out);
+}
+void launch_residual_norm(bf16* h, const float* delta, const bf16* w, bf16* out, int T, int H, float eps, cudaStream_t s, bool pdl) {
+    launch_k(k_residual_norm_rows, dim3(T), dim3(128), 0, s, pdl, h, delta, w, out, H, eps);
 }
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl, unsigned long long* tl) {

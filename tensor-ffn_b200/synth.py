@@ -159,7 +159,14 @@ def write_tokenizer(dirpath: str, cfg: dict):
 
 
 def write_model(dirpath: str, shape: str | dict = "tiny", seed: int = 1234, qkv_bias: bool = True,
-                norm_jitter: float = 0.0, shard_bytes: int = 4 << 30, threads: int = 0, **cfg_over) -> dict:
+                norm_jitter: float = 0.0, shard_bytes: int = 4 << 30, threads: int = 0, head_norm_sigma: float = 0.0,
+                **cfg_over) -> dict:
+    """head_norm_sigma > 0 gives the vocabulary rows (embedding, and LM head when untied) log-normal
+    norms: row v is scaled by exp(head_norm_sigma * z_v). With iid N(0, 0.02) rows the 150 k logits of a
+    random-init model are nearly tied somewhere, so that top-1 agreement between two correct
+    implementations is decided by rounding noise; with heavy-tailed row norms a few rows compete for the
+    maximum and the winner (which still depends on the direction of the final hidden state, i.e. on every
+    layer) leads by far more than the bf16 noise."""
     os.makedirs(dirpath, exist_ok=True)
     cfg = make_config(shape, **cfg_over)
     V = cfg["vocab_size"]
@@ -178,6 +185,12 @@ def write_model(dirpath: str, shape: str | dict = "tiny", seed: int = 1234, qkv_
                 rng = np.random.default_rng([seed, i])
                 return f32_to_bf16(1.0 + norm_jitter * rng.standard_normal(n, dtype=np.float32))
             return f32_to_bf16(np.ones(n, dtype=np.float32))
+        if head_norm_sigma > 0 and name in ("model.embed_tokens.weight", "lm_head.weight"):
+            rng = np.random.default_rng([seed, i])
+            w = rng.standard_normal((shp[0], shp[1]), dtype=np.float32) * np.float32(0.02)
+            z = np.random.default_rng([seed, i, 77]).standard_normal(shp[0], dtype=np.float32)
+            w *= np.exp(np.float32(head_norm_sigma) * z)[:, None]
+            return f32_to_bf16(w.reshape(-1))
         return _normal_bf16([seed, i], n, 0.02)
 
     threads = threads or min(16, os.cpu_count() or 1)

@@ -70,6 +70,11 @@ _SIGS = {
     "tffn_expert_free": (None, [_vp]),
     "tffn_session_create": (_i, [_vp, _vp, _i, _i, _vp, _pp]),
     "tffn_session_free": (None, [_vp]),
+    "tffn_session_create_tp": (_i, [_vp, _vp, _i, _i, _vp, _vp, _pp]),
+    "tffn_tp_unique_id": (_i, [_vp]),
+    "tffn_tp_create": (_i, [_vp, _i, _i, _i, _pp]),
+    "tffn_tp_free": (None, [_vp]),
+    "tffn_tp_partition": (_i, [ctypes.POINTER(Config), _i, _i, _vp]),
     "tffn_session_reset": (_i, [_vp, _i]),
     "tffn_session_seq_len": (_i, [_vp, _i]),
     "tffn_session_set_launch_mode": (_i, [_vp, _i]),
@@ -235,11 +240,46 @@ class QwenModel:
             self.free()
 
 
-def qwen_load(model_dir: str, device: int = 0) -> QwenModel:
-    """qwen_load without the KV cache (inference/src/model/qwen.cu:80-132)"""
+def qwen_load(model_dir: str, device: int = 0, tp_rank: int = 0, tp_size: int = 1) -> QwenModel:
+    """qwen_load without the KV cache (inference/src/model/qwen.cu:80-132); with tp_size > 1 this
+    process loads only the slices of tensor-parallel rank tp_rank"""
     h = _vp()
-    _check(_L.tffn_model_load(model_dir.encode(), device, 0, 1, ctypes.byref(h)))
+    _check(_L.tffn_model_load(model_dir.encode(), device, tp_rank, tp_size, ctypes.byref(h)))
     return QwenModel(h)
+
+
+def tp_unique_id() -> bytes:
+    """the 128-byte id rank 0 hands to the other ranks of a tensor-parallel group"""
+    buf = ctypes.create_string_buffer(128)
+    _check(_L.tffn_tp_unique_id(buf))
+    return buf.raw
+
+
+class TpGroup:
+    """NCCL communicator of a tensor-parallel group (one process per GPU); creation is collective"""
+
+    def __init__(self, unique_id: bytes, tp_rank: int, tp_size: int, device: int):
+        assert len(unique_id) == 128
+        self.rank, self.size = tp_rank, tp_size
+        self._h = _vp()
+        _check(_L.tffn_tp_create(unique_id, tp_rank, tp_size, device, ctypes.byref(self._h)))
+
+    def free(self):
+        if getattr(self, "_h", None):
+            _L.tffn_tp_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        if _L is not None:
+            self.free()
+
+
+def tp_partition(cfg: Config, tp_rank: int, tp_size: int) -> dict:
+    """what rank tp_rank of tp_size owns (host-only arithmetic): heads, intermediate rows, LM-head rows"""
+    out = (ctypes.c_int32 * 8)()
+    _check(_L.tffn_tp_partition(ctypes.byref(cfg), tp_rank, tp_size, out))
+    keys = ("q_head0", "n_q_heads", "kv_head0", "n_kv_heads", "i0", "n_i", "v0", "n_v")
+    return dict(zip(keys, [int(v) for v in out]))
 
 
 def checkpoint_load(path: str, model: QwenModel, output_scale: float = kExpertOutputScale) -> ExpertModel:
@@ -253,13 +293,13 @@ class Session:
     """KV cache + scratch (the second half of qwen_load, inference/src/model/qwen.cu:134-171), paged."""
 
     def __init__(self, model: QwenModel, expert: ExpertModel | None = None, max_batch: int = 1, max_seq: int = 2048,
-                 stream: int | None = None):
-        self.model, self.expert = model, expert
+                 stream: int | None = None, tp: "TpGroup | None" = None):
+        self.model, self.expert, self.tp = model, expert, tp
         self.max_batch, self.max_seq = max_batch, max_seq
         self.V = model.cfg.vocab_size
         self._h = _vp()
-        _check(_L.tffn_session_create(model._h, expert._h if expert else None, max_batch, max_seq, stream,
-                                      ctypes.byref(self._h)))
+        _check(_L.tffn_session_create_tp(model._h, expert._h if expert else None, max_batch, max_seq, stream,
+                                         tp._h if tp else None, ctypes.byref(self._h)))
 
     def free(self):
         if getattr(self, "_h", None):
