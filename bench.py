@@ -7,9 +7,11 @@
 Workload (BASELINE.json configs[1]): Qwen2.5-0.5B shape + expert, bf16, 64 independent
 sequences per GPU, 512-token uniform-random prompts, greedy decode. A "step" is one decode step
 of the whole batch (64 new tokens per GPU). With N > 1 the sequences are sharded data-parallel,
-64 per rank, no collective on the data path (weak scaling). Weights are seeded synthetic
-stand-ins with the real shapes, written to disk in the reference's file formats and loaded
-through the library's loader. One JSON line is printed by rank 0.
+64 per rank, no collective on the data path (weak scaling; a strong-scaling run of 64 sequences
+in total rides along as an extra). --tp N (configs[4], the 7B shape) makes the N ranks one
+tensor-parallel group instead. Weights are seeded synthetic stand-ins with the real shapes,
+written to disk in the reference's file formats and loaded through the library's loader. One
+JSON line is printed by rank 0. The timed region of K steps is repeated and the median taken.
 
 value      decode tok/s with everything resident in HBM (device-side loop, CUDA events)
 e2e        the same metric through the public C ABI with host buffers: every step copies the
@@ -34,7 +36,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "tensor-ffn_b200"))
 
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-METRIC = "decode tok/s, Qwen2.5-0.5B+expert bf16 bs64 (bs1 in extras); % of HBM roofline"
+
+
+def metric_name(a) -> str:
+    name = {"0.5b": "Qwen2.5-0.5B", "1.5b": "Qwen2.5-1.5B", "3b": "Qwen2.5-3B", "7b": "Qwen2.5-7B"}.get(a.shape, a.shape)
+    return f"decode tok/s, {name}+expert bf16 bs{a.seqs} (bs1 in extras); % of HBM roofline"
+
+
+def workload_name(a) -> str:
+    idx = {"0.5b": 1, "1.5b": 2, "3b": 3, "7b": 4}.get(a.shape)
+    name = {"0.5b": "Qwen2.5-0.5B", "1.5b": "Qwen2.5-1.5B", "3b": "Qwen2.5-3B", "7b": "Qwen2.5-7B"}.get(a.shape, a.shape)
+    tag = f"configs[{idx}] shape" if idx is not None else "custom shape"
+    return f"{tag}: {name}+expert, {a.seqs} sequences x {a.prompt}-token prompts, batched greedy decode"
 
 
 def peaks():
@@ -45,7 +58,7 @@ def peaks():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-# DRAM traffic of k_gemm_tc from the ncu capture summarised in profiles/ncu_gemm_tc_decode_shapes.md
+# DRAM traffic of k_gemm_tc from an ncu capture of two launches
 # (one launch each of the two largest decode shapes, 64 tokens): dram read+write bytes per byte of
 # weights for a layer-sized launch whose output stays in L2, and the part of the LM head's fp32 logits
 # that reaches DRAM before the launch ends.
@@ -72,8 +85,9 @@ def ensure_model(shape: str, variant: str = "") -> tuple[str, str, dict]:
     marker = os.path.join(d, ".complete")
     if not os.path.exists(marker):
         shutil.rmtree(d, ignore_errors=True)
-        cfg = synth.write_model(d, shape, seed=1234, head_norm_sigma=1.5 if variant == "peaked" else 0.0)
-        synth.write_expert(ep, cfg, seed=4321)
+        fast = shape == "7b"  # 38 GB of files: cut out of one random block, only the sizes matter for throughput
+        cfg = synth.write_model(d, shape, seed=1234, head_norm_sigma=1.5 if variant == "peaked" else 0.0, fast=fast)
+        synth.write_expert(ep, cfg, seed=4321, fast=fast)
         with open(marker, "w") as f:
             f.write("ok")
     with open(os.path.join(d, "config.json")) as f:
@@ -129,20 +143,20 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def kernel_bytes(cfg: dict, with_expert: bool, n_seqs: int, ctx: float) -> dict:
+def kernel_bytes(cfg: dict, with_expert: bool, n_seqs: int, ctx: float, head_dim: int | None = None) -> dict:
     """Algorithmic HBM bytes per decode step, per kernel class: every weight matrix once per step,
     the KV cache of every sequence once per layer. Activations, partial sums and logits are not credited."""
     H, I, L, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
     nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
-    hd = H // nh
+    hd = head_dim or H // nh
     nqkv = (nh + 2 * nkv) * hd
     ffn = 3 * I * H * 2 * (2 if with_expert else 1)
     kv = n_seqs * 2 * nkv * hd * 2 * (ctx + 1)  # K and V rows of the context plus the new row
     b = {
-        "gemm_tc:qkv": L * nqkv * H * 2, "gemm_tc:o_proj": L * H * H * 2,
+        "gemm_tc:qkv": L * nqkv * H * 2, "gemm_tc:o_proj": L * H * nh * hd * 2,
         "gemm_tc:gate_up_swiglu": L * ffn * 2 // 3, "gemm_tc:down": L * ffn // 3, "gemm_tc:lm_head": V * H * 2,
         "attn_decode": L * kv,
-        "bs1_qkv": L * nqkv * H * 2, "bs1_oproj": L * H * H * 2, "bs1_ffn": L * ffn, "bs1_lmhead": V * H * 2,
+        "bs1_qkv": L * nqkv * H * 2, "bs1_oproj": L * H * nh * hd * 2, "bs1_ffn": L * ffn, "bs1_lmhead": V * H * 2,
     }
     return b
 
@@ -169,6 +183,50 @@ def reduce_max(dist, x: float, device: str) -> float:
     return float(t.item())
 
 
+def timed_decode(sess, stream, n, K, reps, barrier, max_over_ranks, want_tokens=False):
+    """K device-resident decode steps, repeated `reps` times; each repetition is bracketed by a barrier and a
+    synchronize on both sides and timed with CUDA events on the launching stream. Returns (median ms over
+    the repetitions after the max over ranks, all ms, tokens of the first repetition, launches per repetition)."""
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times, toks, launches = [], None, 0
+    for r in range(reps):
+        barrier()
+        l0 = sess.launch_count()
+        e0.record(stream)
+        t = sess.decode_run(n, K, want_tokens=want_tokens and r == 0)
+        e1.record(stream)
+        barrier()
+        if r == 0:
+            toks, launches = t, sess.launch_count() - l0
+        times.append(max_over_ranks(e0.elapsed_time(e1)))
+    return float(np.median(times)), times, toks, launches
+
+
+def reference_bs1(d: str, ep: str, prompt_len: int, n_tokens: int, reps: int):
+    """The reference's own decode loop (oracle/_ref/ref_driver: its unmodified sources) at configs[0]'s shape of
+    work: one sequence, prompt_len-token prompt, n_tokens greedy tokens, with the expert."""
+    import synth
+    drv = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+    if not os.path.exists(drv):
+        return None
+    toks = synth.prompts(1, prompt_len, 0)[0]
+    tf = os.path.join(os.path.dirname(ep), "ref_bs1_tokens.i32")
+    toks.tofile(tf)
+    out = os.path.join(os.path.dirname(ep), "ref_bs1_out")
+    try:
+        subprocess.check_call([drv, "--model", d, "--expert", ep, "--expert-scale", "0.1", "--max-seq",
+                               str(prompt_len + n_tokens + 8), "--tokens", tf, "--prompt-len", str(prompt_len), "--new",
+                               str(n_tokens), "--out", out, "--time", str(reps)], stdout=subprocess.DEVNULL)
+        with open(out + ".time.json") as f:
+            t = json.load(f)
+    except Exception as ex:
+        return {"error": str(ex)}
+    return {"tok_s_best": n_tokens / (t["decode_ms_best"] / 1e3), "tok_s_mean": n_tokens / (t["decode_ms_mean"] / 1e3),
+            "reps": reps, "prompt_len": prompt_len, "new_tokens": n_tokens,
+            "what": "the reference's unmodified CUDA sources, its own loop (token H2D, forward, logits D2H, host argmax)"}
+
+
 def run_ours(a):
     import torch
     import synth
@@ -179,6 +237,9 @@ def run_ours(a):
     if world != a.gpus:
         if world == 1 and a.gpus > 1:
             raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    tp_size = a.tp if a.tp > 1 else 1
+    if tp_size > 1 and tp_size != world:
+        raise SystemExit("--tp N needs exactly N ranks (torchrun --nproc-per-node N ... --gpus N --tp N)")
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
@@ -199,13 +260,19 @@ def run_ours(a):
     barrier()
     d, ep, cfg = ensure_model(a.shape)
     K, W, n = a.steps, a.warmup, a.seqs
-    max_seq = a.prompt + W + K + 8 + 16  # + the per-kernel profile pass and the timeline steps
+    reps = a.reps if a.reps > 0 else max(1, min(10, 256 // max(K, 1)))
+    max_seq = a.prompt + W + K * reps + 8 + 16  # + the per-kernel profile pass and the timeline steps
     stream = torch.cuda.Stream(device=local)
-    model = tffn.qwen_load(d, device=local)
+    group = None
+    if tp_size > 1:
+        meet = os.path.join("/tmp", f"tffn_tp_meet_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
+        group = tffn.TpGroup(tffn.tp_rendezvous(meet, rank, tp_size, 300.0), rank, tp_size, local)
+    model = tffn.qwen_load(d, device=local, tp_rank=rank if tp_size > 1 else 0, tp_size=tp_size)
     expert = tffn.checkpoint_load(ep, model, 0.1)
-    sess = tffn.Session(model, expert, max_batch=n, max_seq=max_seq, stream=stream.cuda_stream)
+    sess = tffn.Session(model, expert, max_batch=n, max_seq=max_seq, stream=stream.cuda_stream, tp=group)
     sess.set_launch_mode(a.launch_mode)
-    prompts = dp_prompts(rank, n, a.prompt)  # distinct sequences on every rank
+    # data parallel: distinct sequences on every rank; tensor parallel: the same sequences on every rank
+    prompts = dp_prompts(0 if tp_size > 1 else rank, n, a.prompt)
     prompt_list = [prompts[i] for i in range(n)]
 
     uuid = None
@@ -223,16 +290,9 @@ def run_ours(a):
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
     sess.decode_run(n, W, want_tokens=False)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    launches0 = sess.launch_count()
-    e0.record(stream)
-    toks_dev = sess.decode_run(n, K, want_tokens=True)
-    e1.record(stream)
-    barrier()
-    launches = sess.launch_count() - launches0
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    value = world * n * K / (ms / 1e3)
+    ms, rep_ms, toks_dev, launches = timed_decode(sess, stream, n, K, reps, barrier, max_over_ranks, want_tokens=True)
+    groups = 1 if tp_size > 1 else world
+    value = groups * n * K / (ms / 1e3)
 
     # ---- per-kernel device time (separate pass; the event pairs serialise the kernels)
     P = min(8, K)
@@ -240,8 +300,13 @@ def run_ours(a):
     sess.decode_run(n, P, want_tokens=False)
     prof = sess.profile_read()
     sess.profile(False)
-    ctx_mid = a.prompt + W + K / 2.0
-    kb = kernel_bytes(cfg, True, n, ctx_mid)
+    ctx_mid = a.prompt + W + K * reps / 2.0
+    cfg_rank = dict(cfg)
+    if tp_size > 1:  # this rank's slices
+        part = tffn.tp_partition(model.cfg, rank, tp_size)
+        cfg_rank.update(num_attention_heads=part["n_q_heads"], num_key_value_heads=part["n_kv_heads"],
+                        intermediate_size=part["n_i"], vocab_size=part["n_v"])
+    kb = kernel_bytes(cfg_rank, True, n, ctx_mid, head_dim=cfg["hidden_size"] // cfg["num_attention_heads"])
     kernels = []
     for name, (kms, cnt) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
         row = {"kernel": name, "launches_per_step": cnt / P, "ms_per_step": kms / P}
@@ -252,18 +317,20 @@ def run_ours(a):
     gemm_ms = sum(v[0] for k, v in prof.items() if k.startswith("gemm_tc:")) / P
     gemm_n = sum(v[1] for k, v in prof.items() if k.startswith("gemm_tc:")) / P
     gemm_bytes = sum(v for k, v in kb.items() if k.startswith("gemm_tc:"))
-    achieved = gemm_bytes / 1e9 / (gemm_ms / 1e3) if gemm_ms > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "k_gemm_tc (all launches of a decode step)", "achieved": achieved,
-                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                "launches_per_step": gemm_n, "avg_launch_us": 1e3 * gemm_ms / max(gemm_n, 1),
-                "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1)}
-    # traffic per launch: the captured ratio applied to this step's weight bytes, plus the logits written
-    traffic = gemm_bytes * NCU_DRAM_BYTES_PER_WEIGHT_BYTE + NCU_LMHEAD_LOGIT_WRITE_FRACTION * n * cfg["vocab_size"] * 4
+    serialised = gemm_bytes / 1e9 / (gemm_ms / 1e3) if gemm_ms > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "k_gemm_tc (all launches of a decode step)", "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "launches_per_step": gemm_n, "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1),
+                # diagnostic only: every launch bracketed by events, which serialises kernels that overlap in the
+                # real step and adds the launch gap to each; the sum can exceed the step itself
+                "serialised": {"achieved": serialised, "frac": serialised / peak, "avg_launch_us": 1e3 * gemm_ms / max(gemm_n, 1)}}
+    # traffic per launch: the captured read ratio applied to this step's weight bytes, plus the logits written
+    traffic = gemm_bytes * NCU_DRAM_BYTES_PER_WEIGHT_BYTE + NCU_LMHEAD_LOGIT_WRITE_FRACTION * n * cfg_rank["vocab_size"] * 4
     roofline["traffic"] = a.traffic if a.traffic is not None else traffic / max(gemm_n, 1)
     roofline["traffic_source"] = ("--traffic" if a.traffic is not None else
-                                  "ncu capture of two launches (profiles/ncu_gemm_tc_decode_shapes.md), scaled by weight bytes")
-    # the same step as it runs (graph + dependent launches): per kernel class the time from the previous
-    # kernel's last CTA leaving to this kernel's last CTA leaving, from in-kernel globaltimer stamps
+                                  "ncu capture of two launches (gate|up rows of one layer, LM head), scaled by weight bytes")
+    # the step as it runs (graph + dependent launches): per kernel class the time from the previous kernel's
+    # last CTA leaving to this kernel's last CTA leaving, from in-kernel globaltimer stamps. The roofline
+    # fraction of the dominant kernel is taken from these times.
     in_situ = None
     try:
         names, tl = sess.timeline(n)
@@ -278,93 +345,168 @@ def run_ours(a):
         in_situ = {"step_us": (int(tl[:, 5].max()) - int(tl[:, 0].min())) / 1e3,
                    "kernels": [{"kernel": nm, "launches": v[0], "us_per_launch": v[1] / v[0]}
                                for nm, v in sorted(agg.items(), key=lambda kv: -kv[1][1])]}
-        # the same roofline figure from these in-situ times (no event pairs between the kernels)
         gemm_us = sum(v[1] for nm, v in agg.items() if nm.startswith("gemm_tc:"))
         if gemm_us > 0:
-            roofline["achieved_in_situ"] = gemm_bytes / 1e9 / (gemm_us / 1e6)
-            roofline["frac_in_situ"] = roofline["achieved_in_situ"] / peak
+            roofline["achieved"] = gemm_bytes / 1e9 / (gemm_us / 1e6)
+            roofline["frac"] = roofline["achieved"] / peak
+            roofline["avg_launch_us"] = gemm_us / max(gemm_n, 1)
+            roofline["timing"] = "in-kernel globaltimer stamps inside the running step"
     except Exception as ex:  # a diagnostic: never fail the bench line for it
         in_situ = {"error": str(ex)}
+    if "frac" not in roofline:
+        roofline.update(achieved=serialised, frac=serialised / peak, avg_launch_us=1e3 * gemm_ms / max(gemm_n, 1),
+                        timing="CUDA events around every launch (serialised)")
     step_bytes = sum(v for k, v in kb.items() if k.startswith("gemm_tc:")) + kb["attn_decode"]
-    step_roofline = {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / 1e9 / (ms / K / 1e3),
+    step_roofline = {"algorithmic_bytes_per_step_per_gpu": step_bytes, "achieved": step_bytes / 1e9 / (ms / K / 1e3),
                      "peak": peak, "unit": "GB/s", "frac": step_bytes / 1e9 / (ms / K / 1e3) / peak}
+    tp_info = None
+    if tp_size > 1:
+        ar = prof.get("nccl_all_reduce", (0.0, 0))
+        step_prof_ms = sum(v[0] for v in prof.values()) / P
+        tp_info = {"tp_size": tp_size, "all_reduce_per_step": ar[1] / P, "all_reduce_us_per_call": 1e3 * ar[0] / max(ar[1], 1),
+                   "all_reduce_share_of_serialised_step": (ar[0] / P) / step_prof_ms if step_prof_ms > 0 else None,
+                   "all_reduce_bytes": n * cfg["hidden_size"] * 4,
+                   "per_rank_roofline_frac": step_roofline["frac"],
+                   "per_rank_roofline_frac_without_all_reduce": step_bytes / 1e9 / max(ms / K - ar[0] / P, 1e-6) * 1e3 / peak}
 
     # ---- end to end through the C ABI with host buffers (e2e)
     e2e = None
     if not a.no_e2e:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sess.qwen_reset()
         nxt, _ = sess.prefill(prompt_list)
         for _ in range(W):
             nxt, _ = sess.decode_step(nxt)
+        e2e_times = []
+        for _ in range(reps):
+            barrier()
+            e0.record(stream)
+            w0 = time.perf_counter()
+            for _ in range(K):
+                nxt, _ = sess.decode_step(nxt)  # host int32[n] in, host int32[n] out, every step
+            e1.record(stream)
+            barrier()
+            wall_ms = (time.perf_counter() - w0) * 1e3
+            e2e_times.append(max_over_ranks(max(e0.elapsed_time(e1), wall_ms)))
+        e2e_ms = float(np.median(e2e_times))
+        e2e = {"value": groups * n * K / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n * world,
+               "d2h_bytes_per_step": 4 * n * world, "ms_per_step": e2e_ms / K, "repetitions": reps}
+
+    # ---- data parallel at N > 1: every rank's tokens are checked, and 64 sequences in total (strong scaling)
+    dp_check, strong = None, None
+    if dist is not None and tp_size == 1:
+        mine = np.ascontiguousarray(np.asarray(toks_dev, dtype=np.int32))
+        sums = [None] * world
+        dist.all_gather_object(sums, int(mine.astype(np.int64).sum()))
+        other = 1 % world
+        box = [mine.tolist() if rank == other else None]
+        dist.broadcast_object_list(box, src=other)
+        same = None
+        if rank == 0:  # rank 0 decodes rank `other`'s shard itself: the tokens must be the same, bit for bit
+            s2 = tffn.Session(model, expert, max_batch=n, max_seq=a.prompt + W + K + 8, stream=stream.cuda_stream)
+            s2.set_launch_mode(a.launch_mode)
+            p2 = dp_prompts(other, n, a.prompt)
+            s2.prefill([p2[i] for i in range(n)])
+            s2.decode_run(n, W, want_tokens=False)
+            t2 = np.asarray(s2.decode_run(n, K, want_tokens=True), dtype=np.int32)
+            same = bool((t2 == np.asarray(box[0], dtype=np.int32).reshape(t2.shape)).all())
+            s2.free()
         barrier()
-        e0.record(stream)
-        w0 = time.perf_counter()
-        for _ in range(K):
-            nxt, _ = sess.decode_step(nxt)  # host int32[n] in, host int32[n] out, every step
-        e1.record(stream)
-        barrier()
-        wall_ms = (time.perf_counter() - w0) * 1e3
-        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
-        e2e = {"value": world * n * K / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n * world,
-               "d2h_bytes_per_step": 4 * n * world, "ms_per_step": e2e_ms / K}
+        dp_check = {"checksum_tokens_per_rank": sums, "rank0_reran_rank": other, "identical_tokens": same}
+        if n % world == 0 and n // world >= 1:
+            ns = n // world
+            s3 = tffn.Session(model, expert, max_batch=ns, max_seq=a.prompt + W + K * reps + 8, stream=stream.cuda_stream)
+            s3.set_launch_mode(a.launch_mode)
+            p3 = synth.prompts(ns, a.prompt, 1, first_seq=rank * ns)  # global sequences [rank*ns, (rank+1)*ns)
+            s3.prefill([p3[i] for i in range(ns)])
+            s3.decode_run(ns, W, want_tokens=False)
+            ms3, _, _, _ = timed_decode(s3, stream, ns, K, reps, barrier, max_over_ranks)
+            kb3 = kernel_bytes(cfg, True, ns, ctx_mid)
+            b3 = sum(v for k, v in kb3.items() if k.startswith("gemm_tc:")) + kb3["attn_decode"]
+            strong = {"value": n * K / (ms3 / 1e3), "unit": "tok/s", "total_sequences": n, "sequences_per_gpu": ns,
+                      "ms_per_step": ms3 / K, "per_gpu_roofline_frac": b3 / 1e9 / (ms3 / K / 1e3) / peak,
+                      "note": "every GPU still streams all weights per step: the aggregate HBM roofline grows only ~1.3x from 1 to 8 GPUs at 64 sequences"}
+            s3.free()
 
     # ---- batch 1 (configs[0]) on the same weights: 128-token prompt, greedy decode
     bs1 = None
-    if not a.no_bs1:
-        s1 = tffn.Session(model, expert, max_batch=1, max_seq=128 + W + a.bs1_steps + 8, stream=stream.cuda_stream)
+    if not a.no_bs1 and tp_size == 1:
+        s1 = tffn.Session(model, expert, max_batch=1, max_seq=128 + W + a.bs1_steps * 4 + 24, stream=stream.cuda_stream)
         s1.set_launch_mode(a.launch_mode)
         p1 = synth.prompts(1, 128, 0)[0]
         s1.prefill([p1])
         s1.decode_run(1, W, want_tokens=False)
-        barrier()
-        l0 = s1.launch_count()
-        e0.record(stream)
-        s1.decode_run(1, a.bs1_steps, want_tokens=False)
-        e1.record(stream)
-        barrier()
-        l1 = s1.launch_count() - l0
-        ms1 = max_over_ranks(e0.elapsed_time(e1))
+        ms1, _, _, l1 = timed_decode(s1, stream, 1, a.bs1_steps, 3, barrier, max_over_ranks)
         s1.profile(True)
         s1.decode_run(1, 8, want_tokens=False)
         prof1 = s1.profile_read()
         s1.profile(False)
-        ctx1 = 128 + W + a.bs1_steps / 2.0
+        ctx1 = 128 + W + a.bs1_steps * 1.5
         kb1 = kernel_bytes(cfg, True, 1, ctx1)
         tok_bytes = kb1["bs1_qkv"] + kb1["bs1_oproj"] + kb1["bs1_ffn"] + kb1["bs1_lmhead"] + kb1["attn_decode"]
-        ffn_ms = prof1.get("bs1_ffn", (0, 1))[0] / 8
         bs1 = {"value": world * a.bs1_steps / (ms1 / 1e3), "unit": "tok/s", "ms_per_token": ms1 / a.bs1_steps,
-               "steps": a.bs1_steps, "launch_mode": a.launch_mode, "gpu_launches": l1,
+               "steps": a.bs1_steps, "repetitions": 3, "launch_mode": a.launch_mode, "gpu_launches": l1,
                "algorithmic_bytes_per_token": tok_bytes,
                "roofline_frac_token": tok_bytes / 1e9 / (ms1 / a.bs1_steps / 1e3) / peak,
-               "dominant_kernel": {"kernel": "k_bs1_ffn", "ms_per_token": ffn_ms,
-                                   "achieved_gbs": kb1["bs1_ffn"] / 1e9 / (ffn_ms / 1e3) if ffn_ms else None,
-                                   "frac": (kb1["bs1_ffn"] / 1e9 / (ffn_ms / 1e3) / peak) if ffn_ms else None},
-               "kernels": [{"kernel": k, "ms_per_token": v[0] / 8, "launches_per_token": v[1] / 8}
-                           for k, v in sorted(prof1.items(), key=lambda kv: -kv[1][0])]}
+               "kernels_serialised": [{"kernel": k, "ms_per_token": v[0] / 8, "launches_per_token": v[1] / 8}
+                                      for k, v in sorted(prof1.items(), key=lambda kv: -kv[1][0])]}
+        try:  # the token as it runs: what each kernel class adds to it (in-kernel stamps, no event pairs)
+            names1, tl1 = s1.timeline(1)
+            tl1 = tl1.astype(np.int64)
+            agg1: dict = {}
+            prev = int(tl1[:, 0].min())
+            for nm, r in zip(names1, tl1):
+                e = agg1.setdefault(nm, [0, 0.0])
+                e[0] += 1
+                e[1] += (int(r[5]) - prev) / 1e3
+                prev = int(r[5])
+            bs1["kernels_in_situ"] = {"token_us": (int(tl1[:, 5].max()) - int(tl1[:, 0].min())) / 1e3,
+                                      "kernels": [{"kernel": nm, "launches": v[0], "us_per_launch": v[1] / v[0]}
+                                                  for nm, v in sorted(agg1.items(), key=lambda kv: -kv[1][1])]}
+            ffn_us = agg1.get("bs1_ffn", [0, 0.0])[1]
+            if ffn_us > 0:
+                bs1["dominant_kernel"] = {"kernel": "k_bs1_ffn", "us_per_token": ffn_us,
+                                          "achieved_gbs": kb1["bs1_ffn"] / 1e9 / (ffn_us / 1e6),
+                                          "frac": kb1["bs1_ffn"] / 1e9 / (ffn_us / 1e6) / peak}
+        except Exception as ex:
+            bs1["kernels_in_situ"] = {"error": str(ex)}
         s1.free()
+        if rank == 0 and world == 1 and not a.no_ref_bs1:
+            bs1["reference"] = reference_bs1(d, ep, 128, a.bs1_steps, 3)
+            if bs1["reference"] and "tok_s_best" in bs1["reference"]:
+                bs1["speedup_vs_reference_same_config"] = bs1["value"] / bs1["reference"]["tok_s_best"]
 
     clocks = sampler.stop() if sampler else None
 
     # ---- CPU baseline: the oracle (a port: the reference has no CPU path), rank 0, one GPU only
     cpu = None
     if rank == 0 and world == 1 and not a.no_cpu:
-        cpu = cpu_baseline(d, ep, a.cpu_prompt, a.cpu_tokens)
+        cpu = cpu_baseline(d, ep, a.cpu_prompt if a.cpu_prompt > 0 else a.prompt, a.cpu_tokens)
 
     if rank == 0:
+        weights_mb = model.weight_bytes(True) / 1e6
         line = {
-            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (seeded random-init weights of the Qwen2.5-0.5B shape + dense N(0,0.02) expert; "
-                    "uniform-random prompts)",
-            "config": {"workload": "configs[1]: Qwen2.5-0.5B+expert, batched greedy decode", "seqs_per_gpu": n,
-                       "prompt_len": a.prompt, "decode_steps": K, "parallelism": f"dp{world} (no collective)",
-                       "l2": "no flush: each step streams 1.6 GB of weights + KV, far more than the 126 MB L2"},
-            "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "step_roofline": step_roofline,
+            "metric": metric_name(a), "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp_size > 1 else "weak",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": f"synthetic (seeded random-init weights of the {a.shape} shape + dense N(0,0.02) expert; uniform-random prompts)",
+            "config": {"workload": workload_name(a), "seqs_per_gpu": n if tp_size == 1 else None,
+                       "seqs_total": n * groups, "prompt_len": a.prompt, "decode_steps": K, "repetitions": reps,
+                       "rep_ms": rep_ms,
+                       "parallelism": f"tp{tp_size} (fp32 all-reduce after o_proj and after the FFN)" if tp_size > 1 else f"dp{world} (no collective)",
+                       "l2": f"no flush: each step streams {weights_mb:.0f} MB of weights per GPU + KV, more than the 126 MB L2"},
+            "e2e": e2e, "gpu_launches": int(launches) * reps, "roofline": roofline, "step_roofline": step_roofline,
             "kernels": kernels, "kernels_in_situ": in_situ, "clocks": clocks, "cpu_baseline": cpu, "prefill_s": prefill_s,
             "checksum_tokens": int(np.asarray(toks_dev, dtype=np.int64).sum()),
         }
         if bs1:
             line["bs1"] = bs1
+        if tp_info:
+            line["tp"] = tp_info
+        if dp_check:
+            line["dp_check"] = dp_check
+        if strong:
+            line["strong_scaling"] = strong
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -385,14 +527,16 @@ def cpu_baseline(d: str, ep: str, prompt_len: int, n_tokens: int) -> dict:
         nxt = int(o.forward([nxt], want_logits=False, last_only=True)["argmax"][0])
     dt = time.perf_counter() - t0
     return {"value": n_tokens / dt, "unit": "tok/s", "cores": o.threads, "kind": "port",
-            "sample": f"1 sequence of the workload, {prompt_len}-token prompt then {n_tokens} greedy tokens; the reference "
-                      "decodes sequences one at a time, so its tok/s does not depend on the batch"}
+            "sample": f"1 sequence of the workload, {prompt_len}-token prompt (untimed) then {n_tokens} greedy tokens (timed); "
+                      "the reference decodes sequences one at a time, so its tok/s does not depend on the batch"}
 
 
 def run_reference(a):
     """The reference's own implementation of the path. It is CUDA-only (no CPU compute path), so
     the compiled reference (oracle/_ref/ref_driver: its unmodified sources + a token-file driver)
-    runs on the GPU when one is present; otherwise the CPU port is timed."""
+    runs on the GPU when one is present; otherwise the CPU port is timed. It has no batching: one of the
+    workload's sequences is decoded, K tokens per repetition, the same number of repetitions as this
+    library's arm, median over the repetitions."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -400,33 +544,35 @@ def run_reference(a):
     d, ep, cfg = ensure_model(a.shape)
     drv = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
     K, W = a.steps, a.warmup
+    reps = a.reps if a.reps > 0 else max(1, min(10, 256 // max(K, 1)))
     have_gpu = shutil.which("nvidia-smi") is not None and subprocess.call(
         ["nvidia-smi", "-L"], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) == 0
-    base = {"metric": METRIC, "unit": "tok/s", "n_gpus": a.gpus, "steps": K, "warmup": W, "higher_is_better": True,
+    base = {"metric": metric_name(a), "unit": "tok/s", "n_gpus": a.gpus, "steps": K, "warmup": W, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference", "data": "synthetic",
-            "config": {"workload": "configs[1]: Qwen2.5-0.5B+expert, batched greedy decode", "seqs_per_gpu": a.seqs,
-                       "prompt_len": a.prompt, "decode_steps": K}}
-    if os.path.exists(drv) and have_gpu:
+            "config": {"workload": workload_name(a), "seqs_per_gpu": a.seqs, "prompt_len": a.prompt, "decode_steps": K,
+                       "repetitions": reps,
+                       "same_config": False,
+                       "note": "the reference decodes one sequence at a time (no batching): one of the workload's sequences is timed"}}
+    if os.path.exists(drv) and have_gpu and cfg["num_hidden_layers"] <= 32:
         toks = synth.prompts(1, a.prompt, 1000)[0]
         tf = os.path.join(model_dir(a.shape), "ref_tokens.i32")
         toks.tofile(tf)
         out = os.path.join(model_dir(a.shape), "ref_out")
-        reps = 3
+        # the repetitions run inside one start of the driver (--time): it reloads the model each time it is started
         subprocess.check_call([drv, "--model", d, "--expert", ep, "--expert-scale", "0.1", "--max-seq",
                                str(a.prompt + K + W + 8), "--tokens", tf, "--prompt-len", str(a.prompt), "--new",
                                str(K), "--out", out, "--time", str(reps + 1)], stdout=subprocess.DEVNULL)
         with open(out + ".time.json") as f:
             t = json.load(f)
-        v = K / (t["decode_ms_best"] / 1e3)
-        line = dict(base, value=v, ms_per_step=t["decode_ms_best"] / K,
+        v = K / (t["decode_ms_mean"] / 1e3)
+        line = dict(base, value=v, ms_per_step=t["decode_ms_mean"] / K, value_best_repetition=K / (t["decode_ms_best"] / 1e3),
                     cpu_baseline={"value": v, "unit": "tok/s", "cores": 1, "kind": "reference",
                                   "sample": f"the reference's unmodified CUDA sources compiled for sm_100 (it has no CPU "
                                             f"path), its own loop: 1 of the {a.seqs} sequences, {a.prompt}-token prompt, "
-                                            f"{K} greedy tokens, best of {reps + 1} repetitions; it has no batching, so "
-                                            "the remaining sequences would run one after another at the same rate"},
+                                            f"{K} greedy tokens, mean of {reps + 1} repetitions"},
                     e2e={"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
     else:
-        c = cpu_baseline(d, ep, min(a.prompt, a.cpu_prompt), min(K, a.cpu_tokens))
+        c = cpu_baseline(d, ep, min(a.prompt, a.cpu_prompt if a.cpu_prompt > 0 else a.prompt), min(K, a.cpu_tokens))
         line = dict(base, value=c["value"], ms_per_step=1e3 / c["value"], cpu_baseline=c,
                     e2e={"value": c["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
     print(json.dumps(line), flush=True)
@@ -508,13 +654,16 @@ def main():
     ap.add_argument("--no-bs1", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--cpu-prompt", type=int, default=64)
-    ap.add_argument("--cpu-tokens", type=int, default=128)
+    ap.add_argument("--cpu-prompt", type=int, default=0, help="prompt length of the CPU baseline (0: the workload's)")
+    ap.add_argument("--cpu-tokens", type=int, default=64)
+    ap.add_argument("--reps", type=int, default=0, help="repetitions of the timed region (0: as many as fit 256 steps, at most 10)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (= number of ranks); 1: data parallel")
+    ap.add_argument("--no-ref-bs1", action="store_true", help="skip the reference run at the batch-1 configuration")
     ap.add_argument("--kernel-case", default="", choices=["", "gemm", "expert_forward"],
                     help="run only the tensor-core GEMM on the decode step's two largest shapes (gate|up rows, LM head) "
                          "through the op-level entry point and exit: the small program that ncu captures are taken from")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), if known")
+                    help="DRAM bytes per launch of the dominant kernel from an ncu capture, if known")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     if a.kernel_case == "expert_forward":

@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_bs1_qkv(Bs1Ctx c, Bs1Layer l
             bias1 = __bfloat162float(ly.bqkv[head * hd + i + half]);
         }
     }
-    pdl_wait();
+    if (warp == 0) pdl_wait();  // one waiting warp per CTA, see k_bs1_ffn
+    __syncthreads();
     if (threadIdx.x == 0) tl_mark(c.tl, 1);
     const bf16* hsrc = c.h_in;
     if (first) {
@@ -149,7 +150,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_bs1_oproj(Bs1Ctx c, Bs1Layer
     RowRegs<NCH> w0, w1;
     if (n0 < H) load_row<NCH>(w0, ly.wo + (size_t)n0 * H, H, lane);
     if (n0 + 1 < H) load_row<NCH>(w1, ly.wo + (size_t)(n0 + 1) * H, H, lane);
-    pdl_wait();
+    if (warp == 0) pdl_wait();  // one waiting warp per CTA, see k_bs1_ffn
+    __syncthreads();
     if (threadIdx.x == 0) tl_mark(c.tl, 1);
     if (n0 >= H) return;
     RowRegs<NCH> x;
@@ -167,7 +169,10 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_bs1_oproj(Bs1Ctx c, Bs1Layer
 }
 
 // ------------------------------------------------------------------------------------------ fused SwiGLU
-constexpr int kFfnWarps = 8;          // consumer warps; warp kFfnWarps is the copy producer
+// Consumer warps; warp kFfnWarps is the copy producer. A warp takes four records at a time and a CTA owns
+// 33 or 34 records of the 0.5B shape: nine warps take the nine chunks at once, eight would leave one warp
+// with two in a row.
+constexpr int kFfnWarps = 9;
 constexpr int kFfnThreads = (kFfnWarps + 1) * 32;
 constexpr int kSmsLeftToAttention = 4;
 
@@ -273,9 +278,10 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         return;
     }
 
-    // consumers
+    // consumers: one warp waits for the previous kernel, the others follow through the CTA barrier
     constexpr int NT = kFfnWarps * 32;
-    pdl_wait();
+    if (warp == 0) pdl_wait();
+    asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
     {
         RowRegs<NCH> xn;
         rmsnorm_regs<NCH>(xn, c.h, ly.ffn_norm, H, c.eps, lane);
@@ -493,7 +499,8 @@ __global__ void __launch_bounds__(kLmThreads, 1) k_bs1_lmhead(Bs1Ctx c, const bf
     }
 
     constexpr int NT = kLmWarps * 32;
-    pdl_wait();
+    if (warp == 0) pdl_wait();  // one waiting warp per CTA, see k_bs1_ffn
+    asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
     // final residual add (the last layer's FFN sums) + final RMSNorm, by the consumer threads together
     fold_norm_block<NT>(c.h_in, c.acc_in, final_norm, H, c.eps, nullptr, xs, s_val, (int)threadIdx.x,
                         [] { asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory"); });

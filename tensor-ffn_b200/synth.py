@@ -158,9 +158,29 @@ def write_tokenizer(dirpath: str, cfg: dict):
     return ids
 
 
+_TILE = {}
+
+
+def _tiled_bf16(seed, n: int, std: float) -> np.ndarray:
+    """n bf16 values ~ N(0, std) cut out of one seeded 32 Mi-value block at a seed-dependent offset (wrapping
+    around): as fast as a copy. For throughput runs on the largest shapes, where only sizes matter."""
+    if std not in _TILE:
+        _TILE[std] = _normal_bf16([99, int(std * 1e6)], 1 << 25, std)
+    blk = _TILE[std]
+    off = int(np.random.default_rng(seed).integers(0, blk.size))
+    out = np.empty(n, dtype=np.uint16)
+    pos = 0
+    while pos < n:
+        m = min(n - pos, blk.size - off)
+        out[pos:pos + m] = blk[off:off + m]
+        pos += m
+        off = 0
+    return out
+
+
 def write_model(dirpath: str, shape: str | dict = "tiny", seed: int = 1234, qkv_bias: bool = True,
                 norm_jitter: float = 0.0, shard_bytes: int = 4 << 30, threads: int = 0, head_norm_sigma: float = 0.0,
-                **cfg_over) -> dict:
+                fast: bool = False, **cfg_over) -> dict:
     """head_norm_sigma > 0 gives the vocabulary rows (embedding, and LM head when untied) log-normal
     norms: row v is scaled by exp(head_norm_sigma * z_v). With iid N(0, 0.02) rows the 150 k logits of a
     random-init model are nearly tied somewhere, so that top-1 agreement between two correct
@@ -191,6 +211,8 @@ def write_model(dirpath: str, shape: str | dict = "tiny", seed: int = 1234, qkv_
             z = np.random.default_rng([seed, i, 77]).standard_normal(shp[0], dtype=np.float32)
             w *= np.exp(np.float32(head_norm_sigma) * z)[:, None]
             return f32_to_bf16(w.reshape(-1))
+        if fast:
+            return _tiled_bf16([seed, i], n, 0.02)
         return _normal_bf16([seed, i], n, 0.02)
 
     threads = threads or min(16, os.cpu_count() or 1)
@@ -216,7 +238,7 @@ def write_model(dirpath: str, shape: str | dict = "tiny", seed: int = 1234, qkv_
 
 def write_expert(path: str, cfg: dict, seed: int = 4321, std: float = 0.02, threads: int = 0,
                  num_layers: int | None = None, hidden: int | None = None, inter: int | None = None,
-                 magic: int = EXPERT_MAGIC, truncate_bytes: int = 0):
+                 magic: int = EXPERT_MAGIC, truncate_bytes: int = 0, fast: bool = False):
     """Expert checkpoint: u32 magic, version, layers, hidden, intermediate; per layer gate, up, down fp32."""
     L = cfg["num_hidden_layers"] if num_layers is None else num_layers
     H = cfg["hidden_size"] if hidden is None else hidden
@@ -225,6 +247,8 @@ def write_expert(path: str, cfg: dict, seed: int = 4321, std: float = 0.02, thre
 
     def gen(args):
         l, m = args
+        if fast:  # see _tiled_bf16: a seeded block, cut at a per-matrix offset
+            return bf16_to_f32(_tiled_bf16([seed, l, m], I * H, std))
         rng = np.random.default_rng([seed, l, m])
         return (rng.standard_normal(I * H, dtype=np.float32) * np.float32(std))
 

@@ -274,6 +274,32 @@ class TpGroup:
             self.free()
 
 
+def tp_rendezvous(directory: str, tp_rank: int, tp_size: int, timeout_s: float = 60.0) -> bytes:
+    """File-based meeting point of a tensor-parallel group on one machine: rank 0 publishes the NCCL id,
+    every rank signs in and waits until all tp_size ranks have. A rank that never arrives makes the
+    others give up after timeout_s with TffnError(-6) instead of entering a collective that could not
+    complete. Returns the 128-byte id for TpGroup."""
+    import time
+    os.makedirs(directory, exist_ok=True)
+    idf = os.path.join(directory, "nccl_id")
+    if tp_rank == 0:
+        tmp = idf + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(tp_unique_id())
+        os.replace(tmp, idf)
+    with open(os.path.join(directory, f"rank{tp_rank}.here"), "w") as f:
+        f.write("1")
+    t_end = time.monotonic() + timeout_s
+    while True:
+        missing = [r for r in range(tp_size) if not os.path.exists(os.path.join(directory, f"rank{r}.here"))]
+        if not missing and os.path.exists(idf):
+            with open(idf, "rb") as f:
+                return f.read()
+        if time.monotonic() > t_end:
+            raise TffnError(-6, f"tensor-parallel rendezvous timed out after {timeout_s:.0f} s: ranks {missing} of {tp_size} never arrived")
+        time.sleep(0.02)
+
+
 def tp_partition(cfg: Config, tp_rank: int, tp_size: int) -> dict:
     """what rank tp_rank of tp_size owns (host-only arithmetic): heads, intermediate rows, LM-head rows"""
     out = (ctypes.c_int32 * 8)()

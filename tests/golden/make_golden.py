@@ -11,6 +11,11 @@ call, then teacher-forced single-token calls) and stores what the reference prod
 all-row prompt logits + one logits row per decode step, the greedy picks, and the residual
 stream after every layer for the prompt. The model files are not stored: they are a pure
 function of the seeds recorded in the fixture.
+
+It also stores what the TRAINER's own expert_forward (trainer/src/model/ffn_expert.cu:151-175, through
+oracle/_ref/ref_trainer_driver) returns for seeded training-shaped inputs [layers, batch_tokens, hidden] and
+the seeded expert weights of two shapes: the fixtures trainer_expert_forward_*.npz pin the restatement
+(oracle.expert_forward_ref) that tffn_expert_forward is checked against.
 """
 import argparse
 import os
@@ -23,6 +28,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, os.path.join(ROOT, "tensor-ffn_b200"))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 P, N = 16, 6  # prompt tokens, teacher-forced decode tokens
 MODEL_SEED, EXPERT_SEED, NORM_JITTER = 1234, 4321, 0.1
@@ -61,6 +67,33 @@ def main():
                                     model_seed=MODEL_SEED, expert_seed=EXPERT_SEED, norm_jitter=NORM_JITTER,
                                     qkv_bias=bias, expert=expert, expert_scale=0.1)
                 print("wrote", name, expert, logits.shape, flush=True)
+    trainer_driver = os.path.join(os.path.dirname(a.driver), "ref_trainer_driver")
+    if os.path.exists(trainer_driver):
+        trainer_expert_forward(a.out, trainer_driver)
+
+
+def trainer_expert_forward(out_dir, driver):
+    """fixtures of the trainer's expert_forward: x (bf16 bits), out (fp32), the seeds of the expert weights"""
+    import synth
+    from conftest import SHAPES
+    for name, T in (("tiny", 37), ("mini05", 64)):
+        shape, _ = SHAPES[name]
+        cfg = synth.make_config(shape)
+        H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+        with tempfile.TemporaryDirectory() as tmp:
+            ep = os.path.join(tmp, "expert.bin")
+            synth.write_expert(ep, cfg, seed=EXPERT_SEED)
+            data = np.memmap(ep, dtype=np.float32, mode="r", offset=20, shape=(L, 3, I * H))
+            w = synth.f32_to_bf16(np.ascontiguousarray(data).reshape(-1))  # RNE, as checkpoint_load casts
+            x = synth.f32_to_bf16(np.random.default_rng([77, T]).standard_normal((L, T, H), dtype=np.float32))
+            wf, xf, of = (os.path.join(tmp, n) for n in ("w.bf16", "x.bf16", "out.f32"))
+            w.tofile(wf)
+            x.tofile(xf)
+            subprocess.check_call([driver, str(L), str(H), str(I), str(T), wf, xf, of])
+            out = np.fromfile(of, dtype=np.float32).reshape(L, T, H)
+        np.savez_compressed(os.path.join(out_dir, f"trainer_expert_forward_{name}.npz"), shape_name=name, x=x, out=out,
+                            batch_tokens=T, expert_seed=EXPERT_SEED, scale=0.01)
+        print("wrote trainer expert_forward", name, out.shape, float(np.abs(out).max()), flush=True)
 
 
 if __name__ == "__main__":

@@ -28,7 +28,41 @@ def _model_for(g, tmp_path):
 
 
 def test_golden_fixtures_exist():
-    assert len(GOLDEN) == 6, "expected base+expert fixtures for tiny, tiny128 and mini05"
+    assert len(GOLDEN) >= 6, "expected base+expert fixtures for tiny, tiny128 and mini05 (and mini_s)"
+
+
+TRAINER_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "trainer_expert_forward_*.npz")))
+
+
+@pytest.mark.parametrize("path", TRAINER_GOLDEN, ids=[os.path.basename(p)[23:-4] for p in TRAINER_GOLDEN])
+def test_expert_forward_restatement_matches_the_trainer(path, tmp_path):
+    """oracle.expert_forward_ref (the checker of tffn_expert_forward) against what the trainer's own
+    expert_forward (trainer/src/model/ffn_expert.cu:151-175, unmodified sources, run on a B200) returned for the
+    same seeded weights and inputs. fp32 accumulation order differs (cuBLAS vs numpy), so single bf16 rounding
+    flips of gate / up / act occur: maximum error <= 2e-2 of the largest value, mean error <= 1e-3."""
+    import oracle
+    import synth
+    from conftest import SHAPES
+    g = np.load(path)
+    shape, _ = SHAPES[str(g["shape_name"])]
+    cfg = synth.make_config(shape)
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    ep = str(tmp_path / "expert.bin")
+    synth.write_expert(ep, cfg, seed=int(g["expert_seed"]))
+    _, _, _, data = oracle.read_expert(ep)
+    x, want = g["x"], g["out"]
+    assert x.shape == (L, int(g["batch_tokens"]), H) and want.shape == x.shape
+    for l in range(L):
+        w = [synth.f32_to_bf16(np.ascontiguousarray(data[l, k])) for k in range(3)]
+        got = oracle.expert_forward_ref(x[l], w[0].reshape(I, H), w[1].reshape(I, H), w[2].reshape(H, I), float(g["scale"]))
+        scale = np.abs(want[l]).max()
+        assert scale > 0
+        assert np.abs(got - want[l]).max() / scale <= 2e-2, l
+        assert np.abs(got - want[l]).mean() / scale <= 1e-3, l
+
+
+def test_trainer_fixtures_exist():
+    assert len(TRAINER_GOLDEN) == 2, "expected trainer expert_forward fixtures for tiny and mini05"
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[4:-4] for p in GOLDEN])
