@@ -134,6 +134,30 @@ int tffn_tokenizer_decode(const tffn_tokenizer* t, const uint32_t* ids, int n, c
     });
     return rc < 0 ? rc : len;
 }
+int tffn_tokenizer_encode_bpe(const tffn_tokenizer* t, const char* text, uint32_t* ids, int cap) {
+    int n = 0;
+    int rc = guard([&] {
+        need(t && text, "NULL argument");
+        auto v = t->t.encode_bpe(text);
+        n = (int)v.size();
+        for (int i = 0; i < n && i < cap && ids; ++i) ids[i] = v[i];
+    });
+    return rc < 0 ? rc : n;
+}
+int tffn_tokenizer_decode_bpe(const tffn_tokenizer* t, const uint32_t* ids, int n, char* out, int cap) {
+    int len = 0;
+    int rc = guard([&] {
+        need(t && (ids || n == 0) && n >= 0, "bad argument");
+        std::string s = t->t.decode_bpe(std::vector<uint32_t>(ids, ids + n));
+        len = (int)s.size();
+        if (out && cap > 0) {
+            int m = len < cap - 1 ? len : cap - 1;
+            memcpy(out, s.data(), m);
+            out[m] = 0;
+        }
+    });
+    return rc < 0 ? rc : len;
+}
 int tffn_tokenizer_token_id(const tffn_tokenizer* t, const char* token, uint32_t* id) {
     return guard([&] {
         need(t && token && id, "NULL argument");

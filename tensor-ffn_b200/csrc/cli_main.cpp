@@ -3,7 +3,9 @@
 // "inference" word is accepted so that `tensor-ffn inference --model ...` from the
 // reference's README works too. Extra flags (not in the reference): --prompt-ids <file> (raw
 // int32 ids instead of --prompt), --ignore-eos, --device <N>, --host-sampling (with --temperature: sample
-// on the host from downloaded logits as the reference does, instead of on the device).
+// on the host from downloaded logits as the reference does, instead of on the device), --bpe (tokenise the
+// prompt and print the output with the byte-level BPE that tokenizer.json specifies, instead of the
+// reference's encoder, which drops spaces and newlines).
 // The usage text, the flag scanning, the ChatML sequence, the stdout protocol and the host sampler
 // are the reference's own (inference/src/main.cpp:17-63, 127-144, 157-198), reproduced on purpose:
 // they ARE the command-line contract. What differs is what runs underneath: the six calls into the
@@ -96,6 +98,7 @@ int main(int argc, char** argv) {
     int device = get_flag_i(argc, argv, "--device", 0);
     bool use_chat = has_switch(argc, argv, "--chat");
     bool ignore_eos = has_switch(argc, argv, "--ignore-eos");
+    bool bpe = has_switch(argc, argv, "--bpe");
 
     if (model_dir.empty() || (prompt.empty() && ids_path.empty())) {
         fprintf(stderr, "--model and --prompt are required\n");
@@ -120,11 +123,12 @@ int main(int argc, char** argv) {
 
     std::vector<uint32_t> prompt_ids;
     auto push_text = [&](const std::string& text) {
-        int n = tffn_tokenizer_encode(tok, text.c_str(), nullptr, 0);
+        auto enc = bpe ? tffn_tokenizer_encode_bpe : tffn_tokenizer_encode;
+        int n = enc(tok, text.c_str(), nullptr, 0);
         if (n <= 0) return;
         size_t o = prompt_ids.size();
         prompt_ids.resize(o + n);
-        tffn_tokenizer_encode(tok, text.c_str(), prompt_ids.data() + o, n);
+        enc(tok, text.c_str(), prompt_ids.data() + o, n);
     };
     auto push_special = [&](const char* name) {
         uint32_t id = 0;
@@ -190,7 +194,7 @@ int main(int argc, char** argv) {
         }
         char text[512];
         uint32_t id = (uint32_t)next;
-        tffn_tokenizer_decode(tok, &id, 1, text, sizeof text);
+        (bpe ? tffn_tokenizer_decode_bpe : tffn_tokenizer_decode)(tok, &id, 1, text, sizeof text);
         printf("%s", text);
         fflush(stdout);
         int32_t fed = next;

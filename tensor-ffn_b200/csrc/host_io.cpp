@@ -324,7 +324,9 @@ void Tokenizer::load(const std::string& dir) {
             if (!c || !id) continue;
             token_to_id_[c->str] = (uint32_t)id->as_int();
             id_to_token_[(uint32_t)id->as_int()] = c->str;
+            if (!c->str.empty()) added_.push_back(c->str);
         }
+        std::sort(added_.begin(), added_.end(), [](const std::string& a, const std::string& b) { return a.size() > b.size(); });
     }
     std::string g = read_text_file(dir + "/generation_config.json", &ok);
     if (ok) {
@@ -378,6 +380,216 @@ std::vector<uint32_t> Tokenizer::encode(const std::string& text) const {
         }
     }
     return ids;
+}
+
+// ---------------------------------------------------------------- byte-level BPE as tokenizer.json specifies it
+namespace {
+
+#include "unicode_tables.inc"
+
+bool in_ranges(const uint32_t (*r)[2], size_t n, uint32_t cp) {
+    size_t lo = 0, hi = n;
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (cp < r[mid][0]) hi = mid;
+        else if (cp > r[mid][1]) lo = mid + 1;
+        else return true;
+    }
+    return false;
+}
+bool is_letter(uint32_t cp) { return in_ranges(kUnicodeLetter, sizeof kUnicodeLetter / sizeof kUnicodeLetter[0], cp); }
+bool is_number(uint32_t cp) { return in_ranges(kUnicodeNumber, sizeof kUnicodeNumber / sizeof kUnicodeNumber[0], cp); }
+bool is_white(uint32_t cp) {
+    for (uint32_t w : kUnicodeWhite)
+        if (w == cp) return true;
+    return false;
+}
+bool is_newline(uint32_t cp) { return cp == '\r' || cp == '\n'; }
+
+// GPT-2's bytes_to_unicode: printable Latin-1 bytes stand for themselves, the other 68 bytes for U+0100 ...
+struct ByteMap {
+    uint32_t to_cp[256];
+    std::unordered_map<uint32_t, uint8_t> to_byte;
+    ByteMap() {
+        int n = 0;
+        for (int b = 0; b < 256; ++b) {
+            const bool keep = (b >= 0x21 && b <= 0x7E) || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
+            to_cp[b] = keep ? (uint32_t)b : (uint32_t)(256 + n++);
+            to_byte[to_cp[b]] = (uint8_t)b;
+        }
+    }
+};
+const ByteMap& byte_map() {
+    static const ByteMap m;
+    return m;
+}
+void put_utf8(std::string& s, uint32_t cp) {
+    if (cp < 0x80) {
+        s += (char)cp;
+    } else if (cp < 0x800) {
+        s += (char)(0xC0 | (cp >> 6));
+        s += (char)(0x80 | (cp & 0x3F));
+    } else if (cp < 0x10000) {
+        s += (char)(0xE0 | (cp >> 12));
+        s += (char)(0x80 | ((cp >> 6) & 0x3F));
+        s += (char)(0x80 | (cp & 0x3F));
+    } else {
+        s += (char)(0xF0 | (cp >> 18));
+        s += (char)(0x80 | ((cp >> 12) & 0x3F));
+        s += (char)(0x80 | ((cp >> 6) & 0x3F));
+        s += (char)(0x80 | (cp & 0x3F));
+    }
+}
+// code points of a UTF-8 string with the byte offset of each (a malformed byte counts as one code point)
+void utf8_points(const std::string& s, std::vector<uint32_t>& cps, std::vector<size_t>& offs) {
+    for (size_t i = 0; i < s.size();) {
+        const unsigned char c = (unsigned char)s[i];
+        int len = c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : (c >> 3) == 30 ? 4 : 1;
+        if (i + len > s.size()) len = 1;
+        uint32_t cp = len == 1 ? c : (c & (0xFF >> (len + 1)));
+        for (int k = 1; k < len; ++k) {
+            if (((unsigned char)s[i + k] & 0xC0) != 0x80) { len = 1; cp = c; break; }
+            cp = (cp << 6) | ((unsigned char)s[i + k] & 0x3F);
+        }
+        cps.push_back(cp);
+        offs.push_back(i);
+        i += len;
+    }
+    offs.push_back(s.size());
+}
+
+// end (exclusive, in code points) of the pre-tokenizer match that starts at i: the pattern's alternatives in order
+size_t pretok_match(const std::vector<uint32_t>& cp, size_t i) {
+    const size_t n = cp.size();
+    auto lower = [](uint32_t c) { return (c >= 'A' && c <= 'Z') ? c + 32 : c; };
+    if (cp[i] == '\'' && i + 1 < n) {  // (?i:'s|'t|'re|'ve|'m|'ll|'d)
+        const uint32_t a = lower(cp[i + 1]), b = i + 2 < n ? lower(cp[i + 2]) : 0;
+        if (a == 's' || a == 't') return i + 2;
+        if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e')) return i + 3;
+        if (a == 'm') return i + 2;
+        if (a == 'l' && b == 'l') return i + 3;
+        if (a == 'd') return i + 2;
+    }
+    {  // [^\r\n\p{L}\p{N}]?\p{L}+
+        size_t j = i;
+        if (!is_letter(cp[j]) && !is_newline(cp[j]) && !is_number(cp[j]) && j + 1 < n && is_letter(cp[j + 1])) ++j;
+        if (is_letter(cp[j])) {
+            while (j < n && is_letter(cp[j])) ++j;
+            return j;
+        }
+    }
+    if (is_number(cp[i])) return i + 1;  // \p{N}
+    {  //  ?[^\s\p{L}\p{N}]+[\r\n]*
+        size_t j = i;
+        auto other = [&](size_t k) { return !is_white(cp[k]) && !is_letter(cp[k]) && !is_number(cp[k]); };
+        if (cp[j] == ' ' && j + 1 < n && other(j + 1)) ++j;
+        if (other(j)) {
+            while (j < n && other(j)) ++j;
+            while (j < n && is_newline(cp[j])) ++j;
+            return j;
+        }
+    }
+    if (is_white(cp[i])) {
+        size_t e = i;
+        while (e < n && is_white(cp[e])) ++e;
+        size_t last_nl = n;  // \s*[\r\n]+ : up to and including the last newline of the run
+        for (size_t k = i; k < e; ++k)
+            if (is_newline(cp[k])) last_nl = k;
+        if (last_nl != n) return last_nl + 1;
+        if (e == n) return e;      // \s+(?!\S) at the end of the text
+        if (e - 1 > i) return e - 1;  // \s+(?!\S): leave the last blank to the next piece
+        return e;                   // \s+
+    }
+    return i + 1;
+}
+
+}  // namespace
+
+void Tokenizer::bpe_piece(const std::string& bytes, std::vector<uint32_t>& out) const {
+    const ByteMap& bm = byte_map();
+    std::vector<uint32_t> ids;
+    ids.reserve(bytes.size());
+    for (unsigned char b : bytes) {
+        std::string ch;
+        put_utf8(ch, bm.to_cp[b]);
+        auto it = token_to_id_.find(ch);
+        if (it == token_to_id_.end()) continue;  // a vocabulary without the byte alphabet: nothing stands for this byte
+        ids.push_back(it->second);
+    }
+    while (ids.size() > 1) {
+        uint32_t best_rank = UINT32_MAX;
+        for (size_t i = 0; i + 1 < ids.size(); ++i) {
+            auto it = merge_rank_.find((uint64_t)ids[i] << 32 | ids[i + 1]);
+            if (it != merge_rank_.end() && it->second < best_rank) best_rank = it->second;
+        }
+        if (best_rank == UINT32_MAX) break;
+        const auto& pr = merges_[best_rank];
+        auto it = token_to_id_.find(id_to_token_.at(pr.first) + id_to_token_.at(pr.second));
+        if (it == token_to_id_.end()) break;
+        // every occurrence of the pair, left to right (what one pass of the standard algorithm does)
+        std::vector<uint32_t> next;
+        next.reserve(ids.size());
+        for (size_t i = 0; i < ids.size();) {
+            if (i + 1 < ids.size() && ids[i] == pr.first && ids[i + 1] == pr.second) {
+                next.push_back(it->second);
+                i += 2;
+            } else {
+                next.push_back(ids[i++]);
+            }
+        }
+        ids.swap(next);
+    }
+    out.insert(out.end(), ids.begin(), ids.end());
+}
+
+std::vector<uint32_t> Tokenizer::encode_bpe(const std::string& text) const {
+    std::vector<uint32_t> out;
+    auto plain = [&](const std::string& t) {
+        if (t.empty()) return;
+        std::vector<uint32_t> cps;
+        std::vector<size_t> offs;
+        utf8_points(t, cps, offs);
+        for (size_t i = 0; i < cps.size();) {
+            const size_t e = pretok_match(cps, i);
+            bpe_piece(t.substr(offs[i], offs[e] - offs[i]), out);
+            i = e;
+        }
+    };
+    size_t start = 0, i = 0;
+    while (i < text.size()) {  // added tokens (the ChatML markers ...) stand for themselves
+        const std::string* hit = nullptr;
+        for (const std::string& a : added_)
+            if (text.compare(i, a.size(), a) == 0) { hit = &a; break; }
+        if (!hit) { ++i; continue; }
+        plain(text.substr(start, i - start));
+        out.push_back(token_to_id_.at(*hit));
+        i += hit->size();
+        start = i;
+    }
+    plain(text.substr(start));
+    return out;
+}
+
+std::string Tokenizer::decode_bpe(const std::vector<uint32_t>& ids) const {
+    const ByteMap& bm = byte_map();
+    std::string out;
+    for (uint32_t id : ids) {
+        auto it = id_to_token_.find(id);
+        if (it == id_to_token_.end()) continue;
+        const std::string& tok = it->second;
+        if (std::find(added_.begin(), added_.end(), tok) != added_.end()) {
+            out += tok;
+            continue;
+        }
+        std::vector<uint32_t> cps;
+        std::vector<size_t> offs;
+        utf8_points(tok, cps, offs);
+        for (uint32_t cp : cps) {
+            auto b = bm.to_byte.find(cp);
+            if (b != bm.to_byte.end()) out += (char)b->second;
+        }
+    }
+    return out;
 }
 
 std::string Tokenizer::decode(const std::vector<uint32_t>& ids) const {

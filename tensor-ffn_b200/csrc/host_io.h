@@ -137,6 +137,15 @@ public:
     void load(const std::string& model_dir);
     std::vector<uint32_t> encode(const std::string& text) const;
     std::string decode(const std::vector<uint32_t>& ids) const;
+    // The tokenisation Qwen2's tokenizer.json actually specifies, which the reference's encode() above does not
+    // implement (it has no pre-tokenizer and no byte-to-unicode map, so spaces and newlines are dropped:
+    // inference/src/io/tokenizer.cpp:86-108; the authors work around it with HF in tools/tokenize_correctly.py):
+    // added tokens are cut out verbatim, the rest is split by the Qwen2 pre-tokenizer pattern
+    //   (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
+    // every piece's UTF-8 bytes go through GPT-2's byte-to-unicode map, and the merges are applied lowest
+    // rank first. decode_bpe maps the characters back to bytes.
+    std::vector<uint32_t> encode_bpe(const std::string& text) const;
+    std::string decode_bpe(const std::vector<uint32_t>& ids) const;
     uint32_t get_id(const std::string& token) const;  // 0 and a warning on stderr when absent
     uint32_t eos_id = 151645, bos_id = 151643, pad_id = 151643;
     size_t vocab_size() const { return token_to_id_.size(); }
@@ -146,6 +155,8 @@ private:
     std::unordered_map<uint32_t, std::string> id_to_token_;
     std::vector<std::pair<uint32_t, uint32_t>> merges_;
     std::unordered_map<uint64_t, uint32_t> merge_rank_;
+    std::vector<std::string> added_;  // added tokens, longest first
+    void bpe_piece(const std::string& bytes, std::vector<uint32_t>& out) const;
 };
 
 std::string read_text_file(const std::string& path, bool* ok);

@@ -58,6 +58,8 @@ _SIGS = {
     "tffn_tokenizer_free": (None, [_vp]),
     "tffn_tokenizer_encode": (_i, [_vp, _cp, _vp, _i]),
     "tffn_tokenizer_decode": (_i, [_vp, _vp, _i, _vp, _i]),
+    "tffn_tokenizer_encode_bpe": (_i, [_vp, _cp, _vp, _i]),
+    "tffn_tokenizer_decode_bpe": (_i, [_vp, _vp, _i, _vp, _i]),
     "tffn_tokenizer_token_id": (_i, [_vp, _cp, ctypes.POINTER(ctypes.c_uint32)]),
     "tffn_tokenizer_special": (_i, [_vp] + [ctypes.POINTER(ctypes.c_uint32)] * 3),
     "tffn_model_load": (_i, [_cp, _i, _i, _i, _pp]),
@@ -179,6 +181,21 @@ class Tokenizer:
         n = _check(_L.tffn_tokenizer_decode(self._h, a.ctypes.data, a.size, None, 0))
         buf = ctypes.create_string_buffer(n + 1)
         _check(_L.tffn_tokenizer_decode(self._h, a.ctypes.data, a.size, buf, n + 1))
+        return buf.raw[:n].decode("utf-8", "replace")
+
+    def encode_bpe(self, text: str) -> list[int]:
+        """the byte-level BPE tokenizer.json specifies (not the reference's space-dropping encoder)"""
+        raw = text.encode("utf-8")
+        n = _check(_L.tffn_tokenizer_encode_bpe(self._h, raw, None, 0))
+        ids = np.zeros(max(n, 1), dtype=np.uint32)
+        _check(_L.tffn_tokenizer_encode_bpe(self._h, raw, ids.ctypes.data, n))
+        return [int(x) for x in ids[:n]]
+
+    def decode_bpe(self, ids) -> str:
+        a = np.ascontiguousarray(ids, dtype=np.uint32)
+        n = _check(_L.tffn_tokenizer_decode_bpe(self._h, a.ctypes.data, a.size, None, 0))
+        buf = ctypes.create_string_buffer(n + 1)
+        _check(_L.tffn_tokenizer_decode_bpe(self._h, a.ctypes.data, a.size, buf, n + 1))
         return buf.raw[:n].decode("utf-8", "replace")
 
     def get_id(self, token: str) -> int:

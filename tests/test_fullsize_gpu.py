@@ -147,8 +147,10 @@ def assert_bars(rep, targets, peaked):
     deeper shapes with a random teacher sit at 3.4e-2 .. 5.1e-2 for all three pairs alike.
     Top-1 >= 99 %: raw on the peaked weights with the greedy teacher stream (peaked = True); otherwise with
     the near-ties of the reference excused (a pick that differs must lie within twice the observed logit
-    error of the reference's own), and raw no more than three points below the reference-vs-oracle figure
-    (93 % where that is unknown; with fewer than 100 rows: at most one row may differ).
+    error of the reference's own), and raw no more than three binomial standard errors (for the number of
+    rows compared) below the reference-vs-oracle rate (96 % where the case has no reference run; a rate above
+    98 % counts as 98 %): with ~100 rows one row is a whole point, and the three pairs have scattered between
+    92 % and 97 % on the same inputs.
     Hidden states: the residual stream is rounded to bf16 twice per layer, so two implementations that
     differ only in summation order drift apart like a random walk, about 2^-8 * sqrt(2 * layer) of the
     largest element (measured reference-vs-oracle on the 0.5B shape: 0.3 % after layer 1, 2.1-2.7 % after
@@ -164,8 +166,8 @@ def assert_bars(rep, targets, peaked):
             assert rep[t + "_top1_raw"] >= TOP1, (t, rep)
         else:
             assert rep[t + "_top1"] >= TOP1, (t, rep)
-            raw_floor = min(0.95, rep.get("oracle_vs_reference_top1_raw", 0.96) - 0.03)
-            assert rep[t + "_top1_raw"] >= raw_floor if rows >= 100 else rep[t + "_top1_raw"] * rows >= rows - 1.01, (t, rep)
+            p0 = min(0.98, rep.get("oracle_vs_reference_top1_raw", 0.96))
+            assert rep[t + "_top1_raw"] >= p0 - 3.0 * (p0 * (1.0 - p0) / rows) ** 0.5, (t, rep)
         if t + "_hidden_by_layer" in rep:
             fm = rep.get("oracle_vs_reference_hidden_by_layer")
             fl = rep.get("oracle_vs_reference_hidden_l2_by_layer")
@@ -361,7 +363,7 @@ def _large_shape_case(shape, P_long, P_short, N_long, batch, ref_layers, tmp_pat
         e.free()
         m.free()
         print("PARITY", shape, f"first {ref_layers} layers" if ref_layers < L else "all layers", rep)
-        assert_bars(rep, targets, False)  # random teacher stream: near-ties excused, raw >= 95 %
+        assert_bars(rep, targets, False)  # random teacher stream: near-ties excused, raw within 3 sigma of the floor
         if ref_layers < L:  # (3)
             rep3 = {}
             m = tffn.qwen_load(d)
