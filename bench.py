@@ -271,6 +271,8 @@ def run_ours(a):
     expert = tffn.checkpoint_load(ep, model, 0.1)
     sess = tffn.Session(model, expert, max_batch=n, max_seq=max_seq, stream=stream.cuda_stream, tp=group)
     sess.set_launch_mode(a.launch_mode)
+    if tp_size > 1 and a.tp_nccl:
+        sess.set_tp_fused(False)
     # data parallel: distinct sequences on every rank; tensor parallel: the same sequences on every rank
     prompts = dp_prompts(0 if tp_size > 1 else rank, n, a.prompt)
     prompt_list = [prompts[i] for i in range(n)]
@@ -361,9 +363,12 @@ def run_ours(a):
                      "peak": peak, "unit": "GB/s", "frac": step_bytes / 1e9 / (ms / K / 1e3) / peak}
     tp_info = None
     if tp_size > 1:
-        ar = prof.get("nccl_all_reduce", (0.0, 0))
+        ar = prof.get("tp_all_reduce", (0.0, 0))
         step_prof_ms = sum(v[0] for v in prof.values()) / P
-        tp_info = {"tp_size": tp_size, "all_reduce_per_step": ar[1] / P, "all_reduce_us_per_call": 1e3 * ar[0] / max(ar[1], 1),
+        tp_info = {"tp_size": tp_size,
+                   "exchange": "ncclAllReduce (fp32, in place)" if a.tp_nccl else
+                   "peer memory: flag hand-shake, then every rank's residual/RMSNorm kernel loads all ranks' fp32 partial sums over NVLink and adds them in rank order",
+                   "all_reduce_per_step": ar[1] / P, "all_reduce_us_per_call": 1e3 * ar[0] / max(ar[1], 1),
                    "all_reduce_share_of_serialised_step": (ar[0] / P) / step_prof_ms if step_prof_ms > 0 else None,
                    "all_reduce_bytes": n * cfg["hidden_size"] * 4,
                    "per_rank_roofline_frac": step_roofline["frac"],
@@ -658,6 +663,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=64)
     ap.add_argument("--reps", type=int, default=0, help="repetitions of the timed region (0: as many as fit 256 steps, at most 10)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (= number of ranks); 1: data parallel")
+    ap.add_argument("--tp-nccl", action="store_true", help="with --tp: every all-reduce through NCCL instead of the peer windows")
     ap.add_argument("--no-ref-bs1", action="store_true", help="skip the reference run at the batch-1 configuration")
     ap.add_argument("--kernel-case", default="", choices=["", "gemm", "expert_forward"],
                     help="run only the tensor-core GEMM on the decode step's two largest shapes (gate|up rows, LM head) "

@@ -128,10 +128,18 @@ void tffn_session_free(tffn_session* s);
  * tffn_expert_load, and creates its session with tffn_session_create_tp. All ranks then make the
  * same tffn_prefill / tffn_decode_step / tffn_decode_run calls with the same arguments; each returns
  * the same tokens (and full logits) on every rank. Inside a step the ranks' partial sums of o_proj
- * and of the down projections (base + scale * expert, summed locally first) are all-reduced in
- * fp32 with NCCL over NVLink before the one bf16 rounding of the residual add, and the greedy pick
- * exchanges one (max, index) pair per sequence and rank. Sampling and tffn_expert_forward are not
- * available on a tensor-parallel model. NCCL (libnccl.so.2) is opened at run time. */
+ * and of the down projections (base + scale * expert, summed locally first) are summed over the ranks in
+ * fp32 before the one bf16 rounding of the residual add, and the greedy pick exchanges one (max, index)
+ * pair per sequence and rank. Launches of up to 256 tokens (decode) exchange the partial sums through peer
+ * memory over NVLink: every rank exports an exchange window (CUDA IPC, so the ranks must be processes on one
+ * machine whose GPUs have peer access), the projections leave their fp32 partial sums in their own rank's
+ * window, and the row kernel that adds the residual and forms the next RMSNorm first hand-shakes with its
+ * peers through flags in those windows (bounded wait: a peer that never arrives gives TFFN_ERR_DEVICE
+ * status after 10 s, not a hang), then loads every rank's part over NVLink and adds them in rank order; the
+ * greedy pick's candidates are stored into every rank's window and fenced by the storing thread. Larger launches
+ * (prefill) use ncclAllReduce. Creating and freeing a tensor-parallel session are collective calls.
+ * Sampling and tffn_expert_forward are not available on a tensor-parallel model. NCCL (libnccl.so.2) is
+ * opened at run time. */
 typedef struct tffn_tp tffn_tp;
 int tffn_tp_unique_id(uint8_t* id128);
 int tffn_tp_create(const uint8_t* id128, int tp_rank, int tp_size, int device, tffn_tp** out);
@@ -143,6 +151,9 @@ void tffn_tp_free(tffn_tp* tp);
 int tffn_tp_partition(const tffn_config* cfg, int tp_rank, int tp_size, int32_t* out8);
 int tffn_session_create_tp(const tffn_model* m, const tffn_expert* expert, int max_batch, int max_seq, void* cuda_stream,
                            tffn_tp* tp, tffn_session** out);
+/* on = 0: every all-reduce of this session through NCCL, also the decode-sized ones (all ranks must choose
+ * alike); default 1 */
+int tffn_session_set_tp_fused(tffn_session* s, int on);
 /* qwen_reset (qwen.cu:174) for one slot, or for all with slot = -1: frees the slot's pages. */
 int tffn_session_reset(tffn_session* s, int slot);
 int tffn_session_seq_len(const tffn_session* s, int slot); /* KVCache::len */
@@ -219,6 +230,9 @@ int tffn_op_swiglu_bs1_noalloc(int device, void* h_io, const void* norm_w, const
 /* Runs a kernel that waits on a barrier nothing signals; returns the device status it
  * recorded (expected: 5). Proves that a wait that runs out returns instead of hanging. */
 int tffn_op_wait_selftest(int device);
+/* The same for the tensor-parallel hand-shake: one GPU plays rank 0 of a group of two whose peer never
+ * signals; the kernel gives up after wait_ms (1..2000) and the recorded status is returned (expected: 7). */
+int tffn_op_tp_wait_selftest(int device, int wait_ms);
 
 #ifdef __cplusplus
 }

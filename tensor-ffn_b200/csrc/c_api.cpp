@@ -295,6 +295,12 @@ int tffn_session_set_launch_mode(tffn_session* s, int mode) {
         s->s->set_launch_mode(mode);
     });
 }
+int tffn_session_set_tp_fused(tffn_session* s, int on) {
+    return guard([&] {
+        need(s, "NULL session");
+        s->s->set_tp_fused(on != 0);
+    });
+}
 int tffn_session_set_ablation(tffn_session* s, unsigned mask) {
     return guard([&] {
         need(s, "NULL session");
@@ -506,6 +512,45 @@ int tffn_op_wait_selftest(int device) {
         DeviceBuffer status;
         status.alloc(4);
         launch_wait_selftest(status.as<int>(), 0);
+        TFFN_CUDA(cudaGetLastError());
+        TFFN_CUDA(cudaDeviceSynchronize());
+        TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));
+    });
+    return rc < 0 ? rc : st;
+}
+
+int tffn_op_tp_wait_selftest(int device, int wait_ms) {
+    int st = 0;
+    int rc = guard([&] {
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
+        need(wait_ms >= 1 && wait_ms <= 2000, "wait_ms must be 1..2000");
+        TFFN_CUDA(cudaSetDevice(device));
+        // rank 0 of a group of two whose second rank does not exist: its window is a second local buffer, so the
+        // signal lands in this GPU's memory and the flag this rank polls is never written
+        const int H = 64, T = 2;
+        DeviceBuffer status, win0, win1, calls, h, xn;
+        status.alloc(4);
+        const size_t flag_floats = (size_t)2 * kTpMaxRanks * kTpFlagBlocks;
+        win0.alloc((flag_floats + 2 * T * H) * 4);
+        win1.alloc((flag_floats + 2 * T * H) * 4);
+        calls.alloc(kTpFlagBlocks * 4);
+        h.alloc(T * H * 2);
+        xn.alloc(T * H * 2);
+        TpPeerSync sy;
+        memset(&sy, 0, sizeof sy);
+        sy.flags_local = win0.as<unsigned>();
+        sy.flags_peer[0] = win0.as<unsigned>();
+        sy.flags_peer[1] = win1.as<unsigned>();
+        sy.calls = calls.as<unsigned>();
+        sy.rank = 0;
+        sy.size = 2;
+        sy.wait_ns = (unsigned long long)wait_ms * 1000000ull;
+        TpParts parts;
+        parts.part[0] = win0.as<float>() + flag_floats;
+        parts.part[1] = win1.as<float>() + flag_floats;
+        for (int p = 2; p < kTpMaxRanks; ++p) parts.part[p] = nullptr;
+        launch_tp_reduce_residual_norm(h.as<bf16>(), parts, sy, nullptr, xn.as<bf16>(), T, H, 1e-6f, status.as<int>(), 0);
         TFFN_CUDA(cudaGetLastError());
         TFFN_CUDA(cudaDeviceSynchronize());
         TFFN_CUDA(cudaMemcpy(&st, status.p, 4, cudaMemcpyDeviceToHost));

@@ -328,7 +328,42 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
     act_b_.alloc(T * I * 2);
     if (e_) act_e_.alloc(T * I * 2);
     xn_last_.alloc(T * H * 2);
-    if (tp_) delta_.alloc(T * H * 4);
+    if (tp_) {
+        delta_.alloc(T * H * 4);
+        // pick exchange: 8 bytes per logits row and rank; sized for the largest launch now, so that no step
+        // allocates (a step may be under stream capture)
+        tp_pick_send_.alloc(T * 8);
+        tp_pick_recv_.alloc(T * 8 * m_->tp.tp_size);
+        // exchange window for decode-sized launches (a whole allocation of its own: it is exported to the peers)
+        const int R = m_->tp.tp_size;
+        if (R > kTpMaxRanks) throw Error(kErrUnsupported, "tensor-parallel groups of more than 8 ranks are not supported");
+        tp_small_rows_ = (int)std::min<size_t>(T, kTpFlagBlocks);
+        const size_t flag_bytes = (size_t)2 * kTpMaxRanks * kTpFlagBlocks * 4;  // hand-shakes of the reduce and of the pick
+        tp_pick_off_ = flag_bytes;
+        const size_t pick_bytes = (size_t)kTpMaxRanks * kTpFlagBlocks * 8;
+        tp_part_off_[0] = (flag_bytes + pick_bytes) / 4;
+        tp_part_off_[1] = tp_part_off_[0] + (size_t)tp_small_rows_ * H;
+        size_t win_bytes = (tp_part_off_[1] + (size_t)tp_small_rows_ * H) * 4;
+        win_bytes = (std::max<size_t>(win_bytes, (size_t)4 << 20) + ((size_t)2 << 20) - 1) & ~(((size_t)2 << 20) - 1);
+        tp_win_.alloc(win_bytes);
+        tp_calls_.alloc((size_t)2 * kTpFlagBlocks * 4);
+        tp_window_open(tp_, tp_win_.p, tp_peers_, stream_);
+        for (int b = 0; b < 2; ++b)
+            for (int p = 0; p < kTpMaxRanks; ++p) tp_parts_[b].part[p] = p < R ? (const float*)tp_peers_[p] + tp_part_off_[b] : nullptr;
+        tp_sync_.flags_local = (unsigned*)tp_win_.p;
+        for (int p = 0; p < kTpMaxRanks; ++p) tp_sync_.flags_peer[p] = p < R ? (unsigned*)tp_peers_[p] : nullptr;
+        tp_sync_.calls = tp_calls_.as<unsigned>();
+        tp_sync_.rank = m_->tp.tp_rank;
+        tp_sync_.size = R;
+        tp_sync_.wait_ns = 10ull * 1000 * 1000 * 1000;
+        tp_pick_sync_ = tp_sync_;
+        tp_pick_sync_.flags_local += (size_t)kTpMaxRanks * kTpFlagBlocks;
+        for (int p = 0; p < R; ++p) tp_pick_sync_.flags_peer[p] += (size_t)kTpMaxRanks * kTpFlagBlocks;
+        tp_pick_sync_.calls += kTpFlagBlocks;
+        tp_pick_push_.n = R;
+        for (int p = 0; p < kTpMaxRanks; ++p)
+            tp_pick_push_.dst[p] = p < R ? (float2*)((char*)tp_peers_[p] + tp_pick_off_) + (size_t)m_->tp.tp_rank * tp_small_rows_ : nullptr;
+    }
     ensure_logits(std::max<size_t>(256, max_batch));
     attn_partials_.alloc((size_t)32 << 20);
     attn_counters_.alloc(16384 * 4);
@@ -356,6 +391,11 @@ Session::~Session() {
     cudaSetDevice(m_->device);
     cudaStreamSynchronize(stream_);
     drop_graphs();
+    if (tp_ && tp_win_.p) {
+        // collective, like the constructor: the window may be freed only when no peer has it mapped any more;
+        // if a peer does not arrive, the window is left allocated
+        if (!tp_window_close(tp_, tp_peers_, stream_, 10.0)) tp_win_.p = nullptr;
+    }
     prof_resolve();
     for (cudaEvent_t e : prof_free_) cudaEventDestroy(e);
     if (h_status_) cudaFreeHost(h_status_);
@@ -501,6 +541,12 @@ void Session::set_launch_mode(int mode) {
     launch_mode_ = mode;
 }
 
+void Session::set_tp_fused(bool on) {
+    if (on == tp_fused_) return;
+    TFFN_CUDA(cudaStreamSynchronize(stream_));
+    tp_fused_ = on;
+    drop_graphs();
+}
 void Session::set_ablation(unsigned mask) {
     TFFN_CUDA(cudaStreamSynchronize(stream_));
     for (auto& kv : dec_graphs_) cudaGraphExecDestroy(kv.second.exec);
@@ -545,7 +591,7 @@ void Session::check_status() {
 const char* kclass_name(int c) {
     static const char* names[KC_COUNT] = {"embed_rows", "rmsnorm_rows", "gemm_tc:qkv", "attn_decode",
                                           "gemm_tc:o_proj", "gemm_tc:gate_up_swiglu", "gemm_tc:down", "gemm_tc:lm_head",
-                                          "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead", "nccl_all_reduce"};
+                                          "argmax_rows", "decode_advance", "bs1_qkv", "bs1_oproj", "bs1_ffn", "bs1_lmhead", "tp_all_reduce"};
     return (c >= 0 && c < KC_COUNT) ? names[c] : "?";
 }
 void Session::set_profile(bool on) {
@@ -636,12 +682,22 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         prof_end();
         launches_++;
     };
+    const bool pdl = launch_mode_ >= 1 && !profile_;
+    // decode-sized launches: partial sums left in this rank's exchange window, read by every rank's row kernel
+    // over NVLink after a flag hand-shake (buffer 0 after o_proj, buffer 1 after down)
+    const bool fused = tp && tp_fused_ && T <= tp_small_rows_;
+    auto reduce_fused = [&](int which, const bf16* norm_w) {
+        prof_begin(KC_ALLREDUCE);
+        launch_tp_reduce_residual_norm(h_.as<bf16>(), tp_parts_[which], tp_sync_, norm_w, xn_.as<bf16>(), T, H, c.rms_norm_eps,
+                                       status_.as<int>(), stream_, pdl);
+        prof_end();
+        launches_++;
+    };
     const int* tokens = decode ? dec_tokens_.as<int>() : tokens_.as<int>();
     const int* tok_seq = decode ? identity_.as<int>() : tok_seq_.as<int>();
     const int* tok_pos = decode ? seq_len_dev_.as<int>() : tok_pos_.as<int>();
     int* status = status_.as<int>();
     const GemmWorkspace gws = gemm_ws();
-    const bool pdl = launch_mode_ >= 1 && !profile_;
     // timing-only ablation: a class in the mask is not launched (results are then meaningless)
     auto live = [&](int cls) { return ((ablate_mask_ >> cls) & 1u) == 0; };
     auto gemm = [&](GemmCall& call, int cls) {
@@ -714,11 +770,15 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         g.op[0] = {ly.wo.as<bf16>(), nh * hd, ctx_.as<bf16>(), nh * hd, nh * hd};
         g.N = H;
         g.mode = tp ? GEMM_STORE_F32 : GEMM_RESIDUAL;
-        g.out = tp ? delta_.p : h_.p;
+        g.out = fused ? (void*)((float*)tp_win_.p + tp_part_off_[0]) : tp ? delta_.p : h_.p;
         g.ldo = H;
         gemm(g, KC_GEMM_OPROJ);
         prof_begin(KC_RMSNORM);
-        if (tp) {
+        if (fused) {
+            prof_end();
+            reduce_fused(0, ly.ffn_norm.as<bf16>());
+            prof_begin(KC_RMSNORM);
+        } else if (tp) {
             prof_end();
             all_reduce_delta(T);
             prof_begin(KC_RMSNORM);
@@ -759,11 +819,13 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
         }
         g.N = H;
         g.mode = tp ? GEMM_STORE_F32 : GEMM_RESIDUAL;
-        g.out = tp ? delta_.p : h_.p;
+        g.out = fused ? (void*)((float*)tp_win_.p + tp_part_off_[1]) : tp ? delta_.p : h_.p;
         g.ldo = H;
         gemm(g, KC_GEMM_DOWN);
         g.alpha = 1.f;
-        if (tp) {
+        if (fused) {
+            reduce_fused(1, l + 1 < c.num_layers ? m_->layers[l + 1].attn_norm.as<bf16>() : nullptr);
+        } else if (tp) {
             all_reduce_delta(T);
             const bf16* next_norm = l + 1 < c.num_layers ? m_->layers[l + 1].attn_norm.as<bf16>() : nullptr;
             prof_begin(KC_RMSNORM);
@@ -814,17 +876,21 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
                 // every rank's best of its vocabulary slice, exchanged (8 bytes per row and rank), then the same
                 // pick on every rank: largest value, lowest global index among equals (main.cpp:45-51)
                 const size_t bytes = (size_t)n_logit_rows * 8;
-                if (tp_pick_send_.bytes < bytes) {
-                    TFFN_CUDA(cudaStreamSynchronize(stream_));
-                    tp_pick_send_.alloc(bytes);
-                    tp_pick_recv_.alloc(bytes * m_->tp.tp_size);
-                    drop_graphs();
+                if (tp_pick_send_.bytes < bytes) throw Error(kErrCapacity, "tensor parallel: more logits rows than the session was sized for");
+                if (tp_fused_ && n_logit_rows <= tp_small_rows_) {
+                    // candidates pushed into every rank's window, hand-shake in the pick kernel: no NCCL call in a decode step
+                    launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),
+                                        nullptr, m_->tp.v0, &tp_pick_push_);
+                    launch_tp_pick_peer((const char*)tp_win_.p + tp_pick_off_, (size_t)tp_small_rows_, tp_pick_sync_, n_logit_rows,
+                                        picks_.as<int>(), status_.as<int>(), stream_, pdl);
+                    launches_ += 1;
+                } else {
+                    launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),
+                                        tp_pick_send_.p, m_->tp.v0);
+                    tp_all_gather_bytes(tp_, tp_pick_send_.p, tp_pick_recv_.p, bytes, stream_);
+                    launch_tp_pick(tp_pick_recv_.p, m_->tp.tp_size, n_logit_rows, picks_.as<int>(), stream_, pdl);
+                    launches_ += 2;
                 }
-                launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),
-                                    tp_pick_send_.p, m_->tp.v0);
-                tp_all_gather_bytes(tp_, tp_pick_send_.p, tp_pick_recv_.p, bytes, stream_);
-                launch_tp_pick(tp_pick_recv_.p, m_->tp.tp_size, n_logit_rows, picks_.as<int>(), stream_, pdl);
-                launches_ += 2;
             } else if (fused_pick)
                 launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX));
             else if (sampling())

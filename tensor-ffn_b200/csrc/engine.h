@@ -52,6 +52,9 @@ int tp_comm_size(const TpComm* c);
 int tp_comm_rank(const TpComm* c);
 void tp_all_reduce_f32(TpComm* c, float* buf, size_t n, cudaStream_t s);                 // in place, sum
 void tp_all_gather_bytes(TpComm* c, const void* send, void* recv, size_t bytes, cudaStream_t s);  // recv[rank * bytes ...]
+// peer-mapped exchange windows (collective calls; see tp_comm.cpp): peers[] has 8 entries
+void tp_window_open(TpComm* c, void* local, void* peers[], cudaStream_t s);
+bool tp_window_close(TpComm* c, void* peers[], cudaStream_t s, double timeout_s);
 
 struct Model {
     Config cfg;         // the whole model, as config.json states it
@@ -110,6 +113,8 @@ public:
     // timing-only: kernel classes (bit = KClass) that the batched path does not launch
     void set_ablation(unsigned mask);
     void set_bs1_path(bool on) { use_bs1_ = on; }
+    // tensor parallel: false = every all-reduce through NCCL (all ranks must choose alike)
+    void set_tp_fused(bool on);
     // temperature <= 0: greedy. Otherwise every pick is sampled on the device as sample() of the
     // reference does on the host, with draws from a std::mt19937(seed) owned by the session.
     void set_sampling(float temperature, uint32_t seed);
@@ -125,6 +130,20 @@ private:
     const Expert* e_;
     TpComm* tp_ = nullptr;  // not owned
     DeviceBuffer delta_, tp_pick_send_, tp_pick_recv_, tp_logits_;  // tensor parallel: fp32 partial sums, pick exchange, gathered logits
+    // Tensor parallel, launches of at most tp_small_rows_ rows (decode): the projections leave their partial
+    // sums in this rank's exchange window, which the peers have mapped, and a row kernel on every rank reads
+    // all ranks' parts over NVLink after a flag hand-shake (k_tp_reduce_residual_norm); larger launches
+    // (prefill) go through NCCL. Window = flags, pick candidates, then two alternating buffers (o_proj / down)
+    // of [tp_small_rows_][H] fp32.
+    DeviceBuffer tp_win_, tp_calls_;
+    void* tp_peers_[kTpMaxRanks] = {};
+    int tp_small_rows_ = 0;
+    size_t tp_part_off_[2] = {0, 0};  // in floats, from the window's start
+    TpParts tp_parts_[2];
+    TpPeerSync tp_sync_, tp_pick_sync_;
+    TpPickPush tp_pick_push_;
+    size_t tp_pick_off_ = 0;  // in bytes: [ranks][tp_small_rows_] candidates of 8 bytes
+    bool tp_fused_ = true;
     void copy_logits_to_host(float* dst, size_t rows);  // rows of logits_ (this rank's vocabulary slice) -> full rows on the host
     int max_batch_, max_seq_, max_pages_per_seq_, num_pages_;
     int cap_tokens_;  // rows of the activation buffers

@@ -46,6 +46,8 @@ struct GemmOperand {
     int64_t ldx;
     int K;          // 0 = operand unused
 };
+constexpr int kTpMaxRanks = 8;  // ranks of a tensor-parallel group
+
 struct GemmCall {
     GemmOperand op[2];
     int N, T;
@@ -96,11 +98,39 @@ void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float
 // u[step * R + row] = canonical uniform draws in [0, 1), step = *step_counter (0 if nullptr)
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
+// Tensor parallel over peer memory (decode-sized launches). Every rank owns an exchange window that the
+// other ranks of the group have mapped; kTpFlagBlocks = the largest grid of a kernel that hand-shakes.
+constexpr int kTpFlagBlocks = 256;
+struct TpPeerSync {
+    unsigned* flags_local;              // this rank's window: [size][kTpFlagBlocks] counters, written by the peers
+    unsigned* flags_peer[kTpMaxRanks];  // the same array inside every peer's window
+    unsigned* calls;                    // this rank only: [kTpFlagBlocks] calls made so far, per block
+    int rank, size;
+    unsigned long long wait_ns;         // how long a block waits for its peers before it gives up
+};
+// destinations of a rank's pick candidates: its row array inside every rank's window
+struct TpPickPush {
+    float2* dst[kTpMaxRanks];
+    int n;
+};
 // per-tile maxima left by the GEMM (GemmCall::amax_val / amax_idx, `tiles` per row) -> argmax per row
 // pack (optional, 8 bytes per row): {the row's maximum, idx_offset + its index} for the exchange between
 // tensor-parallel ranks, which launch_tp_pick resolves (cand = `ranks` such arrays of R rows back to back)
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s,
-                         bool pdl = false, unsigned long long* tl = nullptr, void* pack = nullptr, int idx_offset = 0);
+                         bool pdl = false, unsigned long long* tl = nullptr, void* pack = nullptr, int idx_offset = 0,
+                         const TpPickPush* push = nullptr);  // push: also store the candidate into every rank's window
+// the ranks' partial sums of one exchange: part[p] = rank p's fp32 [rows][H] buffer as mapped into this process
+struct TpParts {
+    const float* part[kTpMaxRanks];
+};
+// h += sum over ranks p (in rank order) of part[p][row * H ...], then out = RMSNorm(h) * w (w == nullptr: no
+// norm). T <= kTpFlagBlocks rows, H a multiple of 4.
+void launch_tp_reduce_residual_norm(bf16* h, const TpParts& parts, const TpPeerSync& sync, const bf16* w, bf16* out, int T, int H,
+                                    float eps, int* status, cudaStream_t s, bool pdl = false);
+// launch_tp_pick over the candidates the ranks pushed into this rank's window (cand[rank * stride + row]), after a
+// hand-shake with the peers; R <= 128 * kTpFlagBlocks rows
+void launch_tp_pick_peer(const void* cand, size_t stride, const TpPeerSync& sync, int R, int* out, int* status, cudaStream_t s,
+                         bool pdl = false);
 void launch_tp_pick(const void* cand, int ranks, int R, int* out, cudaStream_t s, bool pdl = false);
 // tensor parallel: h = bf16(h + delta) and, if w != null, out = rmsnorm(h) * w, per row
 void launch_residual_norm(bf16* h, const float* delta, const bf16* w, bf16* out, int T, int H, float eps, cudaStream_t s,

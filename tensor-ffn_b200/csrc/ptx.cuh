@@ -17,7 +17,8 @@ enum DevStatus : int {
     DEV_ERR_ACC_WAIT = 3,     // epilogue gave up waiting for the accumulator
     DEV_ERR_BOUNDS = 4,       // an index check failed (token id, page id, position)
     DEV_ERR_TEST_WAIT = 5,    // the deliberate never-signalled wait of the self-test
-    DEV_ERR_GRID_WAIT = 6,    // a grid barrier of the persistent batch-1 kernel ran out of polls
+    DEV_ERR_GRID_WAIT = 6,    // a grid barrier ran out of polls
+    DEV_ERR_PEER_WAIT = 7,    // tensor parallel: a peer rank did not signal its partial sums in time
 };
 
 constexpr uint32_t kSpinLimit = 1u << 22;

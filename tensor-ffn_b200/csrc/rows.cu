@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ l
 // (pack: optional {value, idx_offset + index} per row for the exchange between tensor-parallel ranks)
 __global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ val, const int* __restrict__ idx, int tiles,
                                                        int* __restrict__ out, unsigned long long* tl, float2* __restrict__ pack,
-                                                       int idx_offset) {
+                                                       int idx_offset, TpPickPush push) {
     if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
@@ -177,7 +177,14 @@ __global__ void __launch_bounds__(256) k_argmax_tiles(const float* __restrict__ 
         for (int o = 4; o > 0; o >>= 1) argmax_take(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
         if (threadIdx.x == 0) {
             out[r] = (bi == 0x7fffffff) ? 0 : bi;
-            if (pack) pack[r] = make_float2(best, __int_as_float(bi == 0x7fffffff ? 0x7fffffff : bi + idx_offset));
+            const float2 cand = make_float2(best, __int_as_float(bi == 0x7fffffff ? 0x7fffffff : bi + idx_offset));
+            if (pack) pack[r] = cand;
+            if (push.n > 0) {
+                // tensor parallel over peer memory: the candidate goes straight into every rank's window; the fence
+                // waits until the posted stores have been performed there (see k_gemm_tc)
+                for (int q = 0; q < push.n; ++q) push.dst[q][r] = cand;
+                __threadfence_system();
+            }
             tl_mark(tl, 2);
         }
     }
@@ -199,36 +206,169 @@ __global__ void k_tp_pick(const float2* __restrict__ cand, int ranks, int R, int
     out[r] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
-// Tensor parallel: h = bf16(float(h) + delta) (delta = the all-reduced fp32 sum of the ranks' projection
-// outputs; the residual add of inference/src/model/qwen.cu:282-285), and, when w is given, the RMSNorm of
-// the new row (inference/src/backend/cuda_ops.cu:75-96) in the same pass. One block of 128 threads per row.
-__global__ void __launch_bounds__(128) k_residual_norm_rows(bf16* __restrict__ h, const float* __restrict__ delta,
-                                                             const bf16* __restrict__ w, bf16* __restrict__ out, int H, float eps) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int r = blockIdx.x;
-    bf16* hr = h + (size_t)r * H;
-    const float* dr = delta + (size_t)r * H;
-    __shared__ float s_red[4];
+// h = bf16(float(h) + sum) for one row (the residual add of inference/src/model/qwen.cu:282-285) and, when w
+// is given, the RMSNorm of the new row (inference/src/backend/cuda_ops.cu:75-96) in the same pass; `sum4(i)`
+// returns the four fp32 addends of columns i .. i+3. Block of kRowNormThreads threads (one pass over rows of
+// up to 4096 columns, so that all of a thread's loads are in flight at once: they may cross NVLink), H a
+// multiple of 4. Shared by the two tensor-parallel row kernels so that they round alike whichever way the
+// partial sums travelled.
+constexpr int kRowNormThreads = 1024;
+template <typename Sum4>
+__device__ __forceinline__ void residual_norm_row(bf16* __restrict__ hr, const bf16* __restrict__ w, bf16* __restrict__ outr, int H,
+                                                  float eps, float* s_red, Sum4 sum4) {
     float ss = 0.f;
-    for (int i = threadIdx.x * 2; i < H; i += 256) {
-        const uint32_t hv = *(const uint32_t*)(hr + i);
-        const float2 d = __ldcg((const float2*)(dr + i));
-        const float a = bf16_round(bf16_lo(hv) + d.x), b = bf16_round(bf16_hi(hv) + d.y);
-        *(uint32_t*)(hr + i) = (uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16);
-        ss += a * a + b * b;
+    for (int i = threadIdx.x * 4; i < H; i += kRowNormThreads * 4) {
+        const float4 acc = sum4(i);
+        const uint2 hv = *(const uint2*)(hr + i);
+        const float a = bf16_round(bf16_lo(hv.x) + acc.x), b = bf16_round(bf16_hi(hv.x) + acc.y);
+        const float c = bf16_round(bf16_lo(hv.y) + acc.z), d = bf16_round(bf16_hi(hv.y) + acc.w);
+        *(uint2*)(hr + i) = make_uint2((uint32_t)bf16_bits(a) | ((uint32_t)bf16_bits(b) << 16),
+                                       (uint32_t)bf16_bits(c) | ((uint32_t)bf16_bits(d) << 16));
+        ss += a * a + b * b + c * c + d * d;
     }
     if (!w) return;
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
     __syncthreads();
-    const float rinv = rsqrtf((s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)H + eps);
-    for (int i = threadIdx.x * 2; i < H; i += 256) {  // each thread re-reads only what it wrote itself
-        const uint32_t hv = *(const uint32_t*)(hr + i);
-        const uint32_t wv = __ldg((const uint32_t*)(w + i));
-        const float x0 = bf16_lo(hv) * rinv * bf16_lo(wv), x1 = bf16_hi(hv) * rinv * bf16_hi(wv);
-        *(uint32_t*)(out + (size_t)r * H + i) = (uint32_t)bf16_bits(x0) | ((uint32_t)bf16_bits(x1) << 16);
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kRowNormThreads / 32; ++k) tot += s_red[k];
+    const float rinv = rsqrtf(tot / (float)H + eps);
+    for (int i = threadIdx.x * 4; i < H; i += kRowNormThreads * 4) {  // each thread re-reads only what it wrote itself
+        const uint2 hv = *(const uint2*)(hr + i);
+        const uint2 wv = __ldg((const uint2*)(w + i));
+        const float x0 = bf16_lo(hv.x) * rinv * bf16_lo(wv.x), x1 = bf16_hi(hv.x) * rinv * bf16_hi(wv.x);
+        const float x2 = bf16_lo(hv.y) * rinv * bf16_lo(wv.y), x3 = bf16_hi(hv.y) * rinv * bf16_hi(wv.y);
+        *(uint2*)(outr + i) = make_uint2((uint32_t)bf16_bits(x0) | ((uint32_t)bf16_bits(x1) << 16),
+                                         (uint32_t)bf16_bits(x2) | ((uint32_t)bf16_bits(x3) << 16));
     }
+}
+
+// Tensor parallel, launches that went through NCCL: delta = the all-reduced fp32 sum of the ranks' projection
+// outputs. One block per row.
+__global__ void __launch_bounds__(kRowNormThreads) k_residual_norm_rows(bf16* __restrict__ h, const float* __restrict__ delta,
+                                                             const bf16* __restrict__ w, bf16* __restrict__ out, int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_red[kRowNormThreads / 32];
+    const int r = blockIdx.x;
+    const float* dr = delta + (size_t)r * H;
+    residual_norm_row(h + (size_t)r * H, w, out + (size_t)r * H, H, eps, s_red, [&](int i) { return __ldcg((const float4*)(dr + i)); });
+}
+
+// ---------------------------------------------------------------- tensor parallel over peer memory
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Hand-shake of block b with block b of every peer rank: tell them that this rank's kernels before this one
+// have completed (so what they stored into this rank's own window is there to be read), then wait until
+// every peer has said the same. Flags are call counters that only grow: flags[src rank][block], written by the
+// source rank with a system-scope release store into the destination's window, polled here with acquire
+// loads. A peer can be at most one call ahead (it needs this rank's next signal to go further), hence the
+// "at least" comparison and the two alternating buffers of the callers: a rank overwrites a buffer only after
+// a later hand-shake, which its peers enter only when they have finished reading it. The wait is bounded by wall
+// time; when it runs out (or the step has already failed) the status word is set and the block goes on with
+// whatever the slots hold, so that the kernel returns and the host reads the status.
+__device__ __forceinline__ void tp_handshake(const TpPeerSync& a, int* status, unsigned* s_count) {
+    const int b = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const unsigned cnt = a.calls[b] + 1u;
+        a.calls[b] = cnt;
+        *s_count = cnt;
+    }
+    __syncthreads();
+    const unsigned cnt = *s_count;
+    const int p = (int)threadIdx.x;
+    if (p < a.size && p != a.rank) {
+        st_release_sys_u32(a.flags_peer[p] + (size_t)a.rank * kTpFlagBlocks + b, cnt);
+        const unsigned* mine = a.flags_local + (size_t)p * kTpFlagBlocks + b;
+        if (__ldcg(status) == 0) {
+            unsigned long long t0 = 0;
+            for (unsigned i = 0;; ++i) {
+                if ((int)(ld_acquire_sys_u32(mine) - cnt) >= 0) break;
+                if ((i & 255u) == 255u) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > a.wait_ns || i > (1u << 30)) {
+                        dev_fail(status, DEV_ERR_PEER_WAIT);
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// k_tp_pick over peer memory: the ranks' k_argmax_tiles have stored their candidates into this rank's window
+// (cand[src rank * stride + row]); hand-shake, then the same pick on every rank.
+__global__ void __launch_bounds__(128) k_tp_pick_peer(const float2* cand, size_t stride, TpPeerSync sync, int R, int* __restrict__ out,
+                                                       int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned s_count;
+    tp_handshake(sync, status, &s_count);
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < sync.size; ++k) {
+        const float2 c = __ldcg(cand + (size_t)k * stride + r);
+        argmax_take(best, bi, c.x, __float_as_int(c.y));
+    }
+    out[r] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+__device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Tensor parallel, small launches (decode): the all-reduce, the residual add and the next RMSNorm in one
+// kernel, over peer memory. Every rank's projection left its fp32 partial sums in its OWN exchange window
+// (plain local stores, complete and visible once that kernel has finished); after the hand-shake, which
+// tells the peers exactly that, this block loads its row from every rank's window over NVLink (system-scope
+// loads: nothing of an earlier exchange may be served from a cache on this side), adds the parts in rank
+// order, the same order on every rank, so that all ranks keep bit-identical residual streams, then
+// h = bf16(float(h) + sum) (inference/src/model/qwen.cu:282-285) and, when w is given, the RMSNorm of the new row
+// (inference/src/backend/cuda_ops.cu:75-96). No rank ever stores into another rank's partial sums, so no
+// store has to be fenced across GPUs. One block per row; all loads of a thread are issued before the adds.
+__global__ void __launch_bounds__(kRowNormThreads) k_tp_reduce_residual_norm(bf16* __restrict__ h, TpParts parts, TpPeerSync sync,
+                                                                  const bf16* __restrict__ w, bf16* __restrict__ out, int H,
+                                                                  float eps, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned s_count;
+    __shared__ float s_red[kRowNormThreads / 32];
+    tp_handshake(sync, status, &s_count);
+    const int r = blockIdx.x;
+    const size_t row = (size_t)r * H;
+    const int R = sync.size;
+    residual_norm_row(h + row, w, out + row, H, eps, s_red, [&](int i) {
+        float4 v[kTpMaxRanks];
+#pragma unroll
+        for (int p = 0; p < kTpMaxRanks; ++p)
+            if (p < R) v[p] = ld_relaxed_sys_v4(parts.part[p] + row + i);
+        float4 acc = v[0];
+#pragma unroll
+        for (int p = 1; p < kTpMaxRanks; ++p)
+            if (p < R) {
+                acc.x += v[p].x;
+                acc.y += v[p].y;
+                acc.z += v[p].z;
+                acc.w += v[p].w;
+            }
+        return acc;
+    });
 }
 
 // Temperature sampling on the device, the arithmetic of sample() (inference/src/main.cpp:52-63): float
@@ -349,6 +489,8 @@ int rows_prepare() {
     if (e == cudaSuccess) e = prefer_max_shared(k_sample_rows);
     if (e == cudaSuccess) e = prefer_max_shared(k_tp_pick);
     if (e == cudaSuccess) e = prefer_max_shared(k_residual_norm_rows);
+    if (e == cudaSuccess) e = prefer_max_shared(k_tp_reduce_residual_norm);
+    if (e == cudaSuccess) e = prefer_max_shared(k_tp_pick_peer);
     return (int)e;
 }
 
@@ -369,14 +511,24 @@ void launch_argmax(const float* logits, int R, int V, int* out, float* scratch, 
     launch_k(k_argmax_rows, dim3(R, S), dim3(256), 0, s, pdl, logits, V, S, out, scratch, counters, tl);
 }
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s, bool pdl,
-                         unsigned long long* tl, void* pack, int idx_offset) {
-    launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl, (float2*)pack, idx_offset);
+                         unsigned long long* tl, void* pack, int idx_offset, const TpPickPush* push) {
+    TpPickPush none;
+    memset(&none, 0, sizeof none);
+    launch_k(k_argmax_tiles, dim3(R), dim3(256), 0, s, pdl, amax_val, amax_idx, tiles, out, tl, (float2*)pack, idx_offset,
+             push ? *push : none);
+}
+void launch_tp_pick_peer(const void* cand, size_t stride, const TpPeerSync& sync, int R, int* out, int* status, cudaStream_t s, bool pdl) {
+    launch_k(k_tp_pick_peer, dim3((R + 127) / 128), dim3(128), 0, s, pdl, (const float2*)cand, stride, sync, R, out, status);
 }
 void launch_tp_pick(const void* cand, int ranks, int R, int* out, cudaStream_t s, bool pdl) {
     launch_k(k_tp_pick, dim3((R + 127) / 128), dim3(128), 0, s, pdl, (const float2*)cand, ranks, R, out);
 }
 void launch_residual_norm(bf16* h, const float* delta, const bf16* w, bf16* out, int T, int H, float eps, cudaStream_t s, bool pdl) {
-    launch_k(k_residual_norm_rows, dim3(T), dim3(128), 0, s, pdl, h, delta, w, out, H, eps);
+    launch_k(k_residual_norm_rows, dim3(T), dim3(kRowNormThreads), 0, s, pdl, h, delta, w, out, H, eps);
+}
+void launch_tp_reduce_residual_norm(bf16* h, const TpParts& parts, const TpPeerSync& sync, const bf16* w, bf16* out, int T, int H,
+                                    float eps, int* status, cudaStream_t s, bool pdl) {
+    launch_k(k_tp_reduce_residual_norm, dim3(T), dim3(kRowNormThreads), 0, s, pdl, h, parts, sync, w, out, H, eps, status);
 }
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl, unsigned long long* tl) {

@@ -82,6 +82,7 @@ _SIGS = {
     "tffn_session_set_launch_mode": (_i, [_vp, _i]),
     "tffn_expert_forward": (_i, [_vp, _vp, _vp, _i, _vp]),
     "tffn_session_set_ablation": (_i, [_vp, ctypes.c_uint]),
+    "tffn_session_set_tp_fused": (_i, [_vp, _i]),
     "tffn_session_set_sampling": (_i, [_vp, _f, ctypes.c_uint32]),
     "tffn_session_set_bs1_path": (_i, [_vp, _i]),
     "tffn_session_capture_hidden": (_i, [_vp, _i]),
@@ -103,6 +104,7 @@ _SIGS = {
     "tffn_op_swiglu_bs1_trace": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp, _vp, _i]),
     "tffn_op_swiglu_bs1_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _vp]),
     "tffn_op_wait_selftest": (_i, [_i]),
+    "tffn_op_tp_wait_selftest": (_i, [_i, _i]),
 }
 for _name, (_res, _args) in _SIGS.items():
     _fn = getattr(_L, _name)
@@ -363,6 +365,10 @@ class Session:
     def set_launch_mode(self, mode: int):
         _check(_L.tffn_session_set_launch_mode(self._h, mode))
 
+    def set_tp_fused(self, on: bool):
+        """tensor parallel: False sends every all-reduce through NCCL (all ranks alike)"""
+        _check(_L.tffn_session_set_tp_fused(self._h, 1 if on else 0))
+
     def set_ablation(self, mask: int):
         """timing aid: skip the kernel classes whose bit is set (results become meaningless)"""
         _check(_L.tffn_session_set_ablation(self._h, mask))
@@ -513,3 +519,8 @@ def op_swiglu_bs1_noalloc(h_io_ptr: int, norm_w_ptr: int, packed_base_ptr: int, 
 
 def op_wait_selftest(device: int = 0) -> int:
     return _check(_L.tffn_op_wait_selftest(device))
+
+
+def op_tp_wait_selftest(wait_ms: int = 200, device: int = 0) -> int:
+    """tensor-parallel hand-shake with a peer that never signals: the device status after the bounded wait (7)"""
+    return _check(_L.tffn_op_tp_wait_selftest(device, wait_ms))

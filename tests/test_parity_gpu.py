@@ -207,6 +207,17 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert tffn.op_wait_selftest() == 5
 
 
+def test_peer_handshake_gives_up_when_the_peer_never_signals():
+    """the tensor-parallel hand-shake on one GPU against a flag nothing sets: status 7 after the bounded
+    wait, and the context stays usable"""
+    import time
+    import tffn
+    t0 = time.perf_counter()
+    assert tffn.op_tp_wait_selftest(200) == 7
+    assert time.perf_counter() - t0 < 5.0
+    assert tffn.op_wait_selftest() == 5
+
+
 def test_long_context_attention_splits(model_dirs):
     """Contexts beyond 1024 keys make the batch-1 attention split the context over several CTAs and merge
     the parts: 3 splits (single-pass merge) against the oracle, then 20 splits (generic merge) and the

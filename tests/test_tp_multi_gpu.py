@@ -1,6 +1,7 @@
 """-m gpu, needs at least two GPUs (skipped otherwise): tensor-parallel ranks, one process per GPU, against the
 same model on one GPU. Every rank must return the same tokens and the same full logits, within the kernel
-tolerance of the single-GPU result (the fp32 all-reduce changes the order of summation, nothing else).
+tolerance of the single-GPU result (the fp32 sum over the ranks changes the order of summation, nothing else),
+through both exchange paths: partial sums pushed into the peers' windows (decode-sized launches) and NCCL.
 Failure handling is covered without any GPU fault by tests/test_tp_cpu.py (a rank that never arrives)."""
 import os
 import subprocess
@@ -20,6 +21,7 @@ WORKER = textwrap.dedent("""
     sys.path.insert(0, os.path.join(%r, "tensor-ffn_b200"))
     import synth, tffn
     rank, size, meet, d, ep, out, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5], sys.argv[6], int(sys.argv[7])
+    fused = int(sys.argv[8])
     g = None
     if size > 1:
         g = tffn.TpGroup(tffn.tp_rendezvous(meet, rank, size, 120.0), rank, size, rank)
@@ -28,6 +30,8 @@ WORKER = textwrap.dedent("""
     V = m.cfg.vocab_size
     s = tffn.Session(m, e, max_batch=3, max_seq=96, tp=g)
     s.set_launch_mode(mode)
+    if size > 1:
+        s.set_tp_fused(bool(fused))
     prompts = [synth.prompts(1, n, 500 + i, V)[0] for i, n in enumerate((9, 17, 5))]
     forced = synth.prompts(3, 5, 600, V)
     nxt, lg = s.prefill(prompts, want_logits=True)
@@ -44,14 +48,14 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def _run(tmp_path, d, ep, size, mode, tag):
+def _run(tmp_path, d, ep, size, mode, tag, fused=1):
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER % ROOT)
     meet = tmp_path / f"meet_{tag}"
     procs = []
     for r in range(size):
         out = tmp_path / f"out_{tag}_{r}.npz"
-        procs.append((subprocess.Popen([sys.executable, str(script), str(r), str(size), str(meet), d, ep, str(out), str(mode)],
+        procs.append((subprocess.Popen([sys.executable, str(script), str(r), str(size), str(meet), d, ep, str(out), str(mode), str(fused)],
                                        stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                                        env=dict(os.environ, NCCL_NVLS_ENABLE="0")), out))
     res = []
@@ -73,9 +77,14 @@ def test_two_ranks_match_one_gpu(model_dirs, tmp_path, mode):
         pytest.skip("needs two GPUs")
     d, ep, cfg = model_dirs["tiny"]  # 4 query / 2 kv heads, intermediate 512, vocabulary 1024: splits in two
     one = _run(tmp_path, d, ep, 1, mode, f"tp1_{mode}")[0]
-    two = _run(tmp_path, d, ep, 2, mode, f"tp2_{mode}")
-    # both ranks: identical results (they hold the same all-reduced sums and the same exchanged candidates)
-    assert (two[0]["logits"] == two[1]["logits"]).all() and (two[0]["tokens"] == two[1]["tokens"]).all()
+    two = _run(tmp_path, d, ep, 2, mode, f"tp2_{mode}")  # decode-sized launches over peer memory
+    nccl = _run(tmp_path, d, ep, 2, mode, f"tp2n_{mode}", fused=0)  # every all-reduce through NCCL
+    # both ranks: identical results (they hold the same sums, added in the same order, and the same exchanged
+    # candidates)
+    for res in (two, nccl):
+        assert (res[0]["logits"] == res[1]["logits"]).all() and (res[0]["tokens"] == res[1]["tokens"]).all()
+    # the two exchange paths add the same two fp32 partial sums (a + b = b + a) and share the row arithmetic
+    assert (two[0]["logits"] == nccl[0]["logits"]).all() and (two[0]["tokens"] == nccl[0]["tokens"]).all()
     a, b = two[0]["logits"], one["logits"]
     assert np.isfinite(a).all()
     assert np.abs(a - b).max() / np.abs(b).max() <= KERNEL_TOL
