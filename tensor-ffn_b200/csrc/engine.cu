@@ -26,10 +26,17 @@ void DeviceBuffer::alloc(size_t n) {
     TFFN_CUDA(cudaMemset(p, 0, n));
     TFFN_CUDA(cudaStreamSynchronize(0));
 }
+void DeviceBuffer::alloc_raw(size_t n) {
+    release();
+    if (n == 0) return;
+    TFFN_CUDA(cudaMalloc(&p, n));
+    bytes = n;
+}
 void DeviceBuffer::release() {
-    if (p) cudaFree(p);
+    if (p && owned) cudaFree(p);
     p = nullptr;
     bytes = 0;
+    owned = true;
 }
 
 namespace {
@@ -41,6 +48,83 @@ void upload(DeviceBuffer& dst, const void* src, size_t bytes) {
     // the streams that will read it are not ordered after the default stream
     TFFN_CUDA(cudaStreamSynchronize(0));
 }
+
+// Host-to-device staging for the loaders: the weight files are memory-mapped (pageable), so a plain
+// cudaMemcpy would page each tensor in, stage it inside the driver and block. Here the host thread copies the
+// next chunk out of the mapping into one of two pinned buffers while the copy engine still moves the previous
+// one; everything (copies, the re-layout kernels that follow them) is ordered on one stream and the loader
+// waits once at the end.
+class Stager {
+public:
+    explicit Stager(size_t chunk_bytes = (size_t)32 << 20) : chunk_(chunk_bytes) {
+        TFFN_CUDA(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            TFFN_CUDA(cudaMallocHost((void**)&buf_[i], chunk_));
+            TFFN_CUDA(cudaEventCreateWithFlags(&ev_[i], cudaEventDisableTiming));
+        }
+    }
+    ~Stager() {
+        cudaStreamSynchronize(s_);
+        for (int i = 0; i < 2; ++i) {
+            if (buf_[i]) cudaFreeHost(buf_[i]);
+            if (ev_[i]) cudaEventDestroy(ev_[i]);
+        }
+        cudaStreamDestroy(s_);
+    }
+    Stager(const Stager&) = delete;
+    Stager& operator=(const Stager&) = delete;
+    cudaStream_t stream() const { return s_; }
+    void copy(void* dst, const void* src, size_t bytes) {
+        for (size_t o = 0; o < bytes; o += chunk_) put((char*)dst + o, (const char*)src + o, std::min(chunk_, bytes - o), 0, 0, 0);
+    }
+    // `rows` rows of `width` bytes, `src_pitch` bytes apart in the mapping -> dense on the device
+    void copy2d(void* dst, const void* src, size_t src_pitch, size_t width, size_t rows) {
+        if (width == 0 || rows == 0) return;
+        if (src_pitch == width) return copy(dst, src, width * rows);
+        if (width > chunk_) throw Error(kErrUnsupported, "a matrix row is longer than the staging buffer");
+        const size_t rows_per = chunk_ / width;
+        for (size_t r = 0; r < rows; r += rows_per) {
+            const size_t nr = std::min(rows_per, rows - r);
+            put((char*)dst + r * width, (const char*)src + r * src_pitch, nr * width, src_pitch, width, nr);
+        }
+    }
+    void finish() { TFFN_CUDA(cudaStreamSynchronize(s_)); }
+
+private:
+    // one chunk: wait until the pinned buffer's previous transfer has left it, fill it, send it
+    void put(void* dst, const char* src, size_t bytes, size_t pitch, size_t width, size_t rows) {
+        uint8_t* b = buf_[cur_];
+        if (used_[cur_]) TFFN_CUDA(cudaEventSynchronize(ev_[cur_]));
+        if (rows == 0) {
+            memcpy(b, src, bytes);
+        } else {
+            for (size_t r = 0; r < rows; ++r) memcpy(b + r * width, src + r * pitch, width);
+        }
+        TFFN_CUDA(cudaMemcpyAsync(dst, b, bytes, cudaMemcpyHostToDevice, s_));
+        TFFN_CUDA(cudaEventRecord(ev_[cur_], s_));
+        used_[cur_] = true;
+        cur_ ^= 1;
+    }
+    size_t chunk_;
+    cudaStream_t s_ = nullptr;
+    uint8_t* buf_[2] = {nullptr, nullptr};
+    cudaEvent_t ev_[2] = {nullptr, nullptr};
+    bool used_[2] = {false, false};
+    int cur_ = 0;
+};
+
+// carves 256-byte aligned views out of one allocation
+struct Slab {
+    DeviceBuffer* mem;
+    size_t off = 0;
+    void take(DeviceBuffer& dst, size_t bytes) {
+        const size_t a = (off + 255) & ~(size_t)255;
+        if (a + bytes > mem->bytes) throw Error(kErrInvalid, "weight slab too small (internal size computation)");
+        dst.view((char*)mem->p + a, bytes);
+        off = a + bytes;
+    }
+    static size_t padded(size_t bytes) { return (bytes + 255) & ~(size_t)255; }
+};
 
 // one block: publish the picks as the next step's inputs, advance the sequence lengths
 __global__ void k_decode_advance(const int* __restrict__ picks, int n, int* __restrict__ dec_tokens, int* __restrict__ seq_len,
@@ -114,11 +198,6 @@ void Expert::forward_layers(const void* d_x, float* d_out, int T, cudaStream_t s
 }
 
 // ------------------------------------------------------------------------------------------ Model
-// column slice [c0, c0 + nc) of a row-major [rows, cols] bf16 host matrix -> dense [rows, nc] on the device
-static void upload_cols(void* dst, const uint16_t* src, size_t rows, size_t cols, size_t c0, size_t nc) {
-    TFFN_CUDA(cudaMemcpy2D(dst, nc * 2, src + c0, cols * 2, nc * 2, rows, cudaMemcpyHostToDevice));
-}
-
 Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size) {
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) throw Error(kErrCuda, "no CUDA device is available");
@@ -146,51 +225,70 @@ Model* Model::load(const std::string& dir, int device, int tp_rank, int tp_size)
     if (nh / nkv > 8 || nh % nkv != 0) throw Error(kErrUnsupported, "more than 8 query heads per kv head");
 
     SafeTensorsDir st(dir);
-    upload(m->embed, st.bf16("model.embed_tokens.weight", V * H), V * H * 2);  // replicated: a row gather only
-    m->layers.resize(c.num_layers);
     // this rank's rows of q / k / v (whole heads), columns of o_proj, rows of gate / up, columns of down
     const size_t nq = nh * hd, nk = nkv * hd, nqkv = nq + 2 * nk;
     const size_t q0 = (size_t)tp.q_head0 * hd, k0 = (size_t)tp.kv_head0 * hd;
     const size_t nq_full = nh_full * hd, nk_full = (size_t)c.num_kv_heads * hd;
+    const bool has_bias = st.has("model.layers.0.self_attn.q_proj.bias");  // same test as inference/src/model/qwen.cu:99
+    // one allocation for every weight (cudaMalloc and its zero-fill once, not ten times per layer)
+    {
+        size_t total = Slab::padded(V * H * 2) + Slab::padded(H * 2);
+        if (!c.tie_embeddings) total += Slab::padded((size_t)m->V * H * 2);
+        const size_t per_layer = Slab::padded(nqkv * H * 2) + Slab::padded(nqkv * 2) + Slab::padded(H * nq * 2) + 2 * Slab::padded(H * 2) +
+                                 Slab::padded(H * I * 2) + Slab::padded(I * 3 * H * 2);
+        total += per_layer * (size_t)c.num_layers + 256;
+        m->slab.alloc_raw(total);
+    }
+    Slab slab{&m->slab};
+    Stager up;
+    slab.take(m->embed, V * H * 2);
+    up.copy(m->embed.p, st.bf16("model.embed_tokens.weight", V * H), V * H * 2);  // replicated: a row gather only
+    m->layers.resize(c.num_layers);
     DeviceBuffer gate_tmp, up_tmp;
-    gate_tmp.alloc(I * H * 2);
-    up_tmp.alloc(I * H * 2);
+    gate_tmp.alloc_raw(I * H * 2);
+    up_tmp.alloc_raw(I * H * 2);
     for (int l = 0; l < c.num_layers; ++l) {
         LayerWeights& ly = m->layers[l];
         const std::string p = "model.layers." + std::to_string(l) + ".";
-        ly.wqkv.alloc(nqkv * H * 2);
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.weight", nq_full * H) + q0 * H, nq * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + nq * H, st.bf16(p + "self_attn.k_proj.weight", nk_full * H) + k0 * H, nk * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(ly.wqkv.as<bf16>() + (nq + nk) * H, st.bf16(p + "self_attn.v_proj.weight", nk_full * H) + k0 * H, nk * H * 2, cudaMemcpyHostToDevice));
-        if (st.has(p + "self_attn.q_proj.bias")) {  // same test as inference/src/model/qwen.cu:99
+        slab.take(ly.wqkv, nqkv * H * 2);
+        up.copy(ly.wqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.weight", nq_full * H) + q0 * H, nq * H * 2);
+        up.copy(ly.wqkv.as<bf16>() + nq * H, st.bf16(p + "self_attn.k_proj.weight", nk_full * H) + k0 * H, nk * H * 2);
+        up.copy(ly.wqkv.as<bf16>() + (nq + nk) * H, st.bf16(p + "self_attn.v_proj.weight", nk_full * H) + k0 * H, nk * H * 2);
+        if (st.has(p + "self_attn.q_proj.bias")) {
+            if (!has_bias) throw Error(kErrFormat, "some layers have projection biases and some do not");
             ly.has_bias = true;
-            ly.bqkv.alloc(nqkv * 2);
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.bias", nq_full) + q0, nq * 2, cudaMemcpyHostToDevice));
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq, st.bf16(p + "self_attn.k_proj.bias", nk_full) + k0, nk * 2, cudaMemcpyHostToDevice));
-            TFFN_CUDA(cudaMemcpy(ly.bqkv.as<bf16>() + nq + nk, st.bf16(p + "self_attn.v_proj.bias", nk_full) + k0, nk * 2, cudaMemcpyHostToDevice));
+            slab.take(ly.bqkv, nqkv * 2);
+            up.copy(ly.bqkv.as<bf16>(), st.bf16(p + "self_attn.q_proj.bias", nq_full) + q0, nq * 2);
+            up.copy(ly.bqkv.as<bf16>() + nq, st.bf16(p + "self_attn.k_proj.bias", nk_full) + k0, nk * 2);
+            up.copy(ly.bqkv.as<bf16>() + nq + nk, st.bf16(p + "self_attn.v_proj.bias", nk_full) + k0, nk * 2);
         }
-        ly.wo.alloc(H * nq * 2);
-        upload_cols(ly.wo.p, st.bf16(p + "self_attn.o_proj.weight", H * nq_full), H, nq_full, q0, nq);
-        upload(ly.attn_norm, st.bf16(p + "input_layernorm.weight", H), H * 2);
-        upload(ly.ffn_norm, st.bf16(p + "post_attention_layernorm.weight", H), H * 2);
-        TFFN_CUDA(cudaMemcpy(gate_tmp.p, st.bf16(p + "mlp.gate_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2, cudaMemcpyHostToDevice));
-        TFFN_CUDA(cudaMemcpy(up_tmp.p, st.bf16(p + "mlp.up_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2, cudaMemcpyHostToDevice));
-        ly.ffn.down.alloc(H * I * 2);
-        upload_cols(ly.ffn.down.p, st.bf16(p + "mlp.down_proj.weight", H * Ifull), H, Ifull, tp.i0, I);
-        TFFN_CUDA(cudaStreamSynchronize(0));
-        ly.ffn.packed.alloc(I * 3 * H * 2);
-        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), ly.ffn.down.as<bf16>(), ly.ffn.packed.as<bf16>(), (int)I, (int)H, 0);
+        slab.take(ly.wo, H * nq * 2);
+        up.copy2d(ly.wo.p, st.bf16(p + "self_attn.o_proj.weight", H * nq_full) + q0, nq_full * 2, nq * 2, H);
+        slab.take(ly.attn_norm, H * 2);
+        up.copy(ly.attn_norm.p, st.bf16(p + "input_layernorm.weight", H), H * 2);
+        slab.take(ly.ffn_norm, H * 2);
+        up.copy(ly.ffn_norm.p, st.bf16(p + "post_attention_layernorm.weight", H), H * 2);
+        // gate and up pass through two scratch matrices (reused by every layer: the copies and the kernel that
+        // reads them are ordered on the staging stream), down goes to its place and into the records
+        up.copy(gate_tmp.p, st.bf16(p + "mlp.gate_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2);
+        up.copy(up_tmp.p, st.bf16(p + "mlp.up_proj.weight", Ifull * H) + (size_t)tp.i0 * H, I * H * 2);
+        slab.take(ly.ffn.down, H * I * 2);
+        up.copy2d(ly.ffn.down.p, st.bf16(p + "mlp.down_proj.weight", H * Ifull) + tp.i0, Ifull * 2, I * 2, H);
+        slab.take(ly.ffn.packed, I * 3 * H * 2);
+        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), ly.ffn.down.as<bf16>(), ly.ffn.packed.as<bf16>(), (int)I, (int)H, up.stream());
         TFFN_CUDA(cudaGetLastError());
-        TFFN_CUDA(cudaDeviceSynchronize());
     }
-    upload(m->final_norm, st.bf16("model.norm.weight", H), H * 2);
+    slab.take(m->final_norm, H * 2);
+    up.copy(m->final_norm.p, st.bf16("model.norm.weight", H), H * 2);
     // LM head: this rank's rows of the vocabulary
     if (c.tie_embeddings) {
         m->lm_head = m->embed.as<bf16>() + (size_t)tp.v0 * H;
     } else {
-        upload(m->lm_head_own, st.bf16("lm_head.weight", V * H) + (size_t)tp.v0 * H, (size_t)m->V * H * 2);
+        slab.take(m->lm_head_own, (size_t)m->V * H * 2);
+        up.copy(m->lm_head_own.p, st.bf16("lm_head.weight", V * H) + (size_t)tp.v0 * H, (size_t)m->V * H * 2);
         m->lm_head = m->lm_head_own.as<bf16>();
     }
+    up.finish();  // the only wait of the load; the scratch matrices are released after it
     m->bs1_ok = tp_size == 1 && bs1_supported((int)H, (int)I, (int)hd, (int)nh, (int)nkv);
     const uint64_t per_layer = (nqkv * H + H * nq + 3 * I * H) * 2 + 2 * H * 2 + (uint64_t)(m->layers[0].has_bias ? nqkv * 2 : 0);
     m->weight_bytes_base = per_layer * c.num_layers + (uint64_t)m->V * H * 2 + H * 2;
@@ -218,28 +316,33 @@ Expert* Expert::load(const Model* m, const std::string& path, float scale) {
     e->scale = scale;
     const size_t H = c.hidden_size, Ifull = c.intermediate_size, I = m->I, i0 = m->tp.i0, n = H * I;
     e->layers.resize(c.num_layers);
+    e->slab.alloc_raw((Slab::padded(n * 2) + Slab::padded(n * 3 * 2)) * (size_t)c.num_layers + 256);
+    Slab slab{&e->slab};
+    Stager up;
+    // fp32 matrices arrive in a device scratch buffer and are cast to bf16 on the staging stream, which orders
+    // the buffer's reuse; no wait until the end
     DeviceBuffer stage, gate_tmp, up_tmp;
-    stage.alloc(n * 4);
-    gate_tmp.alloc(n * 2);
-    up_tmp.alloc(n * 2);
+    stage.alloc_raw(n * 4);
+    gate_tmp.alloc_raw(n * 2);
+    up_tmp.alloc_raw(n * 2);
     for (int l = 0; l < c.num_layers; ++l) {
         FfnWeights& f = e->layers[l];
-        f.down.alloc(n * 2);
-        f.packed.alloc(n * 3 * 2);
+        slab.take(f.down, n * 2);
+        slab.take(f.packed, n * 3 * 2);
         bf16* dst[3] = {gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>()};
         for (int k = 0; k < 3; ++k) {
+            DeviceBuffer& sb = stage;
             if (k < 2)  // rows i0 .. i0 + I of [Ifull, H]
-                TFFN_CUDA(cudaMemcpy(stage.p, ef.matrix(l, k) + i0 * H, n * 4, cudaMemcpyHostToDevice));
+                up.copy(sb.p, ef.matrix(l, k) + i0 * H, n * 4);
             else        // columns i0 .. i0 + I of [H, Ifull]
-                TFFN_CUDA(cudaMemcpy2D(stage.p, I * 4, ef.matrix(l, k) + i0, Ifull * 4, I * 4, H, cudaMemcpyHostToDevice));
-            launch_cast_f32_bf16(stage.as<float>(), dst[k], n, 0);
+                up.copy2d(sb.p, ef.matrix(l, k) + i0, Ifull * 4, I * 4, H);
+            launch_cast_f32_bf16(sb.as<float>(), dst[k], n, up.stream());
             TFFN_CUDA(cudaGetLastError());
-            TFFN_CUDA(cudaDeviceSynchronize());
         }
-        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>(), f.packed.as<bf16>(), (int)I, (int)H, 0);
+        launch_pack_ffn(gate_tmp.as<bf16>(), up_tmp.as<bf16>(), f.down.as<bf16>(), f.packed.as<bf16>(), (int)I, (int)H, up.stream());
         TFFN_CUDA(cudaGetLastError());
-        TFFN_CUDA(cudaDeviceSynchronize());
     }
+    up.finish();
     e->weight_bytes = (uint64_t)c.num_layers * 3 * n * 2;
     return e.release();
 }
@@ -391,6 +494,7 @@ Session::~Session() {
     cudaSetDevice(m_->device);
     cudaStreamSynchronize(stream_);
     drop_graphs();
+    tmap_cache_free(tmaps_);
     if (tp_ && tp_win_.p) {
         // collective, like the constructor: the window may be freed only when no peer has it mapped any more;
         // if a peer does not arrive, the window is left allocated
@@ -419,6 +523,7 @@ GemmWorkspace Session::gemm_ws() const {
     GemmWorkspace w;
     w.status = status_.as<int>();
     w.num_sms = m_->num_sms;
+    w.tmaps = tmaps_;
     return w;
 }
 AttnWorkspace Session::attn_ws() const {

@@ -18,12 +18,15 @@ void cuda_check(cudaError_t e, const char* what, const char* file, int line);
 struct DeviceBuffer {
     void* p = nullptr;
     size_t bytes = 0;
+    bool owned = true;  // false: a view into a slab that somebody else frees
     DeviceBuffer() = default;
     DeviceBuffer(const DeviceBuffer&) = delete;
     DeviceBuffer& operator=(const DeviceBuffer&) = delete;
-    DeviceBuffer(DeviceBuffer&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+    DeviceBuffer(DeviceBuffer&& o) noexcept : p(o.p), bytes(o.bytes), owned(o.owned) { o.p = nullptr; o.bytes = 0; }
     ~DeviceBuffer() { release(); }
     void alloc(size_t n);  // zero-filled
+    void alloc_raw(size_t n);  // not filled: for buffers that are overwritten whole before anything reads them
+    void view(void* ptr, size_t n) { release(); p = ptr; bytes = n; owned = false; }
     void release();
     template <typename T>
     T* as() const { return (T*)p; }
@@ -62,6 +65,7 @@ struct Model {
     // this rank's sizes: query heads, kv heads, intermediate rows, LM-head rows
     int nh = 0, nkv = 0, I = 0, V = 0;
     int device = 0, num_sms = 0;
+    DeviceBuffer slab;  // the one allocation every weight below is a view of
     DeviceBuffer embed, final_norm, lm_head_own;
     const bf16* lm_head = nullptr;
     std::vector<LayerWeights> layers;
@@ -73,6 +77,7 @@ struct Model {
 struct Expert {
     const Model* model = nullptr;
     float scale = 0.1f;
+    DeviceBuffer slab;  // the one allocation the layers' buffers are views of
     std::vector<FfnWeights> layers;
     uint64_t weight_bytes = 0;
     static Expert* load(const Model* m, const std::string& path, float scale);
@@ -216,6 +221,7 @@ private:
     int hidden_rows_cap_ = 0, hidden_rows_ = 0;
 
     GemmWorkspace gemm_ws() const;
+    TmapCache* tmaps_ = tmap_cache_create();  // encoded tensor maps of this session's GEMM launches
     AttnWorkspace attn_ws() const;
     void ensure_pages(int slot, int new_len);
     void flush_tables();

@@ -603,21 +603,7 @@ struct TmapKeyHash {
 
 bool encode_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows);
 
-// Encoding a tensor map costs microseconds of host time; the same (buffer, shape, box) recurs on
-// every step, so encoded maps are kept per thread (a session is used by one thread at a time).
-bool make_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
-    static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-    TmapKey key{ptr, rows, cols, ld_elems, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) {
-        *tm = it->second;
-        return true;
-    }
-    if (!encode_tmap(tm, ptr, rows, cols, ld_elems, box_rows)) return false;
-    if (cache.size() > 65536) cache.clear();
-    cache.emplace(key, *tm);
-    return true;
-}
+bool make_tmap(TmapCache* cache, CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows);
 
 // 2-D bf16 tensor [rows, cols] with a row stride, box = box_rows x 64 columns, 128-byte swizzle
 bool encode_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
@@ -631,6 +617,29 @@ bool encode_tmap(CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+struct TmapCache {
+    std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> maps;
+};
+TmapCache* tmap_cache_create() { return new TmapCache(); }
+void tmap_cache_free(TmapCache* c) { delete c; }
+
+namespace {
+
+bool make_tmap(TmapCache* cache, CUtensorMap* tm, const bf16* ptr, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
+    if (!cache) return encode_tmap(tm, ptr, rows, cols, ld_elems, box_rows);
+    TmapKey key{ptr, rows, cols, ld_elems, box_rows};
+    auto it = cache->maps.find(key);
+    if (it != cache->maps.end()) {
+        *tm = it->second;
+        return true;
+    }
+    if (!encode_tmap(tm, ptr, rows, cols, ld_elems, box_rows)) return false;
+    cache->maps.emplace(key, *tm);
+    return true;
 }
 
 template <int BN>
@@ -648,8 +657,8 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
             if (pr == 0) p.kblocks[i] = o.K > 0 ? (o.K + BK - 1) / BK : 0;
             if (o.K <= 0) continue;
             if (pr == 1 && (o.K + BK - 1) / BK != p.kblocks[i]) return (int)cudaErrorInvalidValue;
-            if (!make_tmap(&p.tmW[pr * 2 + i], o.W, (uint64_t)c.N, (uint64_t)o.K, (uint64_t)o.ldw, halves ? BM / 2 : BM)) return -1000;
-            if (!make_tmap(&p.tmX[pr * 2 + i], o.X, (uint64_t)(c.x_rows_alloc > c.T ? c.x_rows_alloc : c.T), (uint64_t)o.K,
+            if (!make_tmap(ws.tmaps, &p.tmW[pr * 2 + i], o.W, (uint64_t)c.N, (uint64_t)o.K, (uint64_t)o.ldw, halves ? BM / 2 : BM)) return -1000;
+            if (!make_tmap(ws.tmaps, &p.tmX[pr * 2 + i], o.X, (uint64_t)(c.x_rows_alloc > c.T ? c.x_rows_alloc : c.T), (uint64_t)o.K,
                            (uint64_t)o.ldx, BN))
                 return -1000;
         }

@@ -76,9 +76,17 @@ struct GemmCall {
     unsigned long long* tl;  // optional 6 u64 of the step timeline (see tl_mark)
     bool pdl;          // launch with programmatic dependent launch (the kernel waits before touching X / out)
 };
+// Encoded tensor maps of the (buffer, shape, box) combinations a caller keeps launching with: encoding one costs
+// microseconds of host time and a decode step needs about 200. Owned by whoever owns the buffers (a session keeps
+// one for its lifetime), so entries die with the buffers they describe.
+struct TmapCache;
+TmapCache* tmap_cache_create();
+void tmap_cache_free(TmapCache* c);
+
 struct GemmWorkspace {
     int* status;  // device status word
     int num_sms;
+    TmapCache* tmaps = nullptr;  // optional; without it every launch encodes its maps
 };
 // opt the kernels into their dynamic shared memory sizes (once per device, outside stream capture)
 int gemm_prepare();

@@ -42,6 +42,9 @@ SHAPES = {
     # the same head geometry with an intermediate size that is a multiple of 256
     "mini_s": (dict(hidden_size=448, num_hidden_layers=3, num_attention_heads=7, num_key_value_heads=1,
                     intermediate_size=768, vocab_size=1000, tie_word_embeddings=True), True),
+    # the 7B head geometry (7 query heads per kv head, more than one kv head) for tensor-parallel splits of 2, 4 and 8
+    "mini7": (dict(hidden_size=896, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
+                   intermediate_size=1024, vocab_size=2048, tie_word_embeddings=False), True),
 }
 
 

@@ -93,3 +93,22 @@ def test_two_ranks_match_one_gpu(model_dirs, tmp_path, mode):
     err = np.abs(a - b).max()
     gap = np.take_along_axis(b, pb[..., None], -1)[..., 0] - np.take_along_axis(b, pa[..., None], -1)[..., 0]
     assert ((pa == pb) | (gap <= 2 * err)).all()
+
+
+@pytest.mark.parametrize("size", [4, 8])
+def test_wider_groups_split_a_kv_head(model_dirs, tmp_path, size):
+    """4 and 8 ranks on the 7B head geometry (14 query / 2 kv heads): two or four ranks share a kv head and
+    split its seven query heads 3 + 4 or 1 + 2 + 2 + 2. All ranks identical, within tolerance of one GPU,
+    through both exchange paths."""
+    import tffn
+    if tffn.device_count() < size:
+        pytest.skip(f"needs {size} GPUs")
+    d, ep, cfg = model_dirs["mini7"]
+    one = _run(tmp_path, d, ep, 1, 2, "w_tp1")[0]
+    for fused in (1, 0):
+        res = _run(tmp_path, d, ep, size, 2, f"w_tp{size}_{fused}", fused=fused)
+        for r in res[1:]:
+            assert (res[0]["logits"] == r["logits"]).all() and (res[0]["tokens"] == r["tokens"]).all()
+        a, b = res[0]["logits"], one["logits"]
+        assert np.isfinite(a).all()
+        assert np.abs(a - b).max() / np.abs(b).max() <= KERNEL_TOL, (size, fused)
