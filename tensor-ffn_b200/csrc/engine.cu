@@ -794,7 +794,7 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
     auto reduce_fused = [&](int which, const bf16* norm_w) {
         prof_begin(KC_ALLREDUCE);
         launch_tp_reduce_residual_norm(h_.as<bf16>(), tp_parts_[which], tp_sync_, norm_w, xn_.as<bf16>(), T, H, c.rms_norm_eps,
-                                       status_.as<int>(), stream_, pdl);
+                                       status_.as<int>(), stream_, pdl, tl_next(KC_ALLREDUCE));
         prof_end();
         launches_++;
     };

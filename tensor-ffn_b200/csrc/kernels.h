@@ -134,7 +134,7 @@ struct TpParts {
 // h += sum over ranks p (in rank order) of part[p][row * H ...], then out = RMSNorm(h) * w (w == nullptr: no
 // norm). T <= kTpFlagBlocks rows, H a multiple of 4.
 void launch_tp_reduce_residual_norm(bf16* h, const TpParts& parts, const TpPeerSync& sync, const bf16* w, bf16* out, int T, int H,
-                                    float eps, int* status, cudaStream_t s, bool pdl = false);
+                                    float eps, int* status, cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
 // launch_tp_pick over the candidates the ranks pushed into this rank's window (cand[rank * stride + row]), after a
 // hand-shake with the peers; R <= 128 * kTpFlagBlocks rows
 void launch_tp_pick_peer(const void* cand, size_t stride, const TpPeerSync& sync, int R, int* out, int* status, cudaStream_t s,

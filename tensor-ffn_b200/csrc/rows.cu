@@ -344,12 +344,14 @@ __device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) {
 // store has to be fenced across GPUs. One block per row; all loads of a thread are issued before the adds.
 __global__ void __launch_bounds__(kRowNormThreads) k_tp_reduce_residual_norm(bf16* __restrict__ h, TpParts parts, TpPeerSync sync,
                                                                   const bf16* __restrict__ w, bf16* __restrict__ out, int H,
-                                                                  float eps, int* status) {
+                                                                  float eps, int* status, unsigned long long* tl) {
+    if (threadIdx.x == 0) tl_mark(tl, 0);
     pdl_launch_dependents();
     pdl_wait();
     __shared__ unsigned s_count;
     __shared__ float s_red[kRowNormThreads / 32];
     tp_handshake(sync, status, &s_count);
+    if (threadIdx.x == 0) tl_mark(tl, 1);  // the peers' parts are there: what follows is the transfer and the arithmetic
     const int r = blockIdx.x;
     const size_t row = (size_t)r * H;
     const int R = sync.size;
@@ -369,6 +371,7 @@ __global__ void __launch_bounds__(kRowNormThreads) k_tp_reduce_residual_norm(bf1
             }
         return acc;
     });
+    if (threadIdx.x == 0) tl_mark(tl, 2);
 }
 
 // Temperature sampling on the device, the arithmetic of sample() (inference/src/main.cpp:52-63): float
@@ -527,8 +530,8 @@ void launch_residual_norm(bf16* h, const float* delta, const bf16* w, bf16* out,
     launch_k(k_residual_norm_rows, dim3(T), dim3(kRowNormThreads), 0, s, pdl, h, delta, w, out, H, eps);
 }
 void launch_tp_reduce_residual_norm(bf16* h, const TpParts& parts, const TpPeerSync& sync, const bf16* w, bf16* out, int T, int H,
-                                    float eps, int* status, cudaStream_t s, bool pdl) {
-    launch_k(k_tp_reduce_residual_norm, dim3(T), dim3(kRowNormThreads), 0, s, pdl, h, parts, sync, w, out, H, eps, status);
+                                    float eps, int* status, cudaStream_t s, bool pdl, unsigned long long* tl) {
+    launch_k(k_tp_reduce_residual_norm, dim3(T), dim3(kRowNormThreads), 0, s, pdl, h, parts, sync, w, out, H, eps, status, tl);
 }
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl, unsigned long long* tl) {
