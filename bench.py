@@ -347,6 +347,13 @@ def run_ours(a):
         in_situ = {"step_us": (int(tl[:, 5].max()) - int(tl[:, 0].min())) / 1e3,
                    "kernels": [{"kernel": nm, "launches": v[0], "us_per_launch": v[1] / v[0]}
                                for nm, v in sorted(agg.items(), key=lambda kv: -kv[1][1])]}
+        # tensor parallel over peer memory: of what the exchange kernel adds to the step, how long the last block
+        # waited for its peers after its own dependency wait was over is not in the stamps separately; what is:
+        # entry -> hand-shake over (max over blocks) and hand-shake over -> exit
+        ex = [(int(r[3]) - int(r[0]), int(r[5]) - int(r[3])) for nm, r in zip(names, tl) if nm == "tp_all_reduce"]
+        if ex:
+            in_situ["tp_all_reduce_phases_us"] = {"entry_to_handshake_over": sum(x[0] for x in ex) / len(ex) / 1e3,
+                                                  "handshake_over_to_exit": sum(x[1] for x in ex) / len(ex) / 1e3}
         gemm_us = sum(v[1] for nm, v in agg.items() if nm.startswith("gemm_tc:"))
         if gemm_us > 0:
             roofline["achieved"] = gemm_bytes / 1e9 / (gemm_us / 1e6)
@@ -373,6 +380,11 @@ def run_ours(a):
                    "all_reduce_bytes": n * cfg["hidden_size"] * 4,
                    "per_rank_roofline_frac": step_roofline["frac"],
                    "per_rank_roofline_frac_without_all_reduce": step_bytes / 1e9 / max(ms / K - ar[0] / P, 1e-6) * 1e3 / peak}
+        if in_situ and "kernels" in in_situ:  # what an exchange adds to the running step (peer-memory path only: NCCL kernels carry no stamps)
+            for kk in in_situ["kernels"]:
+                if kk["kernel"] == "tp_all_reduce":
+                    tp_info["all_reduce_us_per_call_in_situ"] = kk["us_per_launch"]
+                    tp_info["all_reduce_share_of_step_in_situ"] = kk["us_per_launch"] * kk["launches"] / in_situ["step_us"]
 
     # ---- end to end through the C ABI with host buffers (e2e)
     e2e = None

@@ -130,7 +130,7 @@ void tffn_session_free(tffn_session* s);
  * the same tokens (and full logits) on every rank. Inside a step the ranks' partial sums of o_proj
  * and of the down projections (base + scale * expert, summed locally first) are summed over the ranks in
  * fp32 before the one bf16 rounding of the residual add, and the greedy pick exchanges one (max, index)
- * pair per sequence and rank. Launches of up to 256 tokens (decode) exchange the partial sums through peer
+ * pair per sequence and rank. Launches of up to 128 tokens (decode) exchange the partial sums through peer
  * memory over NVLink: every rank exports an exchange window (CUDA IPC, so the ranks must be processes on one
  * machine whose GPUs have peer access), the projections leave their fp32 partial sums in their own rank's
  * window, and the row kernel that adds the residual and forms the next RMSNorm first hand-shakes with its

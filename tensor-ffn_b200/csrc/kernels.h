@@ -107,8 +107,10 @@ void launch_rmsnorm(const bf16* x, const bf16* w, bf16* out, int T, int H, float
 void launch_sample(const float* logits, int R, int V, float temperature, const double* u, const int* step_counter, int* out,
                    cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
 // Tensor parallel over peer memory (decode-sized launches). Every rank owns an exchange window that the
-// other ranks of the group have mapped; kTpFlagBlocks = the largest grid of a kernel that hand-shakes.
-constexpr int kTpFlagBlocks = 256;
+// other ranks of the group have mapped; kTpFlagBlocks = the largest grid of a kernel that hand-shakes. Block b
+// waits for block b of every peer, so all blocks of such a grid have to be resident at once on every rank
+// whatever order the hardware starts them in: 128 blocks of 1 024 threads fit the 148 SMs of a B200.
+constexpr int kTpFlagBlocks = 128;
 struct TpPeerSync {
     unsigned* flags_local;              // this rank's window: [size][kTpFlagBlocks] counters, written by the peers
     unsigned* flags_peer[kTpMaxRanks];  // the same array inside every peer's window
