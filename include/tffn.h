@@ -136,8 +136,8 @@ void tffn_session_free(tffn_session* s);
  * window, and the row kernel that adds the residual and forms the next RMSNorm first hand-shakes with its
  * peers through flags in those windows (bounded wait: a peer that never arrives gives TFFN_ERR_DEVICE
  * status after 10 s, not a hang), then loads every rank's part over NVLink and adds them in rank order; the
- * greedy pick's candidates are stored into every rank's window and fenced by the storing thread. Larger launches
- * (prefill) use ncclAllReduce. Creating and freeing a tensor-parallel session are collective calls.
+ * greedy pick exchanges its candidates the same way. The only stores that cross GPUs are the flags. Larger
+ * launches (prefill) use ncclAllReduce. Creating and freeing a tensor-parallel session are collective calls.
  * Sampling and tffn_expert_forward are not available on a tensor-parallel model. NCCL (libnccl.so.2) is
  * opened at run time. */
 typedef struct tffn_tp tffn_tp;

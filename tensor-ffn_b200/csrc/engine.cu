@@ -463,9 +463,7 @@ Session::Session(const Model* m, const Expert* e, int max_batch, int max_seq, cu
         tp_pick_sync_.flags_local += (size_t)kTpMaxRanks * kTpFlagBlocks;
         for (int p = 0; p < R; ++p) tp_pick_sync_.flags_peer[p] += (size_t)kTpMaxRanks * kTpFlagBlocks;
         tp_pick_sync_.calls += kTpFlagBlocks;
-        tp_pick_push_.n = R;
-        for (int p = 0; p < kTpMaxRanks; ++p)
-            tp_pick_push_.dst[p] = p < R ? (float2*)((char*)tp_peers_[p] + tp_pick_off_) + (size_t)m_->tp.tp_rank * tp_small_rows_ : nullptr;
+        for (int p = 0; p < kTpMaxRanks; ++p) tp_pick_parts_.part[p] = p < R ? (const float2*)((const char*)tp_peers_[p] + tp_pick_off_) : nullptr;
     }
     ensure_logits(std::max<size_t>(256, max_batch));
     attn_partials_.alloc((size_t)32 << 20);
@@ -983,11 +981,11 @@ void Session::run_batched(int T, int n_logit_rows, bool logit_rows_are_all, bool
                 const size_t bytes = (size_t)n_logit_rows * 8;
                 if (tp_pick_send_.bytes < bytes) throw Error(kErrCapacity, "tensor parallel: more logits rows than the session was sized for");
                 if (tp_fused_ && n_logit_rows <= tp_small_rows_) {
-                    // candidates pushed into every rank's window, hand-shake in the pick kernel: no NCCL call in a decode step
+                    // candidates left in this rank's window, the pick kernel hand-shakes and loads every rank's: no NCCL call
+                    // in a decode step
                     launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),
-                                        nullptr, m_->tp.v0, &tp_pick_push_);
-                    launch_tp_pick_peer((const char*)tp_win_.p + tp_pick_off_, (size_t)tp_small_rows_, tp_pick_sync_, n_logit_rows,
-                                        picks_.as<int>(), status_.as<int>(), stream_, pdl);
+                                        (char*)tp_win_.p + tp_pick_off_, m_->tp.v0);
+                    launch_tp_pick_peer(tp_pick_parts_, tp_pick_sync_, n_logit_rows, picks_.as<int>(), status_.as<int>(), stream_, pdl);
                     launches_ += 1;
                 } else {
                     launch_argmax_tiles(g.amax_val, g.amax_idx, n_logit_rows, v_tiles, picks_.as<int>(), stream_, pdl, tl_next(KC_ARGMAX),

@@ -146,8 +146,8 @@ private:
     size_t tp_part_off_[2] = {0, 0};  // in floats, from the window's start
     TpParts tp_parts_[2];
     TpPeerSync tp_sync_, tp_pick_sync_;
-    TpPickPush tp_pick_push_;
-    size_t tp_pick_off_ = 0;  // in bytes: [ranks][tp_small_rows_] candidates of 8 bytes
+    TpPickParts tp_pick_parts_;
+    size_t tp_pick_off_ = 0;  // in bytes: [tp_small_rows_] candidates of 8 bytes
     bool tp_fused_ = true;
     void copy_logits_to_host(float* dst, size_t rows);  // rows of logits_ (this rank's vocabulary slice) -> full rows on the host
     int max_batch_, max_seq_, max_pages_per_seq_, num_pages_;

@@ -118,17 +118,15 @@ struct TpPeerSync {
     int rank, size;
     unsigned long long wait_ns;         // how long a block waits for its peers before it gives up
 };
-// destinations of a rank's pick candidates: its row array inside every rank's window
-struct TpPickPush {
-    float2* dst[kTpMaxRanks];
-    int n;
+// the ranks' pick candidates: part[p] = rank p's {maximum, global index} per row as mapped into this process
+struct TpPickParts {
+    const float2* part[kTpMaxRanks];
 };
 // per-tile maxima left by the GEMM (GemmCall::amax_val / amax_idx, `tiles` per row) -> argmax per row
 // pack (optional, 8 bytes per row): {the row's maximum, idx_offset + its index} for the exchange between
 // tensor-parallel ranks, which launch_tp_pick resolves (cand = `ranks` such arrays of R rows back to back)
 void launch_argmax_tiles(const float* amax_val, const int* amax_idx, int R, int tiles, int* out, cudaStream_t s,
-                         bool pdl = false, unsigned long long* tl = nullptr, void* pack = nullptr, int idx_offset = 0,
-                         const TpPickPush* push = nullptr);  // push: also store the candidate into every rank's window
+                         bool pdl = false, unsigned long long* tl = nullptr, void* pack = nullptr, int idx_offset = 0);
 // the ranks' partial sums of one exchange: part[p] = rank p's fp32 [rows][H] buffer as mapped into this process
 struct TpParts {
     const float* part[kTpMaxRanks];
@@ -137,9 +135,9 @@ struct TpParts {
 // norm). T <= kTpFlagBlocks rows, H a multiple of 4.
 void launch_tp_reduce_residual_norm(bf16* h, const TpParts& parts, const TpPeerSync& sync, const bf16* w, bf16* out, int T, int H,
                                     float eps, int* status, cudaStream_t s, bool pdl = false, unsigned long long* tl = nullptr);
-// launch_tp_pick over the candidates the ranks pushed into this rank's window (cand[rank * stride + row]), after a
-// hand-shake with the peers; R <= 128 * kTpFlagBlocks rows
-void launch_tp_pick_peer(const void* cand, size_t stride, const TpPeerSync& sync, int R, int* out, int* status, cudaStream_t s,
+// launch_tp_pick over the candidates every rank left in its own window (launch_argmax_tiles' pack), loaded over
+// NVLink after a hand-shake with the peers; R <= 128 * kTpFlagBlocks rows
+void launch_tp_pick_peer(const TpPickParts& parts, const TpPeerSync& sync, int R, int* out, int* status, cudaStream_t s,
                          bool pdl = false);
 void launch_tp_pick(const void* cand, int ranks, int R, int* out, cudaStream_t s, bool pdl = false);
 // tensor parallel: h = bf16(h + delta) and, if w != null, out = rmsnorm(h) * w, per row
