@@ -23,6 +23,7 @@
 #include <cstdio>
 #include <cstring>
 #include <functional>
+#include <mutex>
 #include <unordered_map>
 
 namespace tffn {
@@ -642,6 +643,29 @@ bool make_tmap(TmapCache* cache, CUtensorMap* tm, const bf16* ptr, uint64_t rows
     return true;
 }
 
+// clusters of `splits` CTAs of k_gemm_tc<BN> with `stages` ring stages that can be resident at once on the
+// current device (cudaOccupancyMaxActiveClusters; remembered per configuration)
+template <int BN>
+int max_active_clusters(const cudaLaunchConfig_t& cfg, int stages, int splits) {
+    static std::mutex mu;
+    static std::unordered_map<long long, int> seen;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const long long key = ((long long)dev << 32) | ((long long)stages << 8) | splits;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = seen.find(key);
+    if (it != seen.end()) return it->second;
+    int n = 0;
+    cudaLaunchConfig_t q = cfg;
+    q.dynamicSmemBytes = GemmCfg<BN>::smem_bytes(stages);
+    if (cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<BN>, &q) != cudaSuccess) {
+        cudaGetLastError();
+        n = 1 << 30;  // unknown: keep the configuration
+    }
+    seen.emplace(key, n);
+    return n;
+}
+
 template <int BN>
 int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, int force_splits) {
     using Cfg = GemmCfg<BN>;
@@ -742,6 +766,22 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    if (splits > 1 && !shared_sm) {
+        // A cluster lives inside one GPC. With deep rings (one CTA per SM) a GPC of 18 SMs holds two clusters
+        // of 8 and leaves two SMs empty, so that 18 clusters need a second wave (seen on the 7B shape over two
+        // ranks: q|k|v, 18 clusters of 8 with 7-stage rings, 2 clusters started 14 us late). Ask how many
+        // clusters of this launch can be resident at once and, if they are fewer than the grid has, give up
+        // ring depth (not below three stages or what the epilogue plane needs) until they all fit. Grids of
+        // more CTAs than SMs already run their shallow shared-SM rings and are left alone.
+        const int clusters = n_tiles * t_tiles * nprob;
+        const int iters = (total_kb + splits - 1) / splits;
+        const int plane_stages = (BN * BM * 4 + BN * 8 + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
+        const int floor_stages = plane_stages > 3 ? plane_stages : (iters < 3 ? iters : 3);
+        while (p.stages > floor_stages && max_active_clusters<BN>(cfg, p.stages, splits) < clusters) {
+            --p.stages;
+            cfg.dynamicSmemBytes = Cfg::smem_bytes(p.stages);
+        }
+    }
     return (int)cudaLaunchKernelEx(&cfg, k_gemm_tc<BN>, p);
 }
 
