@@ -776,7 +776,8 @@ int launch_bn(const GemmCall& c, const GemmWorkspace& ws, cudaStream_t stream, i
         const int clusters = n_tiles * t_tiles * nprob;
         const int iters = (total_kb + splits - 1) / splits;
         const int plane_stages = (BN * BM * 4 + BN * 8 + Cfg::STAGE_BYTES - 1) / Cfg::STAGE_BYTES;
-        const int floor_stages = plane_stages > 3 ? plane_stages : (iters < 3 ? iters : 3);
+        const int want_stages = iters < 3 ? iters : 3;
+        const int floor_stages = plane_stages > want_stages ? plane_stages : want_stages;  // never below the parked plane
         while (p.stages > floor_stages && max_active_clusters<BN>(cfg, p.stages, splits) < clusters) {
             --p.stages;
             cfg.dynamicSmemBytes = Cfg::smem_bytes(p.stages);

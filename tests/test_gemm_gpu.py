@@ -16,7 +16,10 @@ def _ref(X, W):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (5, 256, 128), (16, 384, 448), (17, 1000, 896), (64, 1152, 896),
-                                   (100, 640, 256), (200, 448, 608), (300, 896, 4864), (513, 256, 64)])
+                                   (100, 640, 256), (200, 448, 608), (300, 896, 4864), (513, 256, 64),
+                                   # few wide tiles, short K: split 8 ways into clusters whose rings are then cut back so
+                                   # that all of them are resident at once (the parked plane must still fit the ring)
+                                   (512, 896, 896), (256, 1152, 896), (130, 896, 896), (32, 2304, 3584)])
 def test_gemm_matches_numpy(T, N, K):
     import tffn
     rng = np.random.default_rng([T, N, K])
