@@ -143,7 +143,7 @@ void tffn_session_free(tffn_session* s);
 typedef struct tffn_tp tffn_tp;
 int tffn_tp_unique_id(uint8_t* id128);
 int tffn_tp_create(const uint8_t* id128, int tp_rank, int tp_size, int device, tffn_tp** out);
-void tffn_tp_free(tffn_tp* tp);
+void tffn_tp_free(tffn_tp* tp); /* after every session created with it has been freed */
 /* Host-only: what rank tp_rank of tp_size owns of a model with this config (only the dimensions of cfg
  * are read): out8 = {first query head, query heads, first kv head, kv heads, first intermediate row,
  * intermediate rows, first LM-head row, LM-head rows}. With more ranks than kv heads, tp_size / kv_heads
