@@ -75,7 +75,7 @@ void tffn_tokenizer_free(tffn_tokenizer* t);
 int tffn_tokenizer_encode(const tffn_tokenizer* t, const char* text, uint32_t* ids, int cap);
 /* returns the number of bytes of the decoded text (without NUL; may exceed cap), <0 on error */
 int tffn_tokenizer_decode(const tffn_tokenizer* t, const uint32_t* ids, int n, char* out, int cap);
-/* The byte-level BPE that Qwen2's tokenizer.json specifies (added tokens cut out, the Qwen2 pre-tokenizer
+/* The byte-level BPE that Qwen2's tokenizer.json specifies (added tokens cut out, NFC, the Qwen2 pre-tokenizer
  * pattern, GPT-2's byte-to-unicode map, merges lowest rank first), same calling convention. The reference's
  * encoder (inference/src/io/tokenizer.cpp:86-135) implements none of this and drops spaces and newlines; its
  * authors tokenise with HF instead (tools/tokenize_correctly.py:11-36). tffn_tokenizer_encode / _decode keep

@@ -458,6 +458,119 @@ void utf8_points(const std::string& s, std::vector<uint32_t>& cps, std::vector<s
     offs.push_back(s.size());
 }
 
+// ---- NFC (Unicode Standard Annex 15), the normaliser Qwen2's tokenizer.json runs before the pre-tokenizer
+uint32_t ccc_of(uint32_t cp) {
+    size_t lo = 0, hi = sizeof kUnicodeCcc / sizeof kUnicodeCcc[0];
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (kUnicodeCcc[mid][0] < cp) lo = mid + 1;
+        else if (kUnicodeCcc[mid][0] > cp) hi = mid;
+        else return kUnicodeCcc[mid][1];
+    }
+    return 0;
+}
+constexpr uint32_t kSBase = 0xAC00, kLBase = 0x1100, kVBase = 0x1161, kTBase = 0x11A7;
+constexpr uint32_t kLCount = 19, kVCount = 21, kTCount = 28, kNCount = kVCount * kTCount, kSCount = kLCount * kNCount;
+void decompose_into(uint32_t cp, std::vector<uint32_t>& out) {
+    if (cp >= kSBase && cp < kSBase + kSCount) {  // Hangul syllable: arithmetic
+        const uint32_t sidx = cp - kSBase;
+        out.push_back(kLBase + sidx / kNCount);
+        out.push_back(kVBase + (sidx % kNCount) / kTCount);
+        if (sidx % kTCount) out.push_back(kTBase + sidx % kTCount);
+        return;
+    }
+    size_t lo = 0, hi = sizeof kUnicodeDecomp / sizeof kUnicodeDecomp[0];
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (kUnicodeDecomp[mid][0] < cp) lo = mid + 1;
+        else if (kUnicodeDecomp[mid][0] > cp) hi = mid;
+        else {
+            decompose_into(kUnicodeDecomp[mid][1], out);  // decompositions nest a few levels at most
+            if (kUnicodeDecomp[mid][2]) decompose_into(kUnicodeDecomp[mid][2], out);
+            return;
+        }
+    }
+    out.push_back(cp);
+}
+bool compose_pair(uint32_t a, uint32_t b, uint32_t* c) {
+    if (a >= kLBase && a < kLBase + kLCount && b >= kVBase && b < kVBase + kVCount) {
+        *c = kSBase + ((a - kLBase) * kVCount + (b - kVBase)) * kTCount;
+        return true;
+    }
+    if (a >= kSBase && a < kSBase + kSCount && (a - kSBase) % kTCount == 0 && b > kTBase && b < kTBase + kTCount) {
+        *c = a + (b - kTBase);
+        return true;
+    }
+    size_t lo = 0, hi = sizeof kUnicodeCompose / sizeof kUnicodeCompose[0];
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        const uint32_t* e = kUnicodeCompose[mid];
+        if (e[0] < a || (e[0] == a && e[1] < b)) lo = mid + 1;
+        else if (e[0] > a || (e[0] == a && e[1] > b)) hi = mid;
+        else {
+            *c = e[2];
+            return true;
+        }
+    }
+    return false;
+}
+// NFC of well-formed UTF-8; text without a code point from U+0300 on is in NFC already and returned as it is,
+// and so is text with a malformed byte (re-encoding would change its bytes).
+std::string nfc_utf8(const std::string& s) {
+    bool plain = true;
+    for (unsigned char c : s)
+        if (c >= 0xCC) { plain = false; break; }  // lead bytes below 0xCC encode code points below U+0300
+    if (plain) return s;
+    std::vector<uint32_t> cps;
+    std::vector<size_t> offs;
+    utf8_points(s, cps, offs);
+    for (size_t i = 0; i < cps.size(); ++i) {
+        const size_t len = offs[i + 1] - offs[i];
+        const uint32_t cp = cps[i];
+        const size_t want = cp < 0x80 ? 1 : cp < 0x800 ? 2 : cp < 0x10000 ? 3 : 4;
+        if (len != want || cp > 0x10FFFF || (cp >= 0xD800 && cp < 0xE000)) return s;  // malformed or overlong
+    }
+    std::vector<uint32_t> d;
+    d.reserve(cps.size() + 8);
+    for (uint32_t cp : cps) decompose_into(cp, d);
+    // canonical ordering: inside every run of non-starters, ascending combining class, stable
+    for (size_t i = 1; i < d.size(); ++i) {
+        const uint32_t cc = ccc_of(d[i]);
+        if (cc == 0) continue;
+        size_t j = i;
+        while (j > 0) {
+            const uint32_t pc = ccc_of(d[j - 1]);
+            if (pc == 0 || pc <= cc) break;
+            std::swap(d[j - 1], d[j]);
+            --j;
+        }
+    }
+    // canonical composition: a character combines with the last starter unless something between them blocks it
+    std::vector<uint32_t> out;
+    out.reserve(d.size());
+    size_t starter = (size_t)-1;
+    uint32_t last_cc = 0;
+    for (uint32_t ch : d) {
+        const uint32_t cc = ccc_of(ch);
+        if (starter != (size_t)-1) {
+            const bool adjacent = out.size() - 1 == starter;
+            const bool blocked = !adjacent && (last_cc == 0 || last_cc >= cc);
+            uint32_t c;
+            if (!blocked && compose_pair(out[starter], ch, &c)) {
+                out[starter] = c;
+                continue;
+            }
+        }
+        if (cc == 0) starter = out.size();
+        out.push_back(ch);
+        last_cc = cc;
+    }
+    std::string r;
+    r.reserve(s.size());
+    for (uint32_t cp : out) put_utf8(r, cp);
+    return r;
+}
+
 // end (exclusive, in code points) of the pre-tokenizer match that starts at i: the pattern's alternatives in order
 size_t pretok_match(const std::vector<uint32_t>& cp, size_t i) {
     const size_t n = cp.size();
@@ -544,8 +657,9 @@ void Tokenizer::bpe_piece(const std::string& bytes, std::vector<uint32_t>& out) 
 
 std::vector<uint32_t> Tokenizer::encode_bpe(const std::string& text) const {
     std::vector<uint32_t> out;
-    auto plain = [&](const std::string& t) {
-        if (t.empty()) return;
+    auto plain = [&](const std::string& raw) {
+        if (raw.empty()) return;
+        const std::string t = nfc_utf8(raw);  // tokenizer.json: normalizer NFC, then the Split pre-tokenizer
         std::vector<uint32_t> cps;
         std::vector<size_t> offs;
         utf8_points(t, cps, offs);

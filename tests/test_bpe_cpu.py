@@ -1,6 +1,7 @@
 """The byte-level BPE encoder and decoder (Tokenizer.encode_bpe / decode_bpe, the CLI's --bpe) against the
-HF `tokenizers` library on a tokenizer.json of the Qwen2 layout: added ChatML tokens, the Qwen2 pre-tokenizer
-pattern as a Split step, ByteLevel without its own regex, BPE merges learned here on a small corpus.
+HF `tokenizers` library on a tokenizer.json of the Qwen2 layout: added ChatML tokens, the NFC normaliser, the
+Qwen2 pre-tokenizer pattern as a Split step, ByteLevel without its own regex, BPE merges learned here on a small
+corpus.
 The reference has no such encoder (inference/src/io/tokenizer.cpp:86-135 drops spaces and newlines); its authors
 run HF for correct ids (tools/tokenize_correctly.py:11-36), which is what this test compares with, id for id."""
 import os
@@ -31,8 +32,9 @@ CORPUS = [
 
 @pytest.fixture(scope="module")
 def tok_dir(tmp_path_factory):
-    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    from tokenizers import Regex, Tokenizer, decoders, models, normalizers, pre_tokenizers, trainers
     t = Tokenizer(models.BPE())
+    t.normalizer = normalizers.NFC()
     t.pre_tokenizer = pre_tokenizers.Sequence([
         pre_tokenizers.Split(Regex(QWEN2_PATTERN), behavior="isolated", invert=False),
         pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False),
@@ -66,6 +68,9 @@ CASES = [
     "text<|endoftext|>more text <|im_end|",
     "fibonacci(n - 1) + fibonacci(n - 2)",
     " non-breaking em space　ideographic",
+    # not in NFC: combining sequences, marks out of canonical order, Hangul jamo, singletons
+    "cafe\u0301 A\u030a a\u0323\u0307 a\u0307\u0323 \u1100\u1161\u11a8 \u1112\u1161 \u212b \u2126 \u0958 q\u0307\u0323",
+    "\u0301leading mark, \u0041\u0300\u0301\u0302 stacked, \uac00\u11a8 syllable + final",
 ]
 
 
@@ -81,15 +86,36 @@ def test_bpe_encode_matches_hf(tok_dir):
 
 
 def test_bpe_decode_round_trip(tok_dir):
+    import unicodedata
+
     import tffn
     d, hf = tok_dir
     ours = tffn.Tokenizer(d)
     for text in CASES:
         ids = ours.encode_bpe(text)
-        assert ours.decode_bpe(ids) == text
+        want = unicodedata.normalize("NFC", text)  # what the normaliser makes of the input
+        assert ours.decode_bpe(ids) == want
         # token by token, as the command line prints them: the bytes concatenate to the same text
         raw = b"".join(_decode_bytes(ours, [i]) for i in ids)
-        assert raw.decode("utf-8") == text
+        assert raw.decode("utf-8") == want
+
+
+def test_nfc_matches_unicodedata_on_seeded_strings(tok_dir):
+    """the normaliser alone (through encode + decode, which are otherwise lossless): random strings over starters,
+    combining marks of several classes, precomposed letters, Hangul jamo and syllables, compatibility singletons"""
+    import random
+    import unicodedata
+
+    import tffn
+    d, _ = tok_dir
+    ours = tffn.Tokenizer(d)
+    rng = random.Random(11)
+    pool = ([chr(c) for c in range(0x300, 0x330)] + [chr(c) for c in (0x5B0, 0x5B4, 0x5BC, 0x64B, 0x651, 0x93C, 0x94D, 0xF71, 0xF72, 0xF74)]
+            + list("aeiouAEOUcnsyzdD ") + list("áàâäåçéèêëñöüÅΩǺẛ̣") + [chr(c) for c in (0x1100, 0x1102, 0x1161, 0x1163, 0x11A8, 0x11AF, 0xAC00, 0xAC01, 0xD55C)]
+            + [chr(c) for c in (0x212B, 0x2126, 0x0340, 0x0341, 0x0343, 0x0344, 0x0958, 0x0F43, 0xFB1D, 0x1E9B, 0x1D15E)])
+    for _ in range(500):
+        text = "".join(rng.choice(pool) for _ in range(rng.randint(1, 12)))
+        assert ours.decode_bpe(ours.encode_bpe(text)) == unicodedata.normalize("NFC", text), [hex(ord(c)) for c in text]
 
 
 def _decode_bytes(tok, ids):
