@@ -581,16 +581,16 @@ int attention_splits(int T, int nh, int nkv, int hd, int max_ctx, const AttnWork
     // what one SM can take in, and a launch without splits needs no merge (a partial write, a ticket and a
     // second read-back cost 4 to 6 us per launch, measured with two and three splits). Splits are used only
     // when there are fewer (token, kv head) units than half the SMs and the context is long: a split
-    // must save more key-loop time (about 0.5 us per 128-key stage of 64-wide heads) than the merge costs,
-    // so each split gets at least 1024 keys of 64-wide heads, 512 of 128-wide ones: the same bytes (batch 1 at
-    // a few hundred keys of context: 0.94 -> 0.82 ms per token without splits).
+    // must save more key-loop time (about 0.5 us per 128-key stage) than the merge costs, so each split
+    // gets at least 1024 keys (batch 1 at a few hundred keys of context: 0.94 -> 0.82 ms per token
+    // without splits; halving the minimum for 128-wide heads gained 1.4 us per launch for 32 sequences on a
+    // quarter of the 7B shape's heads and cost batch 1 on the 1.5B shape 16 %: 576 -> 483 tok/s).
     const int G = nh / nkv;
     const int units = T * nkv;
     int splits = 1;
     if (units * 2 <= num_sms) {
         splits = num_sms / units;
-        const int min_rows = hd > 64 ? kMinSplitRows * 64 / hd : kMinSplitRows;
-        const int max_splits = (max_ctx + min_rows - 1) / min_rows;
+        const int max_splits = (max_ctx + kMinSplitRows - 1) / kMinSplitRows;
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
         while (splits > 1 && ((size_t)units * splits * G * (hd + 2) > ws.partial_floats || units > ws.num_counters))
