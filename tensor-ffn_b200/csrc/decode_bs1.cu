@@ -169,9 +169,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_bs1_oproj(Bs1Ctx c, Bs1Layer
 }
 
 // ------------------------------------------------------------------------------------------ fused SwiGLU
-// Consumer warps; warp kFfnWarps is the copy producer. A warp takes four records at a time and a CTA owns
-// 33 or 34 records of the 0.5B shape: nine warps take the nine chunks at once, eight would leave one warp
-// with two in a row.
+// Consumer warps; warp kFfnWarps is the copy producer. A warp takes a chunk of up to four records at a time
+// (fewer when the ring is short, see the kernel).
 constexpr int kFfnWarps = 9;
 constexpr int kFfnThreads = (kFfnWarps + 1) * 32;
 constexpr int kSmsLeftToAttention = 4;
@@ -307,11 +306,16 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
     // and row g + 8 the same of record 2 + g / 4; without it, row g = (record g / 2, {gate, up}[g % 2])
     const int j_lo = expert ? (g >> 2) : (g >> 1), j_hi = 2 + (g >> 2);
     const size_t koff = expert ? (size_t)(g & 1) * row_bytes + (size_t)((g >> 1) & 1) * rec_bytes : (size_t)(g & 1) * row_bytes;
-    const int nchunks = (nrec + 3) >> 2;
+    // Records per chunk. The ring holds S consecutive records, so only S / CH chunks can be worked on at a
+    // time: with four records per chunk a ring of 19 stages (hidden 896) keeps fewer than five of the nine
+    // warps busy, one of 8 (hidden 2048) two. Smaller chunks use a part of the 16 MMA rows only (the unused
+    // rows repeat the chunk's last record and are dropped), which costs less than idle warps.
+    const int CH = S >= 4 * kFfnWarps ? 4 : (S >= 2 * kFfnWarps ? 2 : 1);
+    const int nchunks = (nrec + CH - 1) / CH;
     const int nchunk16 = H >> 3;
     bool ok = true;
     for (int ch = warp; ch < nchunks && ok; ch += kFfnWarps) {
-        const int r0 = ch * 4, nr = min(4, nrec - r0);
+        const int r0 = ch * CH, nr = min(CH, nrec - r0);
         for (int j = 0; j < nr && ok; ++j) {
             const int r = r0 + j;
             ok = item_issued(s_issued, r, c.status) && mbar_wait(&full[r % S], (uint32_t)(r / S) & 1u, c.status, DEV_ERR_FULL_WAIT);
