@@ -326,7 +326,9 @@ __global__ void __launch_bounds__(kFfnThreads, 1) k_bs1_ffn(Bs1Ctx c, Bs1Layer l
         // records past the end of this CTA's slice stand in as copies of the last one; their results are dropped
         auto stage_of = [&](int j) { return ring + (size_t)((r0 + min(j, nr - 1)) % S) * L.stage_bytes; };
         float v_lo, v_hi = 0.f;
-        if (expert) mma_rows_dot<true>(stage_of(j_lo) + koff, stage_of(j_hi) + koff, H, xs, lane, v_lo, v_hi);
+        // with the expert, chunks of one or two records fill the lower eight MMA rows only: the upper half then
+        // stays empty instead of loading copies
+        if (expert && CH > 2) mma_rows_dot<true>(stage_of(j_lo) + koff, stage_of(j_hi) + koff, H, xs, lane, v_lo, v_hi);
         else mma_rows_dot<false>(stage_of(j_lo) + koff, nullptr, H, xs, lane, v_lo, v_hi);
         // a gate row and its up row are neighbours in g: lane ^ 4
         const float p_lo = __shfl_xor_sync(0xffffffffu, v_lo, 4), p_hi = __shfl_xor_sync(0xffffffffu, v_hi, 4);
